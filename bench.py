@@ -1,0 +1,577 @@
+#!/usr/bin/env python
+"""Benchmark of the accelerated path on N GPUs of one node.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload spmv|spmm|pcg|bgemm|gemm]
+                    [--impl ours|reference]
+
+Default workload: CSR SpMV fp64 on the large skewed matrix (2^23 rows, power-law row
+lengths with mean 16 capped at 4096, int64 offsets/indices, about 1.34e8 entries), rows
+partitioned by nnz over the GPUs, x replicated.  A step is one y = A x pass.  The inputs
+of a pass (2.35 GB; 0.29 GB per GPU at N = 8) are larger than the 126 MB L2, so no flush
+is needed between timed iterations.
+
+Prints ONE JSON line on rank 0.  `value` is the whole-job throughput with operands
+resident in HBM (CUDA events around exactly K steps, barrier + synchronize on both
+sides, max over ranks); `e2e` is the same metric through the emitted-module ABI
+(py_spmv with pinned host buffers: host-to-device copies of every operand and the
+device-to-host copy of y inside the timed region); `roofline` relates the dominant
+kernel to the measured HBM copy bandwidth; `cpu_baseline` is the CPU restatement of the
+reference's emitted loop timed on this box's cores (rank 0, N = 1 only).
+
+`--impl reference` times that CPU restatement alone, with all host threads, on the same
+configuration (the reference's own Kokkos build cannot be produced without LLVM/MLIR and
+Kokkos, which are not available offline).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+FALLBACK_HBM_GBS = 6650.0
+
+
+# ---------------------------------------------------------------------------
+# helpers
+# ---------------------------------------------------------------------------
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        with open(path) as f:
+            return json.load(f), "measured"
+    return {"hbm_gbs": FALLBACK_HBM_GBS, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons of one GPU while the timed region runs."""
+
+    def __init__(self, index: int, period_s: float = 0.02):
+        self.index, self.period = index, period_s
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self._nvml = pynvml
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self._nvml = None
+
+    def _loop(self):
+        nv = self._nvml
+        names = {
+            "hw_slowdown": getattr(nv, "nvmlClocksThrottleReasonHwSlowdown", 0x8),
+            "hw_thermal_slowdown": getattr(nv, "nvmlClocksThrottleReasonHwThermalSlowdown", 0x40),
+            "sw_thermal_slowdown": getattr(nv, "nvmlClocksThrottleReasonSwThermalSlowdown", 0x20),
+            "sw_power_cap": getattr(nv, "nvmlClocksThrottleReasonSwPowerCap", 0x4),
+            "hw_power_brake": getattr(nv, "nvmlClocksThrottleReasonHwPowerBrakeSlowdown", 0x80),
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM))
+                mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self._h)
+                for k, bit in names.items():
+                    if mask & bit:
+                        self.reasons.add(k)
+            except Exception:
+                pass
+            self._stop.wait(self.period)
+
+    def start(self):
+        if self._nvml is not None:
+            self._thread = threading.Thread(target=self._loop, daemon=True)
+            self._thread.start()
+
+    def stop(self):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+        return {"sm_mhz": statistics.median(self.samples) if self.samples else None,
+                "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+def physical_cores() -> int:
+    try:
+        import psutil
+        return psutil.cpu_count(logical=False) or os.cpu_count() or 1
+    except Exception:
+        return os.cpu_count() or 1
+
+
+def host_threads() -> int:
+    try:
+        avail = len(os.sched_getaffinity(0))
+    except Exception:
+        avail = os.cpu_count() or 1
+    return max(1, min(avail, physical_cores()))
+
+
+def oracle_native():
+    """The CPU restatement built for this box's cores (falls back to the portable build)."""
+    from oracle import oracle
+    try:
+        oracle.build(native=True)
+        oracle.lib(native=True)
+        return oracle, True
+    except Exception:
+        return oracle, False
+
+
+# ---------------------------------------------------------------------------
+# workloads: each returns host data + byte/flop accounting
+# ---------------------------------------------------------------------------
+def make_workload(name: str, small: bool):
+    from lapis_b200 import workloads as w
+    if name == "spmv":
+        d = w.spmv_power_law(1 << 16 if small else 1 << 23)
+        n, nnz = d["shape"][0], int(d["crd"].size)
+        d.update(unit="GB/s", metric="csr_spmv_hbm_gbs", dtype="f64", unit_scale=1e-9,
+                 work=w.spmv_bytes(n, n, nnz, 8), label=f"CSR SpMV fp64 power-law rows (config 2): {n} rows, {nnz} nnz, int64 indices")
+    elif name == "spmm":
+        d = w.spmm_uniform(1 << 13 if small else 1 << 21)
+        n, nnz = d["shape"][0], int(d["crd"].size)
+        d.update(unit="GB/s", metric="csr_spmm_hbm_gbs", dtype="f64", unit_scale=1e-9,
+                 work=w.spmm_bytes(n, n, nnz, 64, 8), label=f"CSR SpMM fp64 (config 3): {n} rows, 32 nnz/row, k=64, int64 indices")
+    elif name == "pcg":
+        g = 256 if small else 4096
+        d = w.pcg_laplacian(g)
+        n, nnz = d["shape"][0], int(d["crd"].size)
+        d.update(unit="it/s", metric="pcg_iterations_per_s", dtype="f64", unit_scale=1.0, work=1,
+                 bytes_per_step=w.pcg_bytes_per_iteration(n, nnz, 4),
+                 label=f"PCG fp64, 5-point Laplacian {g}x{g} (config 5), Jacobi, int32 indices")
+    elif name == "bgemm":
+        b, m = (64, 128) if small else (4096, 128)
+        d = w.batched_gemm(b, m)
+        d.update(unit="TFLOP/s", metric="batched_gemm_fp32_tflops", dtype="f32 (3xTF32)", unit_scale=1e-12,
+                 work=w.gemm_flops(b, m, m, m), bytes_per_step=w.gemm_bytes(b, m, m, m),
+                 label=f"batched GEMM fp32 (config 4a): {b} x {m}^3")
+    elif name == "gemm":
+        m = 1024 if small else 8192
+        d = w.dense_gemm(m)
+        d.update(unit="TFLOP/s", metric="gemm_fp32_tflops", dtype="f32 (3xTF32)", unit_scale=1e-12,
+                 work=w.gemm_flops(1, m, m, m), bytes_per_step=w.gemm_bytes(1, m, m, m),
+                 label=f"GEMM fp32 (config 4b): {m}^3")
+    else:
+        raise SystemExit(f"unknown workload {name}")
+    d["name"] = name
+    return d
+
+
+# ---------------------------------------------------------------------------
+# reference arm: the CPU restatement on the host cores
+# ---------------------------------------------------------------------------
+def run_reference(args, d):
+    oracle, native = oracle_native()
+    threads = host_threads()
+    name = d["name"]
+    budget_s = 120.0
+    if name in ("spmv", "spmm"):
+        pos, crd, val = d["pos"], d["crd"], d["val"]
+        n = len(pos) - 1
+
+        def make_step(rows):
+            p = np.ascontiguousarray(pos[:rows + 1])
+            if name == "spmv":
+                y = np.zeros(rows)
+                return lambda: oracle.spmv_inplace(p, crd, val, d["x"], y, threads, native)
+            C = np.zeros((rows, 64))
+            return lambda: oracle.spmm_inplace(p, crd, val, d["B"], C, threads, native)
+
+        rows = n
+        step = make_step(rows)
+        t0 = time.perf_counter(); step(); t1 = time.perf_counter() - t0
+        est = t1 * (args.steps + args.warmup)
+        if est > budget_s:
+            rows = max(1, int(n * budget_s / est))
+            step = make_step(rows)
+        frac_nnz = float(pos[rows]) / float(pos[n])
+        work = d["work"] * frac_nnz
+        sample = (f"rows [0, {rows}) of {n} ({100 * frac_nnz:.1f}% of the entries) per step, x/B whole; "
+                  f"throughput scaled by the entries processed")
+    elif name == "pcg":
+        # a solve of `steps` iterations on a grid small enough for the budget
+        g = int(round(len(d["b"]) ** 0.5))
+        from lapis_b200 import workloads as w
+        while True:
+            dd = w.pcg_laplacian(g)
+            t0 = time.perf_counter()
+            oracle.pcg(dd["pos"], dd["crd"], dd["val"], dd["b"], dd["dinv"], 0.0, 2, threads, native=native)
+            t1 = (time.perf_counter() - t0) / 2
+            if t1 * (args.steps + args.warmup) <= budget_s or g <= 256:
+                break
+            g //= 2
+        its = args.steps
+        step = None
+        sample = f"{g}x{g} grid, {its} iterations"
+        for _ in range(1):
+            oracle.pcg(dd["pos"], dd["crd"], dd["val"], dd["b"], dd["dinv"], 0.0, max(1, args.warmup), threads, native=native)
+        t0 = time.perf_counter()
+        oracle.pcg(dd["pos"], dd["crd"], dd["val"], dd["b"], dd["dinv"], 0.0, its, threads, native=native)
+        total = time.perf_counter() - t0
+        scale = (g * g) / float(len(d["b"]))
+        value = its / total * scale  # iterations/s rescaled to the full grid by rows (bandwidth-bound)
+        sample += f"; it/s scaled by rows to the {int(round(len(d['b']) ** 0.5))}^2 grid"
+        return finish_reference(args, d, value, total / its * 1e3, threads, native, sample)
+    else:
+        A, B = d["A"], d["B"]
+        if A.ndim == 2:
+            m = A.shape[0]
+            mm = m
+            while 2.0 * mm ** 3 / 0.3e9 / max(1, threads) * (args.steps + args.warmup) > budget_s and mm > 256:
+                mm //= 2
+            A, B = np.ascontiguousarray(A[:mm, :mm]), np.ascontiguousarray(B[:mm, :mm])
+            C = np.zeros((mm, mm), dtype=np.float32)
+            work = 2.0 * mm ** 3
+            sample = f"{mm}^3 sub-problem per step (naive loop order as emitted)"
+        else:
+            nb = A.shape[0]
+            bb = nb
+            while 2.0 * bb * A.shape[1] ** 3 / 1e9 / max(1, threads) * (args.steps + args.warmup) > budget_s and bb > 8:
+                bb //= 2
+            A, B = A[:bb], B[:bb]
+            C = np.zeros(A.shape, dtype=np.float32)
+            work = 2.0 * bb * A.shape[1] ** 3
+            sample = f"{bb} of {nb} problems per step"
+        lib = oracle.lib(native)
+        import ctypes
+        bt, M, K = (1, *A.shape) if A.ndim == 2 else A.shape
+        N = B.shape[-1]
+
+        def step():
+            lib.oracle_bgemm_f32(ctypes.c_int64(bt), ctypes.c_int64(M), ctypes.c_int64(N), ctypes.c_int64(K),
+                                 A.ctypes.data_as(ctypes.c_void_p), B.ctypes.data_as(ctypes.c_void_p),
+                                 C.ctypes.data_as(ctypes.c_void_p), ctypes.c_int(threads))
+    for _ in range(args.warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step()
+    total = time.perf_counter() - t0
+    value = work * args.steps / total * d["unit_scale"]
+    return finish_reference(args, d, value, total / args.steps * 1e3, threads, native, sample)
+
+
+def finish_reference(args, d, value, ms, threads, native, sample):
+    line = {
+        "impl": "reference", "metric": d["metric"], "value": value, "unit": d["unit"], "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": d["dtype"].split(" ")[0], "data": "synthetic",
+        "config": {"workload": d["label"]},
+        "cpu_baseline": {"value": value, "unit": d["unit"], "cores": threads, "kind": "port",
+                         "sample": sample + ("; -march=native build" if native else "; portable build"),
+                         "note": "CPU restatement of the emitted Kokkos loops (OpenMP); the reference's own Kokkos "
+                                 "build needs LLVM/MLIR and Kokkos, which are not available offline"},
+        "e2e": {"value": value, "unit": d["unit"], "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------
+# our arm
+# ---------------------------------------------------------------------------
+def run_ours(args, d, rank, world, local_rank):
+    import torch
+    import torch.distributed as dist
+
+    from lapis_b200 import KokkosBackend as KB
+    from lapis_b200 import device as D
+    from lapis_b200 import partition as part
+    from tests import mlir_modules as mm
+
+    dev = torch.device(f"cuda:{local_rank}")
+    torch.cuda.set_device(dev)
+    name = d["name"]
+    peaks, peak_kind = measured_peaks()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(step, steps, warmup):
+        for _ in range(warmup):
+            step()
+        barrier()
+        sampler = ClockSampler(local_rank)
+        sampler.start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            step()
+        e1.record()
+        barrier()
+        clocks = sampler.stop()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], dtype=torch.float64, device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms, clocks
+
+    launches_per_step = 1
+    e2e = None
+    kernel_name = ""
+    extra_cfg = {}
+    if name in ("spmv", "spmm"):
+        pos, crd, val = d["pos"], d["crd"], d["val"]
+        n = len(pos) - 1
+        bounds = part.partition_rows(pos, world)
+        r0, r1 = int(bounds[rank]), int(bounds[rank + 1])
+        lpos, lcrd, lval = part.row_block(pos, crd, val, r0, r1)
+        A = D.CsrMatrix.from_host(lpos, lcrd, lval, (r1 - r0, n), dev)
+        extra_cfg = {"partition": "contiguous row blocks, equal nnz", "rows_rank0": int(bounds[1] - bounds[0]),
+                     "replicated": "x" if name == "spmv" else "B"}
+        if name == "spmv":
+            xd = torch.as_tensor(d["x"]).to(dev)
+            yd = torch.zeros(r1 - r0, dtype=torch.float64, device=dev)
+            step = lambda: A.spmv(xd, yd, accumulate=False)
+            kernel_name = "spmv_stream_kernel"
+            host_in = [lpos, lcrd, lval, d["x"]]
+            module = KB.KokkosBackend(decompose_tensors=True).compile(mm.spmv(mm.CSR64))
+        else:
+            Bd = torch.as_tensor(d["B"]).to(dev)
+            Cd = torch.zeros((r1 - r0, 64), dtype=torch.float64, device=dev)
+            step = lambda: A.spmm(Bd, Cd, accumulate=False)
+            kernel_name = "spmm_row_kernel"
+            host_in = [lpos, lcrd, lval, d["B"]]
+            module = KB.KokkosBackend(decompose_tensors=True).compile(mm.spmm(mm.CSR64))
+        # ---- e2e through the emitted-module ABI with pinned host buffers -------------
+        pinned = [torch.as_tensor(np.ascontiguousarray(a)).pin_memory() for a in host_in]
+        out_shape = (r1 - r0,) if name == "spmv" else (r1 - r0, 64)
+        out = torch.zeros(out_shape, dtype=torch.float64).pin_memory()
+        pnp = [t.numpy() for t in pinned]
+        spec = ((r1 - r0, n), (len(lpos), len(lcrd), len(lval)))
+        fn = module.spmv if name == "spmv" else module.spmm
+
+        def e2e_step():
+            fn(pnp[0], pnp[1], pnp[2], spec, pnp[3], out.numpy())
+
+        h2d = sum(int(t.numel() * t.element_size()) for t in pinned) + int(out.numel() * 8)
+        d2h = int(out.numel() * 8)
+        e2e_steps = max(1, min(args.steps, 3))
+        e2e_step()
+        if world > 1:
+            dist.barrier()
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            e2e_step()
+        t_e2e = time.perf_counter() - t0
+        if world > 1:
+            t = torch.tensor([t_e2e], dtype=torch.float64, device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            t_e2e = float(t.item())
+        e2e = {"value": d["work"] * e2e_steps / t_e2e * d["unit_scale"], "unit": d["unit"],
+               "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps,
+               "api": f"KokkosBackend.compile(...).{name} -> py_{name}_f64_i64, pinned host buffers"}
+        del pinned, out
+        algo_bytes_rank = (len(lcrd) * 16 + len(lpos) * 8 + (8 * n + 8 * (r1 - r0)) * (1 if name == "spmv" else 64))
+    elif name == "pcg":
+        from lapis_b200.dist import DistPcg
+        n = d["shape"][0]
+        solver = DistPcg(d["pos"], d["crd"], d["val"], (n, n), d["b"], d["dinv"], dev, use_graph=True)
+        state = {}
+
+        def solve(k):
+            state["out"] = solver.solve(0.0, k, check_every=50)
+
+        # the timed region is one solve of K iterations; warm-up is a solve of W iterations
+        solver_w = DistPcg(d["pos"], d["crd"], d["val"], (n, n), d["b"], d["dinv"], dev, use_graph=True)
+        solver_w.solve(0.0, max(1, args.warmup))
+        solver.solve(0.0, args.steps)  # captures the graph; timed run below replays it
+        kernel_name = "spmv_stream_kernel + pcg_update_kernel + pcg_direction_kernel"
+        launches_per_step = 5 if world == 1 else 7
+        steps_holder = {"k": args.steps}
+        ms, clocks = timed(lambda: solve(steps_holder["k"]), 1, 0)
+        it = state["out"][1]
+        value = it / (ms * 1e-3)
+        algo_bytes_rank = d["bytes_per_step"] / world
+        # e2e: py_pcg with pinned host buffers (single process path only)
+        if world == 1:
+            module = KB.KokkosBackend(decompose_tensors=True).compile(mm.pcg(mm.CSR32))
+            pinned = [torch.as_tensor(np.ascontiguousarray(a)).pin_memory().numpy()
+                      for a in (d["pos"], d["crd"], d["val"], d["b"], d["dinv"])]
+            spec = ((n, n), (n + 1, len(d["crd"]), len(d["val"])))
+            t0 = time.perf_counter()
+            _, it2, _ = module.pcg(pinned[0], pinned[1], pinned[2], spec, pinned[3], pinned[4], 0.0, args.steps)
+            t_e2e = time.perf_counter() - t0
+            e2e = {"value": it2 / t_e2e, "unit": "it/s", "h2d_bytes_per_step": sum(a.nbytes for a in pinned) / it2,
+                   "d2h_bytes_per_step": 8 * n / it2, "steps": it2,
+                   "api": "KokkosBackend.compile(...).pcg -> py_pcg_f64_i32, pinned host buffers, copies amortised over the solve"}
+        return emit(args, d, value, ms / max(1, it), clocks, e2e, launches_per_step * it * world, kernel_name,
+                    algo_bytes_rank, ms / max(1, it), peaks, peak_kind, world, rank, extra_cfg, bound="hbm")
+    else:
+        A_h, B_h = d["A"], d["B"]
+        if A_h.ndim == 3:
+            nb = A_h.shape[0]
+            per = nb // world
+            sl = slice(rank * per, (rank + 1) * per if rank < world - 1 else nb)
+            A_h, B_h = A_h[sl], B_h[sl]
+            extra_cfg = {"partition": "by batch"}
+        Ad, Bd = torch.as_tensor(A_h).to(dev), torch.as_tensor(B_h).to(dev)
+        Cd = torch.zeros(A_h.shape[:-1] + (B_h.shape[-1],), dtype=torch.float32, device=dev)
+        step = lambda: D.bgemm(Ad, Bd, Cd)
+        kernel_name = "bgemm kernel"
+        module = KB.KokkosBackend().compile(mm.MATMUL if A_h.ndim == 2 else mm.BATCH_MATMUL)
+        pa, pb = torch.as_tensor(A_h).pin_memory(), torch.as_tensor(B_h).pin_memory()
+        pc = torch.zeros(Cd.shape, dtype=torch.float32).pin_memory()
+        module.forward(pa.numpy(), pb.numpy(), pc.numpy())
+        t0 = time.perf_counter()
+        module.forward(pa.numpy(), pb.numpy(), pc.numpy())
+        t_e2e = time.perf_counter() - t0
+        if world > 1:
+            t = torch.tensor([t_e2e], dtype=torch.float64, device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            t_e2e = float(t.item())
+        e2e = {"value": d["work"] / t_e2e * d["unit_scale"], "unit": d["unit"],
+               "h2d_bytes_per_step": int(pa.numel() + pb.numel() + pc.numel()) * 4, "d2h_bytes_per_step": int(pc.numel()) * 4,
+               "steps": 1, "api": "KokkosBackend.compile(...).forward -> py_(batch_)matmul_f32, pinned host buffers"}
+        algo_bytes_rank = d["bytes_per_step"] / world
+
+    ms, clocks = timed(step, args.steps, args.warmup)
+    ms_step = ms / args.steps
+    value = d["work"] / (ms_step * 1e-3) * d["unit_scale"]
+    bound = "hbm" if name in ("spmv", "spmm", "bgemm") else "tensor"
+    emit(args, d, value, ms_step, clocks, e2e, launches_per_step * args.steps * world, kernel_name, algo_bytes_rank,
+         ms_step, peaks, peak_kind, world, rank, extra_cfg, bound=bound)
+
+
+# DRAM bytes per launch of the dominant kernel from the committed ncu captures under profiles/
+# (dram__bytes_read.sum + dram__bytes_write.sum, scaled to a full launch by entries processed).
+NCU_TRAFFIC = {}
+
+
+def emit(args, d, value, ms_step, clocks, e2e, launches, kernel_name, algo_bytes_rank, kernel_ms, peaks, peak_kind,
+         world, rank, extra_cfg, bound):
+    if rank != 0:
+        return
+    if bound == "hbm":
+        achieved = algo_bytes_rank / (kernel_ms * 1e-3) * 1e-9
+        peak = float(peaks["hbm_gbs"])
+        roof = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                "traffic": NCU_TRAFFIC.get(d["name"]), "kernel": kernel_name, "peak_source": f"{peak_kind} copy bandwidth",
+                "algorithmic_bytes_per_launch": algo_bytes_rank, "frac_of_8TBs": achieved / 8000.0}
+    else:
+        # 3xTF32: three tensor-core products per fp32 product; dense TF32 peak taken as half the measured bf16 peak
+        tf32_peak = float(peaks["bf16_tflops_sustained"]) / 2.0
+        achieved = 3.0 * d["work"] / world / (kernel_ms * 1e-3) * 1e-12
+        roof = {"bound": "tensor", "achieved": achieved, "peak": tf32_peak, "unit": "TFLOP/s", "frac": achieved / tf32_peak,
+                "traffic": NCU_TRAFFIC.get(d["name"]), "kernel": kernel_name,
+                "peak_source": f"{peak_kind} bf16 sustained / 2 (TF32); achieved counts the 3 TF32 products per fp32 product"}
+    line = {
+        "metric": d["metric"], "value": value, "unit": d["unit"], "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": d["dtype"], "data": "synthetic",
+        "config": {"workload": d["label"], "l2": "inputs larger than L2, no flush between iterations", **extra_cfg},
+        "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "roofline": roof,
+    }
+    if world == 1 and not args.no_cpu_baseline:
+        line["cpu_baseline"] = cpu_baseline(d)
+    print(json.dumps(line), flush=True)
+
+
+def cpu_baseline(d):
+    """The CPU restatement timed on this box's cores on a bounded sample (about 10-30 s)."""
+    oracle, native = oracle_native()
+    threads = host_threads()
+    name = d["name"]
+    budget = 15.0
+    if name == "spmv":
+        y = np.zeros(len(d["pos"]) - 1)
+        step = lambda: oracle.spmv_inplace(d["pos"], d["crd"], d["val"], d["x"], y, threads, native)
+        work, sample = d["work"], "the whole matrix, repeated"
+    elif name == "spmm":
+        C = np.zeros((len(d["pos"]) - 1, 64))
+        step = lambda: oracle.spmm_inplace(d["pos"], d["crd"], d["val"], d["B"], C, threads, native)
+        work, sample = d["work"], "the whole matrix, repeated"
+    elif name == "pcg":
+        its = 5
+        step = lambda: oracle.pcg(d["pos"], d["crd"], d["val"], d["b"], d["dinv"], 0.0, its, threads, native=native)
+        work, sample = its, f"{its} iterations per repetition on the full grid"
+    else:
+        A, B = d["A"], d["B"]
+        if A.ndim == 2:
+            m = min(A.shape[0], 1024)
+            A, B = np.ascontiguousarray(A[:m, :m]), np.ascontiguousarray(B[:m, :m])
+            sample = f"{m}^3 sub-problem (naive loop order as emitted)"
+            work = 2.0 * m ** 3
+        else:
+            nb = min(A.shape[0], 256)
+            A, B = A[:nb], B[:nb]
+            sample = f"{nb} problems of {A.shape[1]}^3"
+            work = 2.0 * nb * A.shape[1] ** 3
+        C = np.zeros(A.shape[:-1] + (B.shape[-1],), dtype=np.float32)
+        step = lambda: oracle.bgemm(A, B, C, threads, native)
+    step()
+    reps, t0 = 0, time.perf_counter()
+    while True:
+        step()
+        reps += 1
+        el = time.perf_counter() - t0
+        if el > budget or reps >= 50:
+            break
+    return {"value": work * reps / el * d["unit_scale"], "unit": d["unit"], "cores": threads, "kind": "port",
+            "sample": f"{sample}; {reps} repetitions in {el:.1f} s; " + ("-march=native build" if native else "portable build"),
+            "ms_per_step": el / reps * 1e3}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=None)
+    ap.add_argument("--warmup", type=int, default=None)
+    ap.add_argument("--workload", default="spmv", choices=["spmv", "spmm", "pcg", "bgemm", "gemm"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--small", action="store_true", help="reduced sizes (for profiler captures and quick checks)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    defaults = {"spmv": (500, 10), "spmm": (50, 5), "pcg": (200, 5), "bgemm": (200, 10), "gemm": (20, 3)}
+    if args.steps is None:
+        args.steps = defaults[args.workload][0] if args.impl == "ours" else 10
+    if args.warmup is None:
+        args.warmup = defaults[args.workload][1] if args.impl == "ours" else 3
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        if rank != 0:
+            return 0
+        d = make_workload(args.workload, args.small)
+        run_reference(args, d)
+        return 0
+
+    import torch
+    import torch.distributed as dist
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: lapis_b200 has no CPU path")
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local_rank}"))
+    d = make_workload(args.workload, args.small)
+    try:
+        run_ours(args, d, rank, world, local_rank)
+    finally:
+        if world > 1:
+            dist.barrier()
+            dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,192 @@
+/*
+ * lapis_b200 -- C ABI of the B200-native replacement for the kernels that the
+ * LAPIS Kokkos emitter produces for CSR SpMV / SpMM, dense and batched matmul,
+ * and the PCG solve loop.
+ *
+ * Two layers, both plain C (pointers and sizes only):
+ *
+ *  1. The emitted-module ABI (host buffers in, host-visible results out).  These
+ *     are the symbols a LAPIS-generated module exports and its generated Python
+ *     class binds: lapis_initialize / lapis_finalize and one py_<func> per public
+ *     function, taking StridedMemRefType descriptors.  One LAPIS module is
+ *     compiled for one index width, and C has no overloading, so the entry point
+ *     names carry the element / index types as a suffix; the Python
+ *     `KokkosBackend.compile()` binds the un-suffixed method name (`spmv`, `pcg`,
+ *     `forward`) to the right one.
+ *
+ *  2. The device-resident layer (lapis_b200_*): what a C++ caller that keeps
+ *     LAPIS::DualViews on the device does (benchmarks/spmv/main.cpp:52-62).
+ *     All pointers are device pointers on the current CUDA device; `stream` is a
+ *     cudaStream_t passed as void* (NULL = default stream).  Calls are
+ *     asynchronous on that stream unless stated otherwise.
+ *
+ * Error behaviour: the emitted code aborts the process (Kokkos::abort).  Here no
+ * entry point aborts: layer-2 functions return a status, layer-1 functions keep
+ * the emitted `void` signature and record the status, which the caller reads
+ * with lapis_last_error() (the Python binding raises).  There is no CPU
+ * fallback: without a usable CUDA device every compute entry point fails with
+ * LAPIS_ECUDA.
+ *
+ * Threading: like the emitted modules (LAPISSupport.hpp:114 keeps a plain static
+ * vector), one caller thread per process at a time.
+ *
+ * Citations are paths within the LAPIS project.
+ */
+#ifndef LAPIS_B200_H
+#define LAPIS_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes --------------------------------------------------------- */
+enum {
+  LAPIS_OK = 0,
+  LAPIS_EBADSHAPE = 1,   /* inconsistent sizes, mismatching contraction dimension */
+  LAPIS_ELAYOUT = 2,     /* descriptor is not C-contiguous (LAPISSupport.hpp:80-89 aborts) */
+  LAPIS_ECUDA = 3,       /* CUDA runtime error, or no device */
+  LAPIS_EBADARG = 4,     /* null pointer, bad handle, misaligned device pointer */
+  LAPIS_ENOTINIT = 5,    /* compute call before lapis_initialize */
+  LAPIS_ETOOBIG = 6      /* size beyond a stated limit of the entry point */
+};
+
+/* Last status recorded by this thread's most recent call and its message. */
+int lapis_last_error(void);
+const char *lapis_last_error_message(void);
+
+/* ---- descriptors ---------------------------------------------------------- */
+/* Layout-identical to StridedMemRefType<T,N> (LAPISSupport.hpp:7-14):
+ * {T* basePtr; T* data; int64 offset; int64 sizes[N]; int64 strides[N]}.
+ * The element pointer is data + offset; all memrefs must be C-contiguous. */
+typedef struct { void *basePtr; void *data; int64_t offset; int64_t sizes[1]; int64_t strides[1]; } lapis_memref1;
+typedef struct { void *basePtr; void *data; int64_t offset; int64_t sizes[2]; int64_t strides[2]; } lapis_memref2;
+typedef struct { void *basePtr; void *data; int64_t offset; int64_t sizes[3]; int64_t strides[3]; } lapis_memref3;
+
+/* Sparse storage specifier as the emitter flattens it for a 2-D CSR tensor
+ * (TranslateToKokkosCpp.cpp:4495-4546; benchmarks/spmv/main.cpp:48-51):
+ * {rows, cols, len(pos), len(crd), len(val)} as five contiguous int64. */
+typedef struct { int64_t dims[2]; int64_t mem_sizes[3]; } lapis_csr_spec;
+
+/* ---- layer 1: emitted-module ABI ------------------------------------------ */
+
+/* TranslateToKokkosCpp.cpp:4281-4378.  initialize is idempotent; finalize frees
+ * every result buffer handed out since initialize (LAPISSupport.hpp:93-120). */
+void lapis_initialize(void);
+void lapis_finalize(void);
+
+/* y = y_in + A x on CSR A; returns (aliases) the caller's y buffer.
+ * Replaces the module function `spmv` of benchmarks/spmv/spmv.mlir:1-7 and
+ * examples/spmv_noalloc.py:7-13,29 (wrapper shape: TranslateToKokkosCpp.cpp:2541-2684). */
+void py_spmv_f64_i32(lapis_memref1 **ret0, lapis_memref1 *pos, lapis_memref1 *crd, lapis_memref1 *val,
+                     const lapis_csr_spec *spec, lapis_memref1 *x, lapis_memref1 *y);
+void py_spmv_f64_i64(lapis_memref1 **ret0, lapis_memref1 *pos, lapis_memref1 *crd, lapis_memref1 *val,
+                     const lapis_csr_spec *spec, lapis_memref1 *x, lapis_memref1 *y);
+
+/* C = C_in + A B, CSR A times dense row-major B; returns the caller's C.
+ * Same convention as py_spmv for a `linalg.matmul` with a CSR first operand
+ * (semantics: examples/spmm_dcsr_opdsl.py:40-101, examples/bspmm.py:15-52). */
+void py_spmm_f64_i32(lapis_memref2 **ret0, lapis_memref1 *pos, lapis_memref1 *crd, lapis_memref1 *val,
+                     const lapis_csr_spec *spec, lapis_memref2 *B, lapis_memref2 *C);
+void py_spmm_f64_i64(lapis_memref2 **ret0, lapis_memref1 *pos, lapis_memref1 *crd, lapis_memref1 *val,
+                     const lapis_csr_spec *spec, lapis_memref2 *B, lapis_memref2 *C);
+
+/* C = C_in + A B, fp32, row-major; returns the caller's C.  Replaces `forward`
+ * of examples/gemm_no_alloc.py:8-24,38 / benchmarks/gemm/gemm.mlir:1-15.
+ * A contraction-dimension mismatch (cf.assert, gemm.mlir:10-11) gives LAPIS_EBADSHAPE. */
+void py_matmul_f32(lapis_memref2 **ret0, lapis_memref2 *A, lapis_memref2 *B, lapis_memref2 *C);
+
+/* C[b] = C_in[b] + A[b] B[b], fp32.  Replaces `forward` of
+ * examples/batched_gemm_no_alloc.py:8-31,45 / benchmarks/batched_gemm/batched_gemm.mlir:1-24. */
+void py_batch_matmul_f32(lapis_memref3 **ret0, lapis_memref3 *A, lapis_memref3 *B, lapis_memref3 *C);
+
+/* Jacobi-preconditioned CG, examples/pcg_solve.py:52-101,129: returns x (module-owned,
+ * valid until lapis_finalize), the iteration count and the final relative residual. */
+void py_pcg_f64_i32(lapis_memref1 **ret0, size_t *ret1, double *ret2, lapis_memref1 *pos, lapis_memref1 *crd,
+                    lapis_memref1 *val, const lapis_csr_spec *spec, lapis_memref1 *b, lapis_memref1 *dinv,
+                    double tol, size_t maxiter);
+void py_pcg_f64_i64(lapis_memref1 **ret0, size_t *ret1, double *ret2, lapis_memref1 *pos, lapis_memref1 *crd,
+                    lapis_memref1 *val, const lapis_csr_spec *spec, lapis_memref1 *b, lapis_memref1 *dinv,
+                    double tol, size_t maxiter);
+
+/* ---- layer 2: device-resident entry points -------------------------------- */
+
+/* A CSR matrix resident on the device plus this library's streaming plan for it
+ * (row ranges per thread block, in device scratch owned by the handle).
+ * Counterpart of the DualViews a C++ caller keeps alive across calls
+ * (benchmarks/spmv/main.cpp:42-51).  pos/crd/val stay owned by the caller and
+ * must outlive the handle; val and crd must be 16-byte aligned.  pos[0] may be
+ * non-zero (a row block of a larger matrix addressed in place). */
+typedef struct lapis_b200_csr *lapis_b200_csr_t;
+
+/* idx_bytes: 4 (int32 pos/crd) or 8 (int64).  Synchronises `stream` once. */
+int lapis_b200_csr_create(lapis_b200_csr_t *out, int idx_bytes, int64_t nrows, int64_t ncols,
+                          const void *d_pos, const void *d_crd, const double *d_val, void *stream);
+int lapis_b200_csr_destroy(lapis_b200_csr_t h);
+int64_t lapis_b200_csr_nnz(lapis_b200_csr_t h);
+
+/* y = (accumulate ? y : 0) + A x.  The emitted kernel always accumulates
+ * (loop_mapping_2.mlir.gold:12-37); accumulate = 0 fuses the linalg.fill that
+ * callers put in front of it (examples/pcg_solve.py:13-20). */
+int lapis_b200_spmv_f64(lapis_b200_csr_t h, const double *d_x, double *d_y, int accumulate, void *stream);
+
+/* C = (accumulate ? C : 0) + A B with dense row-major B (ncols x k), C (nrows x k). */
+int lapis_b200_spmm_f64(lapis_b200_csr_t h, int64_t k, const double *d_B, double *d_C, int accumulate,
+                        void *stream);
+
+/* C[b] = C[b] + A[b] B[b], fp32 row-major, batch >= 1 (batch = 1: dense matmul). */
+int lapis_b200_bgemm_f32(int64_t batch, int64_t M, int64_t N, int64_t K, const float *d_A, const float *d_B,
+                         float *d_C, void *stream);
+
+/* Vector kernels of examples/pcg_solve.py:22-48.  dot writes its result to *d_out. */
+int lapis_b200_dot_f64(int64_t n, const double *d_x, const double *d_y, double *d_out, void *stream);
+int lapis_b200_axpby_f64(int64_t n, double a, const double *d_x, double b, const double *d_y, double *d_dst,
+                         void *stream);
+int lapis_b200_mult_f64(int64_t n, const double *d_x, const double *d_y, double *d_dst, void *stream);
+
+/* PCG with all state on the device (examples/pcg_solve.py:52-101).  d_x receives
+ * the solution; *iters and *relres are host outputs.  Blocks until finished. */
+int lapis_b200_pcg_f64(lapis_b200_csr_t h, const double *d_b, const double *d_dinv, double tol, uint64_t maxiter,
+                       double *d_x, uint64_t *iters, double *relres, void *stream);
+
+/* Step-level PCG entry points: the three passes of one iteration, for callers that
+ * put an exchange between them (row-block partitioned solves put a halo copy of p in
+ * front of pass A and an allreduce of the scalar block behind passes A and B).
+ * lapis_b200_pcg_f64 above is exactly these steps in a loop.
+ *
+ * d_work is caller-allocated device memory of lapis_b200_pcg_workspace_bytes(n, n_p)
+ * bytes, 16-byte aligned.  Layout in doubles: [0] p.Ap, [1] r.r, [2] r.z (new),
+ * [3] r.z (carried), [4] initial residual norm, [5] relres, [6] alpha, [7] beta,
+ * [8] done flag and [9] count of completed iterations as int64, then scratch and the vectors
+ * r, z, p, Ap.  n = local rows; n_p >= n = length of the p buffer the matrix's
+ * column indices address; the local part of p starts at p_offset in it.
+ * `derive` != 0 lets the pass also run the scalar recurrence that consumes its
+ * sums (single-device use); with derive == 0 the caller reduces slots [0] or
+ * [1..2] across devices and then calls lapis_b200_pcg_derive.
+ * kind: 1 = after init, 2 = alpha after pass A, 3 = stop test and beta after pass B. */
+int64_t lapis_b200_pcg_workspace_bytes(int64_t n, int64_t n_p);
+/* Offsets (in doubles from d_work) of the vectors r, z, p, Ap. */
+int lapis_b200_pcg_workspace_layout(int64_t n, int64_t n_p, int64_t *offsets4);
+int lapis_b200_pcg_init(void *d_work, int64_t n, int64_t n_p, int64_t p_offset, const double *d_b,
+                        const double *d_dinv, double *d_x, int derive, void *stream);
+int lapis_b200_pcg_derive(void *d_work, int kind, double tol, uint64_t maxiter, void *stream);
+int lapis_b200_pcg_step_spmv(void *d_work, lapis_b200_csr_t h, int64_t n_p, int64_t p_offset, int derive,
+                             void *stream);
+int lapis_b200_pcg_step_update(void *d_work, int64_t n, int64_t n_p, int64_t p_offset, const double *d_dinv,
+                               double *d_x, int derive, double tol, uint64_t maxiter, void *stream);
+int lapis_b200_pcg_step_direction(void *d_work, int64_t n, int64_t n_p, int64_t p_offset, void *stream);
+/* Copies {done, iters, relres} to the host; synchronises `stream`. */
+int lapis_b200_pcg_status(void *d_work, int *done, uint64_t *iters, double *relres, void *stream);
+
+/* nnz-balanced contiguous row partition of a CSR matrix over G devices (host
+ * arrays): bounds[g] = first row whose start offset is >= pos[0] + g*nnz/G,
+ * bounds[G] = nrows.  The reference has no multi-device path; this is the
+ * partition rule of this library. */
+int lapis_b200_partition_rows(int idx_bytes, int64_t nrows, const void *pos, int G, int64_t *bounds);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LAPIS_B200_H */

@@ -1,0 +1,313 @@
+"""Compile-and-call surface of ``lapis.KokkosBackend`` bound to prebuilt sm_100a kernels.
+
+The reference class (python/lapis/KokkosBackend.py:10-121 in the LAPIS project)
+shells out to ``lapis-opt`` and ``lapis-translate``, builds the emitted Kokkos C++
+with CMake and returns a generated ``LAPISModule`` whose methods call the
+``py_<func>`` symbols of the built library
+(mlir/lib/Target/KokkosCpp/TranslateToKokkosCpp.cpp:2757-2977, :4393-4411).
+
+Here nothing is compiled at call time.  ``compile()`` reads the MLIR text, finds
+the public functions, and binds each one that lies on the accelerated path --
+CSR ``linalg.matvec`` (SpMV), CSR x dense ``linalg.matmul`` (SpMM), dense
+``linalg.matmul`` / ``linalg.batch_matmul`` in f32, and the ``@pcg`` solve loop of
+examples/pcg_solve.py -- to the matching entry point of ``liblapis_b200.so``.  A
+module with any other public function is rejected: there is no general MLIR
+lowering and no CPU fallback in this package.
+
+Calling convention of the returned object, as in the generated class: memref
+arguments are numpy arrays (or CPU torch tensors), forced C-contiguous with
+``numpy.require``; a decomposed sparse tensor is the four arguments
+``pos, crd, val, ((rows, cols), (len(pos), len(crd), len(val)))``; results come
+back as numpy arrays / python scalars, several results as a tuple.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import re
+
+import numpy as np
+
+from . import _memref as rt
+from ._lib import check_last, load
+
+_PAR_STRATEGIES = ("none", "dense-outer-loop", "any-storage-outer-loop", "dense-any-loop", "any-storage-any-loop")
+
+
+# ---------------------------------------------------------------------------
+# MLIR text inspection
+# ---------------------------------------------------------------------------
+def _split_top(s: str):
+    out, depth, cur = [], 0, []
+    for ch in s:
+        if ch in "<([":
+            depth += 1
+        elif ch in ">)]":
+            depth -= 1
+        if ch == "," and depth == 0:
+            out.append("".join(cur).strip())
+            cur = []
+        else:
+            cur.append(ch)
+    tail = "".join(cur).strip()
+    if tail:
+        out.append(tail)
+    return out
+
+
+class _Type:
+    def __init__(self, text: str, encodings: dict):
+        self.text = text.strip()
+        self.rank = None
+        self.elem = None
+        self.sparse = None  # encoding dict when the tensor has a sparse encoding
+        m = re.match(r"(?:tensor|memref)<(.*)>$", self.text, re.S)
+        if m:
+            parts = _split_top(m.group(1))
+            dims = parts[0].split("x")
+            self.elem = dims[-1].strip()
+            self.rank = len(dims) - 1
+            if len(parts) > 1 and parts[1].startswith("#"):
+                self.sparse = encodings.get(parts[1].strip())
+                if self.sparse is None:
+                    raise Exception(f"unknown tensor encoding {parts[1]}")
+        else:
+            self.elem = self.text
+            self.rank = 0 if self.text in ("f64", "f32", "index", "i32", "i64") else None
+
+
+def _parse_encodings(text: str) -> dict:
+    enc = {}
+    for m in re.finditer(r"(#\w+)\s*=\s*#sparse_tensor\.encoding<\{(.*?)\}>", text, re.S):
+        body = m.group(2)
+        lvl = re.search(r"map\s*=\s*\([^)]*\)\s*->\s*\(([^)]*)\)", body)
+        levels = re.findall(r"\w+\s*:\s*(\w+)", lvl.group(1)) if lvl else []
+        pw = re.search(r"posWidth\s*=\s*(\d+)", body)
+        cw = re.search(r"crdWidth\s*=\s*(\d+)", body)
+        enc[m.group(1)] = {"levels": levels, "posWidth": int(pw.group(1)) if pw else 0,
+                           "crdWidth": int(cw.group(1)) if cw else 0}
+    return enc
+
+
+def _parse_functions(text: str, encodings: dict):
+    funcs = []
+    for m in re.finditer(r"func\.func\s+(private\s+)?@(\w+)\s*\(", text):
+        # argument list: balance parentheses from m.end()
+        i, depth = m.end(), 1
+        while depth:
+            depth += {"(": 1, ")": -1}.get(text[i], 0)
+            i += 1
+        args_text = text[m.end():i - 1]
+        j = text.index("{", i)
+        res_text = text[i:j].strip()
+        if "attributes" in res_text:
+            res_text = res_text.split("attributes")[0].strip()
+        res_text = res_text[2:].strip() if res_text.startswith("->") else ""
+        if res_text.startswith("("):
+            res_text = res_text[1:res_text.rindex(")")]
+        k, depth = j + 1, 1
+        while depth:
+            depth += {"{": 1, "}": -1}.get(text[k], 0)
+            k += 1
+        args = []
+        for a in _split_top(args_text):
+            args.append(_Type(a.split(":", 1)[1], encodings))
+        results = [_Type(r, encodings) for r in _split_top(res_text)] if res_text else []
+        funcs.append({"name": m.group(2), "private": bool(m.group(1)), "args": args, "results": results,
+                      "body": text[j:k]})
+    return funcs
+
+
+def _is_csr(t: _Type) -> bool:
+    return t.sparse is not None and t.rank == 2 and t.sparse["levels"] == ["dense", "compressed"]
+
+
+def _index_dtype(enc: dict):
+    widths = {enc["posWidth"], enc["crdWidth"]}
+    if widths == {32}:
+        return np.int32, "i32"
+    if widths <= {0, 64} and len(widths) == 1:
+        # width 0 means `index`, emitted as size_t (TranslateToKokkosCpp.cpp:4440-4441): 64-bit here
+        return np.int64, "i64"
+    raise Exception("posWidth and crdWidth must both be 32 or both be 64/index on the accelerated path")
+
+
+def _dense(t: _Type, rank: int, elem: str) -> bool:
+    return t.sparse is None and t.rank == rank and t.elem == elem
+
+
+def _classify(fn: dict, all_funcs: dict):
+    """Returns (kind, index suffix, index dtype) or raises for an off-path function."""
+    a, r, body = fn["args"], fn["results"], fn["body"]
+    if (len(a) == 3 and _is_csr(a[0]) and a[0].elem == "f64" and _dense(a[1], 1, "f64") and _dense(a[2], 1, "f64")
+            and "linalg.matvec" in body and len(r) == 1):
+        dt, sfx = _index_dtype(a[0].sparse)
+        return "spmv", sfx, dt
+    if (len(a) == 3 and _is_csr(a[0]) and a[0].elem == "f64" and _dense(a[1], 2, "f64") and _dense(a[2], 2, "f64")
+            and "linalg.matmul" in body and len(r) == 1):
+        dt, sfx = _index_dtype(a[0].sparse)
+        return "spmm", sfx, dt
+    if (len(a) == 3 and all(_dense(t, 2, "f32") for t in a) and "linalg.matmul" in body and len(r) == 1):
+        return "matmul", "", None
+    if (len(a) == 3 and all(_dense(t, 3, "f32") for t in a) and "linalg.batch_matmul" in body and len(r) == 1):
+        return "batch_matmul", "", None
+    if (len(a) == 5 and _is_csr(a[0]) and a[0].elem == "f64" and _dense(a[1], 1, "f64") and _dense(a[2], 1, "f64")
+            and a[3].elem == "f64" and a[4].elem == "index" and len(r) == 3 and "scf.while" in body
+            and all(f"@{h}" in body for h in ("spmv", "dot", "axpby", "mult"))
+            and all(h in all_funcs for h in ("spmv", "dot", "axpby", "mult"))
+            and "linalg.matvec" in all_funcs["spmv"]["body"] and "linalg.dot" in all_funcs["dot"]["body"]):
+        dt, sfx = _index_dtype(a[0].sparse)
+        return "pcg", sfx, dt
+    raise Exception(
+        f"function @{fn['name']} is not on the accelerated path (CSR matvec/matmul in f64, dense matmul / "
+        "batch_matmul in f32, the Jacobi PCG loop); lapis_b200 has no general MLIR lowering and no fallback")
+
+
+# ---------------------------------------------------------------------------
+# The module object returned by compile()
+# ---------------------------------------------------------------------------
+def _desc(arr):
+    return ctypes.pointer(rt.get_ranked_memref_descriptor(arr))
+
+
+def _ret_slot(rank):
+    return ctypes.pointer(ctypes.pointer(rt.make_nd_memref_descriptor(rank)()))
+
+
+def _flatten_spec(spec):
+    flat = np.zeros(5, dtype=np.int64)
+    for i in range(2):
+        flat[i] = spec[0][i]
+    for i in range(3):
+        flat[2 + i] = spec[1][i]
+    return flat
+
+
+class LAPISModule:
+    """Same lifecycle as the generated class: initialize on construction, finalize on deletion."""
+
+    def __init__(self, bindings: dict):
+        self.libHandle = load()
+        self.libHandle.lapis_initialize()
+        check_last()
+        self._live = True
+        for name, (kind, sfx, idx_dtype) in bindings.items():
+            setattr(self, name, self._bind(kind, sfx, idx_dtype))
+
+    def __del__(self):
+        if getattr(self, "_live", False):
+            self._live = False
+            self.libHandle.lapis_finalize()
+
+    def _bind(self, kind, sfx, idx_dtype):
+        lib = self.libHandle
+
+        def csr_args(pos, crd, val, spec):
+            pos = np.require(pos, dtype=idx_dtype, requirements=["C"])
+            crd = np.require(crd, dtype=idx_dtype, requirements=["C"])
+            val = np.require(val, dtype=np.float64, requirements=["C"])
+            flat = _flatten_spec(spec)
+            return (pos, crd, val, flat), (_desc(pos), _desc(crd), _desc(val), flat.ctypes.data_as(ctypes.c_void_p))
+
+        if kind == "spmv":
+            fn = getattr(lib, f"py_spmv_f64_{sfx}")
+
+            def spmv(pos, crd, val, spec, x, y):
+                keep, cargs = csr_args(pos, crd, val, spec)
+                x = np.require(x, dtype=np.float64, requirements=["C"])
+                y = np.require(y, dtype=np.float64, requirements=["C"])
+                ret0 = _ret_slot(1)
+                fn(ret0, *cargs, _desc(x), _desc(y))
+                check_last()
+                del keep
+                return y  # the function returns its outs argument
+
+            return spmv
+        if kind == "spmm":
+            fn = getattr(lib, f"py_spmm_f64_{sfx}")
+
+            def spmm(pos, crd, val, spec, B, C):
+                keep, cargs = csr_args(pos, crd, val, spec)
+                B = np.require(B, dtype=np.float64, requirements=["C"])
+                C = np.require(C, dtype=np.float64, requirements=["C"])
+                ret0 = _ret_slot(2)
+                fn(ret0, *cargs, _desc(B), _desc(C))
+                check_last()
+                del keep
+                return C
+
+            return spmm
+        if kind in ("matmul", "batch_matmul"):
+            fn = lib.py_matmul_f32 if kind == "matmul" else lib.py_batch_matmul_f32
+            rank = 2 if kind == "matmul" else 3
+
+            def forward(A, B, C):
+                A = np.require(A, dtype=np.float32, requirements=["C"])
+                B = np.require(B, dtype=np.float32, requirements=["C"])
+                C = np.require(C, dtype=np.float32, requirements=["C"])
+                ret0 = _ret_slot(rank)
+                fn(ret0, _desc(A), _desc(B), _desc(C))
+                check_last()
+                return C
+
+            return forward
+        if kind == "pcg":
+            fn = getattr(lib, f"py_pcg_f64_{sfx}")
+
+            def pcg(pos, crd, val, spec, b, dinv, tol, maxiter):
+                keep, cargs = csr_args(pos, crd, val, spec)
+                b = np.require(b, dtype=np.float64, requirements=["C"])
+                dinv = np.require(dinv, dtype=np.float64, requirements=["C"])
+                ret0 = _ret_slot(1)
+                ret1 = ctypes.c_size_t(0)
+                ret2 = ctypes.c_double(0.0)
+                fn(ret0, ctypes.byref(ret1), ctypes.byref(ret2), *cargs, _desc(b), _desc(dinv),
+                   ctypes.c_double(tol), ctypes.c_size_t(maxiter))
+                check_last()
+                del keep
+                # unmanaged alias of module-owned memory, valid until lapis_finalize
+                return (rt.ranked_memref_to_numpy(ret0[0], np.float64), int(ret1.value), float(ret2.value))
+
+            return pcg
+        raise AssertionError(kind)
+
+
+class KokkosBackend:
+    """Main entry point, same constructor as the reference class (python/lapis/KokkosBackend.py:13)."""
+
+    def __init__(self, decompose_tensors=False, parallel_strategy="any-storage-any-loop", dump_mlir=False,
+                 index_instance=0, num_instances=0, ws=os.getcwd()):
+        super().__init__()
+        if parallel_strategy not in _PAR_STRATEGIES:
+            raise Exception(f"unknown parallelization strategy {parallel_strategy!r}")
+        self.dump_mlir = dump_mlir
+        self.ws = ws
+        self.index_instance = index_instance
+        self.num_instances = num_instances
+        self.decompose_tensors = decompose_tensors
+        self.parallel_strategy = parallel_strategy
+        self.package_name = "lapis_package" if index_instance == 0 else "lapis_package_" + str(index_instance)
+
+    def compile(self, module):
+        moduleText = str(module)
+        if self.dump_mlir:
+            print("== High-Level ==")
+            print(moduleText)
+        encodings = _parse_encodings(moduleText)
+        funcs = _parse_functions(moduleText, encodings)
+        by_name = {f["name"]: f for f in funcs}
+        public = [f for f in funcs if not f["private"]]
+        if not public:
+            raise Exception("module has no public function")
+        bindings = {}
+        for fn in public:
+            kind, sfx, dt = _classify(fn, by_name)
+            if sfx and not self.decompose_tensors:
+                raise Exception("sparse tensor arguments need decompose_tensors=True (pos, crd, val, specifier "
+                                "arguments); the opaque sparse-runtime handle form is not supported")
+            bindings[fn["name"]] = (kind, sfx, dt)
+        if self.dump_mlir:
+            print("== Bound ==")
+            for name, (kind, sfx, _) in bindings.items():
+                print(f"@{name} -> {kind}{'_' + sfx if sfx else ''}")
+        return LAPISModule(bindings)

@@ -1,0 +1,410 @@
+// Vector kernels and the PCG solve loop for sm_100a.
+//
+// The emitted PCG (examples/pcg_solve.py:52-101, host `while` loop printed by
+// mlir/lib/Target/KokkosCpp/TranslateToKokkosCpp.cpp:1512-1593) launches ten
+// Kokkos kernels per iteration (fill, SpMV, 4 dots, 3 axpby, mult) and reads four
+// scalars back to the host.  Here one iteration is three streaming passes whose
+// scalars never leave the device:
+//
+//   pass A  Ap = A p, fused with the partial sums of p.Ap          (spmv.cu)
+//   pass B  x += alpha p ; r -= alpha Ap ; z = r*dinv ; partial r.r and r.z
+//   pass C  p = z + beta p
+//
+// r.z at the top of an iteration equals the r.z' computed at the end of the
+// previous one (same operands), so it is carried instead of recomputed.
+// Between the passes a single-block kernel adds the per-block partials in a fixed
+// order (results are run-to-run identical) and derives alpha / relres / beta and
+// the stop flag.  Every kernel returns at once when the stop flag is set, so the
+// host can enqueue iterations ahead and only look at the flag now and then.
+//
+// Arithmetic follows the emitted element-wise bodies: axpby is (x*a) + (y*b) with
+// separate roundings (examples/pcg_solve.py:30-39), mult is x*y (:41-48).
+#include <cmath>
+
+#include "common.h"
+
+namespace lapis_b200 {
+
+int spmv_launch(const lapis_b200_csr *h, const double *x, double *y, int accumulate, const double *dotvec,
+                double *blk_partial, const int *skip_flag, cudaStream_t st);
+
+constexpr int VEC_THREADS = 256;
+constexpr int SUM_THREADS = 1024;
+
+// Device scalar block at the head of a PCG workspace (doubles, then flags).
+enum { SC_PAP = 0, SC_RR = 1, SC_RZNEW = 2, SC_RZ = 3, SC_INITRES = 4, SC_RELRES = 5, SC_ALPHA = 6, SC_BETA = 7, SC_COUNT = 8 };
+enum { FL_DONE = 0, FL_ITERS = 1, FL_COUNT = 2 };  // int64 each
+enum { DERIVE_NONE = 0, DERIVE_INIT = 1, DERIVE_ALPHA = 2, DERIVE_DECIDE = 3 };
+
+__device__ __forceinline__ double block_sum_vec(double v, double *s_red) {
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) v = __dadd_rn(v, __shfl_xor_sync(0xffffffffu, v, off));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  __syncthreads();
+  if (lane == 0) s_red[warp] = v;
+  __syncthreads();
+  double t = 0.0;
+  if (warp == 0) {
+    t = lane < (int)(blockDim.x >> 5) ? s_red[lane] : 0.0;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) t = __dadd_rn(t, __shfl_xor_sync(0xffffffffu, t, off));
+  }
+  return t;  // valid in thread 0
+}
+
+// Scalar recurrences of one PCG iteration (examples/pcg_solve.py:70-71, 78, 84-90, 96).
+// The iteration counter lives on the device (fl[FL_ITERS]) so that one iteration can be
+// captured in a CUDA graph and replayed.
+__device__ void pcg_derive(int kind, double *sc, long long *fl, double tol, unsigned long long maxiter) {
+  if (kind == DERIVE_INIT) {
+    sc[SC_INITRES] = sqrt(sc[SC_RR]);
+    sc[SC_RZ] = sc[SC_RZNEW];
+    fl[FL_DONE] = 0;
+    fl[FL_ITERS] = 0;
+  } else if (kind == DERIVE_ALPHA) {
+    sc[SC_ALPHA] = sc[SC_RZ] / sc[SC_PAP];
+  } else if (kind == DERIVE_DECIDE) {
+    const double relres = sqrt(sc[SC_RR]) / sc[SC_INITRES];
+    sc[SC_RELRES] = relres;
+    const unsigned long long iter = (unsigned long long)fl[FL_ITERS] + 1;  // i starts at 1
+    fl[FL_ITERS] = (long long)iter;
+    const bool not_converged = relres > tol;  // ordered compare: NaN stops the loop
+    const bool below_maxiter = iter != maxiter;
+    if (!(not_converged && below_maxiter)) {
+      fl[FL_DONE] = 1;
+    } else {
+      sc[SC_BETA] = sc[SC_RZNEW] / sc[SC_RZ];
+      sc[SC_RZ] = sc[SC_RZNEW];
+    }
+  }
+}
+
+// out[c] = sum_b partials[c*nb + b] for c < count (count <= 2), fixed order; then
+// optionally the scalar step that consumes the sums.
+__global__ void __launch_bounds__(SUM_THREADS)
+sum_partials_kernel(const double *__restrict__ partials, int64_t nb, int count, double *out0, double *out1,
+                    int derive, double *sc, long long *fl, double tol, unsigned long long maxiter,
+                    const long long *skip) {
+  __shared__ double s_red[SUM_THREADS / 32];
+  if (skip != nullptr && skip[FL_DONE] != 0) return;
+  for (int c = 0; c < count; ++c) {
+    double acc = 0.0;
+    const double *p = partials + (int64_t)c * nb;
+    for (int64_t i = threadIdx.x; i < nb; i += SUM_THREADS) acc = __dadd_rn(acc, p[i]);
+    const double t = block_sum_vec(acc, s_red);
+    if (threadIdx.x == 0) *(c == 0 ? out0 : out1) = t;
+  }
+  if (derive != DERIVE_NONE && threadIdx.x == 0) pcg_derive(derive, sc, fl, tol, maxiter);
+}
+
+__global__ void pcg_derive_kernel(int kind, double *sc, long long *fl, double tol, unsigned long long maxiter) {
+  if (kind != DERIVE_INIT && fl[FL_DONE] != 0) return;
+  pcg_derive(kind, sc, fl, tol, maxiter);
+}
+
+// ---- plain vector kernels (examples/pcg_solve.py:22-48) ------------------------
+__global__ void __launch_bounds__(VEC_THREADS)
+dot_partial_kernel(int64_t n, const double *__restrict__ x, const double *__restrict__ y,
+                   double *__restrict__ partials) {
+  __shared__ double s_red[VEC_THREADS / 32];
+  double acc = 0.0;
+  for (int64_t i = (int64_t)blockIdx.x * VEC_THREADS + threadIdx.x; i < n; i += (int64_t)gridDim.x * VEC_THREADS)
+    acc = __dadd_rn(acc, __dmul_rn(x[i], y[i]));
+  const double t = block_sum_vec(acc, s_red);
+  if (threadIdx.x == 0) partials[blockIdx.x] = t;
+}
+
+__global__ void __launch_bounds__(VEC_THREADS)
+axpby_kernel(int64_t n, double a, const double *__restrict__ x, double b, const double *__restrict__ y,
+             double *__restrict__ dst) {
+  for (int64_t i = (int64_t)blockIdx.x * VEC_THREADS + threadIdx.x; i < n; i += (int64_t)gridDim.x * VEC_THREADS)
+    dst[i] = __dadd_rn(__dmul_rn(x[i], a), __dmul_rn(y[i], b));
+}
+
+__global__ void __launch_bounds__(VEC_THREADS)
+mult_kernel(int64_t n, const double *__restrict__ x, const double *__restrict__ y, double *__restrict__ dst) {
+  for (int64_t i = (int64_t)blockIdx.x * VEC_THREADS + threadIdx.x; i < n; i += (int64_t)gridDim.x * VEC_THREADS)
+    dst[i] = __dmul_rn(x[i], y[i]);
+}
+
+// ---- PCG passes --------------------------------------------------------------------
+// r = b; z = r*dinv; p = z; x = 0; partials of r.r and r.z  (examples/pcg_solve.py:65-70)
+__global__ void __launch_bounds__(VEC_THREADS)
+pcg_init_kernel(int64_t n, const double *__restrict__ b, const double *__restrict__ dinv, double *__restrict__ r,
+                double *__restrict__ z, double *__restrict__ p, double *__restrict__ x,
+                double *__restrict__ partials) {
+  __shared__ double s_red[VEC_THREADS / 32];
+  double rr = 0.0, rz = 0.0;
+  for (int64_t i = (int64_t)blockIdx.x * VEC_THREADS + threadIdx.x; i < n; i += (int64_t)gridDim.x * VEC_THREADS) {
+    const double ri = b[i];
+    const double zi = __dmul_rn(ri, dinv[i]);
+    r[i] = ri;
+    z[i] = zi;
+    p[i] = zi;
+    x[i] = 0.0;
+    rr = __dadd_rn(rr, __dmul_rn(ri, ri));
+    rz = __dadd_rn(rz, __dmul_rn(ri, zi));
+  }
+  const double t0 = block_sum_vec(rr, s_red);
+  const double t1 = block_sum_vec(rz, s_red);
+  if (threadIdx.x == 0) {
+    partials[blockIdx.x] = t0;
+    partials[gridDim.x + blockIdx.x] = t1;
+  }
+}
+
+// x = x*1 + p*alpha ; r = r*1 + Ap*(-alpha) ; z = r*dinv ; partials of r.r and r.z
+// (examples/pcg_solve.py:79-84, 94-95)
+__global__ void __launch_bounds__(VEC_THREADS)
+pcg_update_kernel(int64_t n, const double *__restrict__ sc, const long long *__restrict__ fl,
+                  const double *__restrict__ p, const double *__restrict__ Ap, const double *__restrict__ dinv,
+                  double *__restrict__ x, double *__restrict__ r, double *__restrict__ z,
+                  double *__restrict__ partials) {
+  __shared__ double s_red[VEC_THREADS / 32];
+  if (fl[FL_DONE] != 0) return;
+  const double alpha = sc[SC_ALPHA];
+  const double malpha = -alpha;
+  double rr = 0.0, rz = 0.0;
+  for (int64_t i = (int64_t)blockIdx.x * VEC_THREADS + threadIdx.x; i < n; i += (int64_t)gridDim.x * VEC_THREADS) {
+    const double xi = __dadd_rn(__dmul_rn(x[i], 1.0), __dmul_rn(p[i], alpha));
+    const double ri = __dadd_rn(__dmul_rn(r[i], 1.0), __dmul_rn(Ap[i], malpha));
+    const double zi = __dmul_rn(ri, dinv[i]);
+    x[i] = xi;
+    r[i] = ri;
+    z[i] = zi;
+    rr = __dadd_rn(rr, __dmul_rn(ri, ri));
+    rz = __dadd_rn(rz, __dmul_rn(ri, zi));
+  }
+  const double t0 = block_sum_vec(rr, s_red);
+  const double t1 = block_sum_vec(rz, s_red);
+  if (threadIdx.x == 0) {
+    partials[blockIdx.x] = t0;
+    partials[gridDim.x + blockIdx.x] = t1;
+  }
+}
+
+// p = z*1 + p*beta  (examples/pcg_solve.py:97)
+__global__ void __launch_bounds__(VEC_THREADS)
+pcg_direction_kernel(int64_t n, const double *__restrict__ sc, const long long *__restrict__ fl,
+                     const double *__restrict__ z, double *__restrict__ p) {
+  if (fl[FL_DONE] != 0) return;
+  const double beta = sc[SC_BETA];
+  for (int64_t i = (int64_t)blockIdx.x * VEC_THREADS + threadIdx.x; i < n; i += (int64_t)gridDim.x * VEC_THREADS)
+    p[i] = __dadd_rn(__dmul_rn(z[i], 1.0), __dmul_rn(p[i], beta));
+}
+
+static inline unsigned vec_grid(int64_t n) {
+  const int64_t want = (n + VEC_THREADS - 1) / VEC_THREADS;
+  const int64_t cap = (int64_t)sm_count() * 8;
+  int64_t g = want < cap ? want : cap;
+  return (unsigned)(g < 1 ? 1 : g);
+}
+
+// Workspace layout (doubles): [scalars 8][flags 2 (as int64)][pad to 16][partials 2*G][r n][z n][p n_p][Ap n]
+// where G = 8 * SM count and n_p >= n is the length of the (halo-extended) p buffer.
+struct PcgWork {
+  double *sc;
+  long long *fl;
+  double *partials;
+  double *r, *z, *p, *Ap;
+  unsigned grid;
+};
+
+static inline int64_t pcg_partials_len() { return 2 * (int64_t)sm_count() * 8; }
+
+static PcgWork carve(void *d_work, int64_t n, int64_t n_p) {
+  PcgWork w;
+  double *base = static_cast<double *>(d_work);
+  w.sc = base;
+  w.fl = reinterpret_cast<long long *>(base + SC_COUNT);
+  w.partials = base + 16;
+  double *vecs = w.partials + pcg_partials_len();
+  w.r = vecs;
+  w.z = vecs + n;
+  w.p = vecs + 2 * n;
+  w.Ap = vecs + 2 * n + n_p;
+  w.grid = vec_grid(n);
+  return w;
+}
+
+}  // namespace lapis_b200
+
+using namespace lapis_b200;
+
+extern "C" int lapis_b200_dot_f64(int64_t n, const double *d_x, const double *d_y, double *d_out, void *stream) {
+  clear_error();
+  if (n < 0) return fail(LAPIS_EBADSHAPE, "dot: negative length");
+  if (d_out == nullptr || (n > 0 && (d_x == nullptr || d_y == nullptr))) return fail(LAPIS_EBADARG, "dot: null operand");
+  cudaStream_t st = as_stream(stream);
+  const unsigned g = vec_grid(n);
+  double *partials = nullptr;
+  LAPIS_CUDA_TRY(cudaMallocAsync(&partials, g * sizeof(double), st));
+  dot_partial_kernel<<<g, VEC_THREADS, 0, st>>>(n, d_x, d_y, partials);
+  sum_partials_kernel<<<1, SUM_THREADS, 0, st>>>(partials, g, 1, d_out, nullptr, DERIVE_NONE, nullptr, nullptr, 0.0, 0,
+                                                 nullptr);
+  LAPIS_CUDA_TRY(cudaGetLastError());
+  LAPIS_CUDA_TRY(cudaFreeAsync(partials, st));
+  return LAPIS_OK;
+}
+
+extern "C" int lapis_b200_axpby_f64(int64_t n, double a, const double *d_x, double b, const double *d_y,
+                                    double *d_dst, void *stream) {
+  clear_error();
+  if (n < 0) return fail(LAPIS_EBADSHAPE, "axpby: negative length");
+  if (n == 0) return LAPIS_OK;
+  if (d_x == nullptr || d_y == nullptr || d_dst == nullptr) return fail(LAPIS_EBADARG, "axpby: null operand");
+  axpby_kernel<<<vec_grid(n), VEC_THREADS, 0, as_stream(stream)>>>(n, a, d_x, b, d_y, d_dst);
+  LAPIS_CUDA_TRY(cudaGetLastError());
+  return LAPIS_OK;
+}
+
+extern "C" int lapis_b200_mult_f64(int64_t n, const double *d_x, const double *d_y, double *d_dst, void *stream) {
+  clear_error();
+  if (n < 0) return fail(LAPIS_EBADSHAPE, "mult: negative length");
+  if (n == 0) return LAPIS_OK;
+  if (d_x == nullptr || d_y == nullptr || d_dst == nullptr) return fail(LAPIS_EBADARG, "mult: null operand");
+  mult_kernel<<<vec_grid(n), VEC_THREADS, 0, as_stream(stream)>>>(n, d_x, d_y, d_dst);
+  LAPIS_CUDA_TRY(cudaGetLastError());
+  return LAPIS_OK;
+}
+
+// ---- step-level PCG entry points (shared by the single-device driver below and by
+// ---- multi-device callers that put a halo exchange / allreduce between the steps) ---
+extern "C" int64_t lapis_b200_pcg_workspace_bytes(int64_t n, int64_t n_p) {
+  if (n < 0 || n_p < n) return -1;
+  return (int64_t)sizeof(double) * (16 + pcg_partials_len() + 3 * n + n_p);
+}
+
+extern "C" int lapis_b200_pcg_workspace_layout(int64_t n, int64_t n_p, int64_t *offsets4) {
+  clear_error();
+  if (n < 0 || n_p < n || offsets4 == nullptr) return fail(LAPIS_EBADARG, "pcg_workspace_layout: bad arguments");
+  const int64_t vecs = 16 + pcg_partials_len();
+  offsets4[0] = vecs;               // r
+  offsets4[1] = vecs + n;           // z
+  offsets4[2] = vecs + 2 * n;       // p (length n_p)
+  offsets4[3] = vecs + 2 * n + n_p; // Ap
+  return LAPIS_OK;
+}
+
+extern "C" int lapis_b200_pcg_init(void *d_work, int64_t n, int64_t n_p, int64_t p_offset, const double *d_b,
+                                   const double *d_dinv, double *d_x, int derive, void *stream) {
+  clear_error();
+  if (d_work == nullptr || n < 0 || n_p < n || p_offset < 0 || p_offset + n > n_p)
+    return fail(LAPIS_EBADARG, "pcg_init: bad workspace arguments");
+  PcgWork w = carve(d_work, n, n_p);
+  cudaStream_t st = as_stream(stream);
+  LAPIS_CUDA_TRY(cudaMemsetAsync(w.sc, 0, 16 * sizeof(double), st));
+  if (n_p > n) LAPIS_CUDA_TRY(cudaMemsetAsync(w.p, 0, (size_t)n_p * sizeof(double), st));
+  LAPIS_CUDA_TRY(cudaMemsetAsync(w.partials, 0, (size_t)pcg_partials_len() * sizeof(double), st));
+  pcg_init_kernel<<<w.grid, VEC_THREADS, 0, st>>>(n, d_b, d_dinv, w.r, w.z, w.p + p_offset, d_x, w.partials);
+  sum_partials_kernel<<<1, SUM_THREADS, 0, st>>>(w.partials, w.grid, 2, w.sc + SC_RR, w.sc + SC_RZNEW,
+                                                 derive ? DERIVE_INIT : DERIVE_NONE, w.sc, w.fl, 0.0, 0, nullptr);
+  LAPIS_CUDA_TRY(cudaGetLastError());
+  return LAPIS_OK;
+}
+
+extern "C" int lapis_b200_pcg_derive(void *d_work, int kind, double tol, uint64_t maxiter, void *stream) {
+  clear_error();
+  if (d_work == nullptr || kind < DERIVE_INIT || kind > DERIVE_DECIDE) return fail(LAPIS_EBADARG, "pcg_derive: bad arguments");
+  double *base = static_cast<double *>(d_work);
+  pcg_derive_kernel<<<1, 1, 0, as_stream(stream)>>>(kind, base, reinterpret_cast<long long *>(base + SC_COUNT), tol, maxiter);
+  LAPIS_CUDA_TRY(cudaGetLastError());
+  return LAPIS_OK;
+}
+
+// Pass A: Ap = A p_ext (p_ext = the workspace's p buffer of length n_p, columns of A
+// index into it), partial sums of p.Ap reduced into the scalar block.
+extern "C" int lapis_b200_pcg_step_spmv(void *d_work, lapis_b200_csr_t h, int64_t n_p, int64_t p_offset, int derive,
+                                        void *stream) {
+  clear_error();
+  if (d_work == nullptr || h == nullptr) return fail(LAPIS_EBADARG, "pcg_step_spmv: null argument");
+  const int64_t n = h->nrows;
+  PcgWork w = carve(d_work, n, n_p);
+  cudaStream_t st = as_stream(stream);
+  const int *skip = reinterpret_cast<const int *>(w.fl);  // low word of the little-endian int64 flag
+  LAPIS_TRY(spmv_launch(h, w.p, w.Ap, 0, w.p + p_offset, h->blk_partial, skip, st));
+  sum_partials_kernel<<<1, SUM_THREADS, 0, st>>>(h->blk_partial, h->nblk, 1, w.sc + SC_PAP, nullptr,
+                                                 derive ? DERIVE_ALPHA : DERIVE_NONE, w.sc, w.fl, 0.0, 0, w.fl);
+  LAPIS_CUDA_TRY(cudaGetLastError());
+  return LAPIS_OK;
+}
+
+// Pass B: x, r, z updates and the partial sums of r.r and r.z.
+extern "C" int lapis_b200_pcg_step_update(void *d_work, int64_t n, int64_t n_p, int64_t p_offset, const double *d_dinv,
+                                          double *d_x, int derive, double tol, uint64_t maxiter, void *stream) {
+  clear_error();
+  if (d_work == nullptr) return fail(LAPIS_EBADARG, "pcg_step_update: null workspace");
+  PcgWork w = carve(d_work, n, n_p);
+  cudaStream_t st = as_stream(stream);
+  pcg_update_kernel<<<w.grid, VEC_THREADS, 0, st>>>(n, w.sc, w.fl, w.p + p_offset, w.Ap, d_dinv, d_x, w.r, w.z,
+                                                    w.partials);
+  sum_partials_kernel<<<1, SUM_THREADS, 0, st>>>(w.partials, w.grid, 2, w.sc + SC_RR, w.sc + SC_RZNEW,
+                                                 derive ? DERIVE_DECIDE : DERIVE_NONE, w.sc, w.fl, tol, maxiter, w.fl);
+  LAPIS_CUDA_TRY(cudaGetLastError());
+  return LAPIS_OK;
+}
+
+// Pass C: p = z + beta p.
+extern "C" int lapis_b200_pcg_step_direction(void *d_work, int64_t n, int64_t n_p, int64_t p_offset, void *stream) {
+  clear_error();
+  if (d_work == nullptr) return fail(LAPIS_EBADARG, "pcg_step_direction: null workspace");
+  PcgWork w = carve(d_work, n, n_p);
+  pcg_direction_kernel<<<w.grid, VEC_THREADS, 0, as_stream(stream)>>>(n, w.sc, w.fl, w.z, w.p + p_offset);
+  LAPIS_CUDA_TRY(cudaGetLastError());
+  return LAPIS_OK;
+}
+
+// Reads {done, iters} and relres back (synchronises the stream).
+extern "C" int lapis_b200_pcg_status(void *d_work, int *done, uint64_t *iters, double *relres, void *stream) {
+  clear_error();
+  if (d_work == nullptr) return fail(LAPIS_EBADARG, "pcg_status: null workspace");
+  double host[16];
+  cudaStream_t st = as_stream(stream);
+  LAPIS_CUDA_TRY(cudaMemcpyAsync(host, d_work, sizeof(host), cudaMemcpyDeviceToHost, st));
+  LAPIS_CUDA_TRY(cudaStreamSynchronize(st));
+  const long long *fl = reinterpret_cast<const long long *>(host + SC_COUNT);
+  if (done) *done = (int)fl[FL_DONE];
+  if (iters) *iters = (uint64_t)fl[FL_ITERS];
+  if (relres) *relres = host[SC_RELRES];
+  return LAPIS_OK;
+}
+
+extern "C" int lapis_b200_pcg_f64(lapis_b200_csr_t h, const double *d_b, const double *d_dinv, double tol,
+                                  uint64_t maxiter, double *d_x, uint64_t *iters, double *relres, void *stream) {
+  clear_error();
+  if (h == nullptr) return fail(LAPIS_EBADARG, "pcg: null matrix handle");
+  if (h->nrows != h->ncols) return fail(LAPIS_EBADSHAPE, "pcg: matrix is not square");
+  const int64_t n = h->nrows;
+  if (n > 0 && (d_b == nullptr || d_dinv == nullptr || d_x == nullptr)) return fail(LAPIS_EBADARG, "pcg: null operand");
+  cudaStream_t st = as_stream(stream);
+  if (n == 0) {  // 0/0 residual: the ordered compare fails and the loop stops after one pass
+    if (iters) *iters = 1;
+    if (relres) *relres = NAN;
+    return LAPIS_OK;
+  }
+  void *work = nullptr;
+  LAPIS_CUDA_TRY(cudaMalloc(&work, (size_t)lapis_b200_pcg_workspace_bytes(n, n)));
+  int status = lapis_b200_pcg_init(work, n, n, 0, d_b, d_dinv, d_x, 1, st);
+  int done = 0;
+  uint64_t it = 0;
+  double rel = 0.0;
+  // The emitted loop stops when relres <= tol or i == maxiter with i starting at 1
+  // (examples/pcg_solve.py:72,86-90); maxiter == 0 therefore never stops on the count.
+  // The same holds here, up to a bound of 2^31 iterations.
+  const uint64_t limit = maxiter == 0 ? (1ull << 31) : maxiter;
+  const uint64_t check_every = 16;
+  for (uint64_t i = 1; status == LAPIS_OK && !done && i <= limit; ++i) {
+    status = lapis_b200_pcg_step_spmv(work, h, n, 0, 1, st);
+    if (status == LAPIS_OK)
+      status = lapis_b200_pcg_step_update(work, n, n, 0, d_dinv, d_x, 1, tol, maxiter, st);
+    if (status == LAPIS_OK) status = lapis_b200_pcg_step_direction(work, n, n, 0, st);
+    if (status == LAPIS_OK && (i % check_every == 0 || i == limit))
+      status = lapis_b200_pcg_status(work, &done, &it, &rel, st);
+  }
+  if (status == LAPIS_OK && !done) status = lapis_b200_pcg_status(work, &done, &it, &rel, st);
+  cudaFree(work);
+  if (status != LAPIS_OK) return status;
+  if (iters) *iters = it;
+  if (relres) *relres = rel;
+  return LAPIS_OK;
+}

@@ -1,0 +1,138 @@
+"""Device-resident layer: the ``lapis_b200_*`` entry points over torch CUDA tensors.
+
+torch is used for device memory and streams only; every operation below is one
+call into ``liblapis_b200.so`` on torch's current stream.  This is the layer a
+caller uses who keeps operands on the GPU between calls, as the C++ drivers of
+the reference do with ``LAPIS::DualView`` (benchmarks/spmv/main.cpp:42-62).
+"""
+from __future__ import annotations
+
+import ctypes
+
+import numpy as np
+import torch
+
+from ._lib import c_dbl, c_int, c_u64, c_vp, check, load
+
+
+def _stream():
+    return c_vp(torch.cuda.current_stream().cuda_stream)
+
+
+def _ptr(t):
+    return c_vp(0 if t is None or t.numel() == 0 else t.data_ptr())
+
+
+def _f64(t, name):
+    if not (t.is_cuda and t.dtype == torch.float64 and t.is_contiguous()):
+        raise TypeError(f"{name} must be a contiguous float64 CUDA tensor")
+    return t
+
+
+class CsrMatrix:
+    """CSR matrix on the device with its streaming plan (``lapis_b200_csr_t``).
+
+    ``pos``/``crd`` are int32 or int64 CUDA tensors, ``val`` float64; they are
+    borrowed (kept referenced here) and must not be modified while in use.
+    ``pos`` may be a slice of a larger offsets array (non-zero ``pos[0]``).
+    """
+
+    def __init__(self, pos: torch.Tensor, crd: torch.Tensor, val: torch.Tensor, shape):
+        if pos.dtype != crd.dtype or pos.dtype not in (torch.int32, torch.int64):
+            raise TypeError("pos/crd must both be int32 or both int64")
+        for t in (pos, crd, val):
+            if not (t.is_cuda and t.is_contiguous()):
+                raise TypeError("pos/crd/val must be contiguous CUDA tensors")
+        if val.dtype != torch.float64:
+            raise TypeError("val must be float64")
+        self.pos, self.crd, self.val = pos, crd, val
+        self.nrows, self.ncols = int(shape[0]), int(shape[1])
+        if pos.numel() != self.nrows + 1:
+            raise ValueError("pos must have rows+1 entries")
+        self._lib = load()
+        h = c_vp()
+        with torch.cuda.device(pos.device):
+            check(self._lib.lapis_b200_csr_create(ctypes.byref(h), c_int(pos.element_size()), self.nrows, self.ncols,
+                                                  _ptr(pos), _ptr(crd), _ptr(val), _stream()))
+        self._h = h
+        self.nnz = int(self._lib.lapis_b200_csr_nnz(h))
+
+    @classmethod
+    def from_host(cls, pos, crd, val, shape, device="cuda"):
+        return cls(torch.as_tensor(np.ascontiguousarray(pos)).to(device), torch.as_tensor(np.ascontiguousarray(crd)).to(device),
+                   torch.as_tensor(np.ascontiguousarray(val, dtype=np.float64)).to(device), shape)
+
+    @property
+    def handle(self):
+        return self._h
+
+    def __del__(self):
+        h = getattr(self, "_h", None)
+        if h:
+            self._lib.lapis_b200_csr_destroy(h)
+            self._h = None
+
+    def spmv(self, x: torch.Tensor, y: torch.Tensor, accumulate: bool = True) -> torch.Tensor:
+        """y = (y if accumulate else 0) + A x, in place."""
+        _f64(x, "x"), _f64(y, "y")
+        if x.numel() != self.ncols or y.numel() != self.nrows:
+            raise ValueError("spmv: x/y length mismatch")
+        check(self._lib.lapis_b200_spmv_f64(self._h, _ptr(x), _ptr(y), c_int(1 if accumulate else 0), _stream()))
+        return y
+
+    def spmm(self, B: torch.Tensor, C: torch.Tensor, accumulate: bool = True) -> torch.Tensor:
+        """C = (C if accumulate else 0) + A B, in place; B [ncols, k], C [nrows, k] row-major."""
+        _f64(B, "B"), _f64(C, "C")
+        if B.shape[0] != self.ncols or C.shape[0] != self.nrows or B.shape[1] != C.shape[1]:
+            raise ValueError("spmm: B/C shape mismatch")
+        check(self._lib.lapis_b200_spmm_f64(self._h, int(B.shape[1]), _ptr(B), _ptr(C), c_int(1 if accumulate else 0),
+                                            _stream()))
+        return C
+
+    def pcg(self, b: torch.Tensor, dinv: torch.Tensor, tol: float, maxiter: int):
+        """Returns (x, iters, relres); blocks until the solve has finished."""
+        _f64(b, "b"), _f64(dinv, "dinv")
+        x = torch.empty_like(b)
+        iters, relres = c_u64(0), c_dbl(0.0)
+        check(self._lib.lapis_b200_pcg_f64(self._h, _ptr(b), _ptr(dinv), c_dbl(tol), c_u64(maxiter), _ptr(x),
+                                           ctypes.byref(iters), ctypes.byref(relres), _stream()))
+        return x, int(iters.value), float(relres.value)
+
+
+def bgemm(A: torch.Tensor, B: torch.Tensor, C: torch.Tensor) -> torch.Tensor:
+    """C = C + A @ B in place; fp32, [M,K]x[K,N] or batched [b,M,K]x[b,K,N]."""
+    for t in (A, B, C):
+        if not (t.is_cuda and t.dtype == torch.float32 and t.is_contiguous()):
+            raise TypeError("bgemm operands must be contiguous float32 CUDA tensors")
+    if A.dim() == 2:
+        batch, (M, K), (K2, N) = 1, A.shape, B.shape
+    else:
+        batch, M, K = A.shape
+        b2, K2, N = B.shape
+        if b2 != batch:
+            raise ValueError("mismatching contracting dimension")
+    if K != K2:
+        raise ValueError("mismatching contracting dimension")
+    if tuple(C.shape) != (tuple(A.shape[:-1]) + (N,)):
+        raise ValueError("bgemm: output shape mismatch")
+    check(load().lapis_b200_bgemm_f32(batch, M, N, K, _ptr(A), _ptr(B), _ptr(C), _stream()))
+    return C
+
+
+def dot(x: torch.Tensor, y: torch.Tensor) -> torch.Tensor:
+    _f64(x, "x"), _f64(y, "y")
+    out = torch.empty(1, dtype=torch.float64, device=x.device)
+    check(load().lapis_b200_dot_f64(x.numel(), _ptr(x), _ptr(y), _ptr(out), _stream()))
+    return out
+
+
+def axpby(a: float, x: torch.Tensor, b: float, y: torch.Tensor, dst: torch.Tensor) -> torch.Tensor:
+    _f64(x, "x"), _f64(y, "y"), _f64(dst, "dst")
+    check(load().lapis_b200_axpby_f64(x.numel(), c_dbl(a), _ptr(x), c_dbl(b), _ptr(y), _ptr(dst), _stream()))
+    return dst
+
+
+def mult(x: torch.Tensor, y: torch.Tensor, dst: torch.Tensor) -> torch.Tensor:
+    _f64(x, "x"), _f64(y, "y"), _f64(dst, "dst")
+    check(load().lapis_b200_mult_f64(x.numel(), _ptr(x), _ptr(y), _ptr(dst), _stream()))
+    return dst

@@ -1,0 +1,214 @@
+"""Row-partitioned SpMV / SpMM / PCG over the GPUs of one node, one process per GPU.
+
+``torch.distributed`` carries the plumbing (NCCL over NVLink on GPUs; gloo in the
+CPU tests of the host logic).  The data path has an exchange only where the
+operator needs one:
+
+* SpMV / SpMM: rank g owns an nnz-balanced block of rows; x (or B) is replicated, as
+  a caller that holds the same right-hand side on every GPU has it; no collective.
+* PCG: every vector is split like the rows.  Before the SpMV pass each rank receives
+  the pieces of p that its columns reach outside its own block (for a banded matrix
+  one grid row from each neighbour) with point-to-point sends, and the two scalar
+  groups of an iteration (p.Ap; r.r and r.z) are summed with an allreduce of the
+  solver's scalar block.  One iteration is captured in a CUDA graph and replayed, so
+  the host is not in the loop between checks of the stop flag.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+from . import partition as part
+
+
+class HaloExchanger:
+    """Moves the non-owned pieces of a window [c0, c1) of a row-distributed vector.
+
+    ``ext`` passed to :meth:`exchange` is this rank's window buffer: element i holds
+    global entry c0 + i; the owned entries [r0, r1) must be current on entry, the rest is
+    overwritten with the owners' values.
+    """
+
+    def __init__(self, bounds, windows, rank: int, group=None):
+        self.rank = rank
+        self.group = group
+        self.bounds = np.asarray(bounds, dtype=np.int64)
+        self.c0, self.c1 = windows[rank]
+        self.r0, self.r1 = int(self.bounds[rank]), int(self.bounds[rank + 1])
+        recv, send = part.exchange_plan(self.bounds, windows)
+        self.recv, self.send = recv[rank], send[rank]
+
+    @property
+    def own_offset(self) -> int:
+        return self.r0 - self.c0
+
+    @property
+    def window_len(self) -> int:
+        return self.c1 - self.c0
+
+    def exchange(self, ext: torch.Tensor) -> None:
+        if not self.recv and not self.send:
+            return
+        ops = []
+        # Every rank lists its transfers by ascending peer, sends and receives interleaved the
+        # same way on both sides, so that batched point-to-point calls pair up.
+        peers = sorted({p for p, _, _ in self.recv} | {p for p, _, _ in self.send})
+        for peer in peers:
+            for (p, s, e) in self.send:
+                if p == peer:
+                    ops.append(dist.P2POp(dist.isend, ext[s - self.c0:e - self.c0], self._global_rank(peer), self.group))
+            for (p, s, e) in self.recv:
+                if p == peer:
+                    ops.append(dist.P2POp(dist.irecv, ext[s - self.c0:e - self.c0], self._global_rank(peer), self.group))
+        for req in dist.batch_isend_irecv(ops):
+            req.wait()
+
+    def _global_rank(self, group_rank: int) -> int:
+        return group_rank if self.group is None else dist.get_global_rank(self.group, group_rank)
+
+
+def local_block(pos, crd, val, rank: int, world: int):
+    """This rank's row block of a host CSR: (bounds, local pos, crd, val)."""
+    bounds = part.partition_rows(pos, world)
+    lpos, lcrd, lval = part.row_block(pos, crd, val, int(bounds[rank]), int(bounds[rank + 1]))
+    return bounds, lpos, lcrd, lval
+
+
+def all_windows(pos, crd, bounds):
+    """Column window of every rank (each rank can compute all of them from the host CSR)."""
+    wins = []
+    for g in range(len(bounds) - 1):
+        r0, r1 = int(bounds[g]), int(bounds[g + 1])
+        wins.append(part.column_window(crd[int(pos[r0]):int(pos[r1])], r0, r1))
+    return wins
+
+
+class ShardedSpmv:
+    """y_local = (y_local) + A[rows of this rank, :] x with x replicated on every rank."""
+
+    def __init__(self, pos, crd, val, shape, rank: int, world: int, device):
+        from .device import CsrMatrix
+        self.bounds, lpos, lcrd, lval = local_block(pos, crd, val, rank, world)
+        self.r0, self.r1 = int(self.bounds[rank]), int(self.bounds[rank + 1])
+        self.matrix = CsrMatrix.from_host(lpos, lcrd, lval, (self.r1 - self.r0, shape[1]), device)
+
+    def spmv(self, x, y_local, accumulate=True):
+        return self.matrix.spmv(x, y_local, accumulate)
+
+    def spmm(self, B, C_local, accumulate=True):
+        return self.matrix.spmm(B, C_local, accumulate)
+
+
+class DistPcg:
+    """Jacobi-preconditioned CG (examples/pcg_solve.py:52-101 in the LAPIS project) on a
+    row-partitioned matrix.  Construct on every rank with the same host CSR, b and dinv."""
+
+    def __init__(self, pos, crd, val, shape, b, dinv, device, group=None, use_graph: bool = True):
+        from ._lib import check, load
+        from .device import CsrMatrix
+        self._check, self._lib = check, load()
+        self.group = group
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.device = torch.device(device)
+        self.use_graph = use_graph
+        n_global = int(shape[0])
+        if shape[0] != shape[1]:
+            raise ValueError("pcg: matrix is not square")
+        self.bounds, lpos, lcrd, lval = local_block(pos, crd, val, self.rank, self.world)
+        windows = all_windows(pos, crd, self.bounds)
+        self.halo = HaloExchanger(self.bounds, windows, self.rank, group)
+        self.n = self.halo.r1 - self.halo.r0
+        self.n_p = self.halo.window_len
+        self.p_off = self.halo.own_offset
+        lcrd = (lcrd.astype(np.int64) - self.halo.c0).astype(lcrd.dtype)  # columns index the window
+        with torch.cuda.device(self.device):
+            self.matrix = CsrMatrix.from_host(lpos, lcrd, lval, (self.n, self.n_p), self.device)
+            sl = slice(self.halo.r0, self.halo.r1)
+            self.b = torch.as_tensor(np.ascontiguousarray(b[sl])).to(self.device)
+            self.dinv = torch.as_tensor(np.ascontiguousarray(dinv[sl])).to(self.device)
+            self.x = torch.zeros(self.n, dtype=torch.float64, device=self.device)
+            nbytes = int(self._lib.lapis_b200_pcg_workspace_bytes(self.n, self.n_p))
+            self.work = torch.zeros(nbytes // 8, dtype=torch.float64, device=self.device)
+            offs = (ctypes.c_int64 * 4)()
+            check(self._lib.lapis_b200_pcg_workspace_layout(self.n, self.n_p, offs))
+            self.p_ext = self.work[offs[2]:offs[2] + self.n_p]
+            self.sc = self.work[0:8]
+            self.flags = self.work[8:10].view(torch.int64)
+        self.n_global = n_global
+        self._graph = None
+
+    # -- one iteration, enqueued on the current stream ---------------------------------
+    def _stream(self):
+        return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    def _allreduce(self, t):
+        if self.world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.SUM, group=self.group)
+
+    def _iteration(self, tol: float, maxiter: int):
+        lib, check, w = self._lib, self._check, ctypes.c_void_p(self.work.data_ptr())
+        single = 1 if self.world == 1 else 0
+        if self.world > 1:
+            self.halo.exchange(self.p_ext)
+        check(lib.lapis_b200_pcg_step_spmv(w, self.matrix.handle, self.n_p, self.p_off, single, self._stream()))
+        if not single:
+            self._allreduce(self.sc[0:1])
+            check(lib.lapis_b200_pcg_derive(w, 2, tol, maxiter, self._stream()))
+        check(lib.lapis_b200_pcg_step_update(w, self.n, self.n_p, self.p_off, ctypes.c_void_p(self.dinv.data_ptr()),
+                                             ctypes.c_void_p(self.x.data_ptr()), single, tol, maxiter, self._stream()))
+        if not single:
+            self._allreduce(self.sc[1:3])
+            check(lib.lapis_b200_pcg_derive(w, 3, tol, maxiter, self._stream()))
+        check(lib.lapis_b200_pcg_step_direction(w, self.n, self.n_p, self.p_off, self._stream()))
+
+    def _init(self, tol, maxiter):
+        lib, check, w = self._lib, self._check, ctypes.c_void_p(self.work.data_ptr())
+        single = 1 if self.world == 1 else 0
+        check(lib.lapis_b200_pcg_init(w, self.n, self.n_p, self.p_off, ctypes.c_void_p(self.b.data_ptr()),
+                                      ctypes.c_void_p(self.dinv.data_ptr()), ctypes.c_void_p(self.x.data_ptr()),
+                                      single, self._stream()))
+        if not single:
+            self._allreduce(self.sc[1:3])
+            check(lib.lapis_b200_pcg_derive(w, 1, tol, maxiter, self._stream()))
+
+    def solve(self, tol: float, maxiter: int, check_every: int = 25):
+        """Returns (x_local, iters, relres); x_local holds rows [bounds[rank], bounds[rank+1])."""
+        limit = maxiter if maxiter > 0 else 1 << 31
+        with torch.cuda.device(self.device):
+            self._init(tol, maxiter)
+            if self.use_graph and self._graph is None:
+                # Warm up once on a side stream (NCCL and the kernels must have run before capture);
+                # then rewind the solver state and capture one iteration.
+                s = torch.cuda.Stream()
+                s.wait_stream(torch.cuda.current_stream())
+                with torch.cuda.stream(s):
+                    self._iteration(tol, maxiter)
+                torch.cuda.current_stream().wait_stream(s)
+                torch.cuda.synchronize()
+                self._init(tol, maxiter)
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g):
+                    self._iteration(tol, maxiter)
+                self._graph = (g, tol, maxiter)
+                self._init(tol, maxiter)  # capture does not execute; state is still the initial one
+            if self._graph is not None and self._graph[1:] != (tol, maxiter):
+                raise ValueError("a captured solver is bound to its tol/maxiter; build a new DistPcg")
+            i = 0
+            done = False
+            while not done and i < limit:
+                burst = min(check_every, limit - i)
+                for _ in range(burst):
+                    if self._graph is not None:
+                        self._graph[0].replay()
+                    else:
+                        self._iteration(tol, maxiter)
+                i += burst
+                fl = self.flags.cpu()
+                done = bool(fl[0].item())
+            iters = int(self.flags[1].item())
+            relres = float(self.sc[5].item())
+        return self.x, iters, relres

@@ -1,0 +1,147 @@
+"""MLIR inputs for the compile-and-call tests: the same operations a LAPIS user hands to
+``KokkosBackend.compile`` for the accelerated path, written out for these tests."""
+
+CSR32 = "#CSR = #sparse_tensor.encoding<{ map = (i, j) -> (i : dense, j : compressed), posWidth = 32, crdWidth = 32 }>"
+CSR64 = "#CSR = #sparse_tensor.encoding<{ map = (i, j) -> (i : dense, j : compressed), posWidth = 64, crdWidth = 64 }>"
+CSRIDX = "#CSR = #sparse_tensor.encoding<{ map = (i, j) -> (i : dense, j : compressed) }>"
+
+
+def spmv(enc=CSR32):
+    return enc + """
+module {
+  func.func @spmv(%A: tensor<?x?xf64, #CSR>, %x: tensor<?xf64>, %y: tensor<?xf64>) -> tensor<?xf64> {
+    %r = linalg.matvec ins(%A, %x : tensor<?x?xf64, #CSR>, tensor<?xf64>) outs(%y : tensor<?xf64>) -> tensor<?xf64>
+    return %r : tensor<?xf64>
+  }
+}"""
+
+
+def spmm(enc=CSR64):
+    return enc + """
+module {
+  func.func @spmm(%A: tensor<?x?xf64, #CSR>, %B: tensor<?x?xf64>, %C: tensor<?x?xf64>) -> tensor<?x?xf64> {
+    %r = linalg.matmul ins(%A, %B : tensor<?x?xf64, #CSR>, tensor<?x?xf64>) outs(%C : tensor<?x?xf64>) -> tensor<?x?xf64>
+    return %r : tensor<?x?xf64>
+  }
+}"""
+
+
+MATMUL = """
+module {
+  func.func @forward(%a: tensor<?x?xf32>, %b: tensor<?x?xf32>, %c: tensor<?x?xf32>) -> tensor<?x?xf32> {
+    %i1 = arith.constant 1 : index
+    %i0 = arith.constant 0 : index
+    %ka = tensor.dim %a, %i1 : tensor<?x?xf32>
+    %kb = tensor.dim %b, %i0 : tensor<?x?xf32>
+    %same = arith.cmpi eq, %ka, %kb : index
+    cf.assert %same, "mismatching contracting dimension for torch.aten.mm"
+    %r = linalg.matmul ins(%a, %b : tensor<?x?xf32>, tensor<?x?xf32>) outs(%c : tensor<?x?xf32>) -> tensor<?x?xf32>
+    return %r : tensor<?x?xf32>
+  }
+}"""
+
+BATCH_MATMUL = """
+module {
+  func.func @forward(%a: tensor<?x?x?xf32>, %b: tensor<?x?x?xf32>, %c: tensor<?x?x?xf32>) -> tensor<?x?x?xf32> {
+    %r = linalg.batch_matmul ins(%a, %b : tensor<?x?x?xf32>, tensor<?x?x?xf32>) outs(%c : tensor<?x?x?xf32>) -> tensor<?x?x?xf32>
+    return %r : tensor<?x?x?xf32>
+  }
+}"""
+
+
+def pcg(enc=CSR32):
+    return enc + """
+#id = affine_map<(i) -> (i)>
+module {
+  func.func private @spmv(%A: tensor<?x?xf64, #CSR>, %x: tensor<?xf64>, %y: tensor<?xf64>) -> tensor<?xf64> {
+    %z = arith.constant 0.0 : f64
+    %y0 = linalg.fill ins(%z : f64) outs(%y : tensor<?xf64>) -> tensor<?xf64>
+    %r = linalg.matvec ins(%A, %x : tensor<?x?xf64, #CSR>, tensor<?xf64>) outs(%y0 : tensor<?xf64>) -> tensor<?xf64>
+    return %r : tensor<?xf64>
+  }
+  func.func private @dot(%x: tensor<?xf64>, %y: tensor<?xf64>) -> f64 {
+    %z = arith.constant 0.0 : f64
+    %acc = tensor.splat %z[] : tensor<f64>
+    %d = linalg.dot ins(%x, %y : tensor<?xf64>, tensor<?xf64>) outs(%acc : tensor<f64>) -> tensor<f64>
+    %s = tensor.extract %d[] : tensor<f64>
+    return %s : f64
+  }
+  func.func private @axpby(%a: f64, %x: tensor<?xf64>, %b: f64, %y: tensor<?xf64>, %dst: tensor<?xf64>) -> tensor<?xf64> {
+    %r = linalg.generic {indexing_maps = [#id, #id, #id], iterator_types = ["parallel"]}
+        ins(%x, %y : tensor<?xf64>, tensor<?xf64>) outs(%dst : tensor<?xf64>) {
+    ^bb0(%xv: f64, %yv: f64, %o: f64):
+      %t0 = arith.mulf %xv, %a : f64
+      %t1 = arith.mulf %yv, %b : f64
+      %t2 = arith.addf %t0, %t1 : f64
+      linalg.yield %t2 : f64
+    } -> tensor<?xf64>
+    return %r : tensor<?xf64>
+  }
+  func.func private @mult(%x: tensor<?xf64>, %y: tensor<?xf64>, %dst: tensor<?xf64>) -> tensor<?xf64> {
+    %r = linalg.generic {indexing_maps = [#id, #id, #id], iterator_types = ["parallel"]}
+        ins(%x, %y : tensor<?xf64>, tensor<?xf64>) outs(%dst : tensor<?xf64>) {
+    ^bb0(%xv: f64, %yv: f64, %o: f64):
+      %t = arith.mulf %xv, %yv : f64
+      linalg.yield %t : f64
+    } -> tensor<?xf64>
+    return %r : tensor<?xf64>
+  }
+  func.func @pcg(%A: tensor<?x?xf64, #CSR>, %b: tensor<?xf64>, %dinv: tensor<?xf64>, %tol: f64, %maxiter: index) -> (tensor<?xf64>, index, f64) {
+    %c0 = arith.constant 0 : index
+    %c1 = arith.constant 1 : index
+    %n = tensor.dim %b, %c0 : tensor<?xf64>
+    %f0 = arith.constant 0.0 : f64
+    %f1 = arith.constant 1.0 : f64
+    %e0 = tensor.empty(%n) : tensor<?xf64>
+    %e1 = tensor.empty(%n) : tensor<?xf64>
+    %e2 = tensor.empty(%n) : tensor<?xf64>
+    %e3 = tensor.empty(%n) : tensor<?xf64>
+    %r0 = linalg.copy ins(%b : tensor<?xf64>) outs(%e0 : tensor<?xf64>) -> tensor<?xf64>
+    %z0 = func.call @mult(%r0, %dinv, %e1) : (tensor<?xf64>, tensor<?xf64>, tensor<?xf64>) -> tensor<?xf64>
+    %p0 = linalg.copy ins(%z0 : tensor<?xf64>) outs(%e2 : tensor<?xf64>) -> tensor<?xf64>
+    %x0 = tensor.splat %f0[%n] : tensor<?xf64>
+    %rr0 = func.call @dot(%r0, %r0) : (tensor<?xf64>, tensor<?xf64>) -> f64
+    %res0 = math.sqrt %rr0 : f64
+    %x, %p, %z, %r, %relres, %rzout, %iters = scf.while (%xi = %x0, %pi = %p0, %zi = %z0, %ri = %r0, %rzi = %f0, %i = %c1)
+        : (tensor<?xf64>, tensor<?xf64>, tensor<?xf64>, tensor<?xf64>, f64, index)
+        -> (tensor<?xf64>, tensor<?xf64>, tensor<?xf64>, tensor<?xf64>, f64, f64, index) {
+      %Ap = func.call @spmv(%A, %pi, %e3) : (tensor<?x?xf64, #CSR>, tensor<?xf64>, tensor<?xf64>) -> tensor<?xf64>
+      %pAp = func.call @dot(%pi, %Ap) : (tensor<?xf64>, tensor<?xf64>) -> f64
+      %rz = func.call @dot(%ri, %zi) : (tensor<?xf64>, tensor<?xf64>) -> f64
+      %alpha = arith.divf %rz, %pAp : f64
+      %nalpha = arith.negf %alpha : f64
+      %xn = func.call @axpby(%f1, %xi, %alpha, %pi, %xi) : (f64, tensor<?xf64>, f64, tensor<?xf64>, tensor<?xf64>) -> tensor<?xf64>
+      %rn = func.call @axpby(%f1, %ri, %nalpha, %Ap, %ri) : (f64, tensor<?xf64>, f64, tensor<?xf64>, tensor<?xf64>) -> tensor<?xf64>
+      %rr = func.call @dot(%rn, %rn) : (tensor<?xf64>, tensor<?xf64>) -> f64
+      %nrm = math.sqrt %rr : f64
+      %rel = arith.divf %nrm, %res0 : f64
+      %open = arith.cmpf ogt, %rel, %tol : f64
+      %more = arith.cmpi ne, %i, %maxiter : index
+      %go = arith.andi %open, %more : i1
+      scf.condition(%go) %xn, %pi, %zi, %rn, %rel, %rz, %i : tensor<?xf64>, tensor<?xf64>, tensor<?xf64>, tensor<?xf64>, f64, f64, index
+    } do {
+    ^bb0(%xi: tensor<?xf64>, %pi: tensor<?xf64>, %zi: tensor<?xf64>, %ri: tensor<?xf64>, %unused: f64, %rzi: f64, %i: index):
+      %zn = func.call @mult(%ri, %dinv, %zi) : (tensor<?xf64>, tensor<?xf64>, tensor<?xf64>) -> tensor<?xf64>
+      %rzn = func.call @dot(%ri, %zn) : (tensor<?xf64>, tensor<?xf64>) -> f64
+      %beta = arith.divf %rzn, %rzi : f64
+      %pn = func.call @axpby(%f1, %zn, %beta, %pi, %pi) : (f64, tensor<?xf64>, f64, tensor<?xf64>, tensor<?xf64>) -> tensor<?xf64>
+      %in = arith.addi %i, %c1 : index
+      scf.yield %xi, %pn, %zn, %ri, %rzn, %in : tensor<?xf64>, tensor<?xf64>, tensor<?xf64>, tensor<?xf64>, f64, index
+    }
+    return %x, %iters, %relres : tensor<?xf64>, index, f64
+  }
+}"""
+
+UNSUPPORTED = """
+module {
+  func.func @relu(%x: tensor<?xf32>) -> tensor<?xf32> {
+    %z = arith.constant 0.0 : f32
+    %r = linalg.generic {indexing_maps = [affine_map<(i) -> (i)>, affine_map<(i) -> (i)>], iterator_types = ["parallel"]}
+        ins(%x : tensor<?xf32>) outs(%x : tensor<?xf32>) {
+    ^bb0(%v: f32, %o: f32):
+      %m = arith.maximumf %v, %z : f32
+      linalg.yield %m : f32
+    } -> tensor<?xf32>
+    return %r : tensor<?xf32>
+  }
+}"""

@@ -1,0 +1,139 @@
+"""CPU-side checks of the boundary: the library loads and exports what the header declares,
+fails loudly without a device, and its host-side integer logic matches the oracle."""
+import ctypes
+import os
+import re
+
+import numpy as np
+import pytest
+import torch
+
+from lapis_b200 import KokkosBackend as KB
+from lapis_b200 import _lib, _memref, partition
+from oracle import oracle
+from tests import mlir_modules as mm
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+HAS_GPU = torch.cuda.is_available()
+
+
+def _declared_symbols():
+    text = open(os.path.join(ROOT, "include", "lapis_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    names = re.findall(r"\b((?:lapis|py)_\w+)\s*\(", text)
+    return sorted(set(names))
+
+
+def test_library_exports_every_declared_symbol():
+    lib = _lib.load()
+    names = _declared_symbols()
+    assert len(names) >= 30
+    for n in names:
+        assert hasattr(lib, n), f"{n} is declared in include/lapis_b200.h but not exported"
+
+
+def test_descriptor_layout_matches_strided_memref():
+    # {T* basePtr; T* data; int64 offset; int64 sizes[N]; int64 strides[N]} (LAPISSupport.hpp:7-14)
+    for rank in (1, 2, 3):
+        D = _memref.make_nd_memref_descriptor(rank)
+        assert ctypes.sizeof(D) == 8 * (3 + 2 * rank)
+    a = np.arange(24, dtype=np.float64).reshape(2, 3, 4)
+    d = _memref.get_ranked_memref_descriptor(a)
+    assert list(d.shape) == [2, 3, 4] and list(d.strides) == [12, 4, 1] and d.offset == 0
+    back = _memref.ranked_memref_to_numpy(ctypes.pointer(d), np.float64)
+    assert np.array_equal(back, a) and back.ctypes.data == a.ctypes.data
+
+
+@pytest.mark.skipif(HAS_GPU, reason="checks the no-device behaviour")
+def test_no_device_fails_loudly():
+    lib = _lib.load()
+    lib.lapis_initialize()
+    assert lib.lapis_last_error() == 3  # LAPIS_ECUDA
+    assert b"no CPU path" in lib.lapis_last_error_message()
+    with pytest.raises(_lib.LapisError):
+        KB.KokkosBackend(decompose_tensors=True).compile(mm.spmv())
+
+
+def test_compute_before_initialize_is_refused():
+    lib = _lib.load()
+    pos = np.array([0, 1], dtype=np.int32)
+    crd = np.array([0], dtype=np.int32)
+    val = np.array([2.0])
+    x = np.array([3.0])
+    y = np.zeros(1)
+    spec = np.array([1, 1, 2, 1, 1], dtype=np.int64)
+    d = lambda a: ctypes.pointer(_memref.get_ranked_memref_descriptor(a))
+    ret = ctypes.pointer(ctypes.pointer(_memref.make_nd_memref_descriptor(1)()))
+    # make sure no module is alive in this process
+    while lib.lapis_last_error() != 5:
+        lib.lapis_finalize()
+        lib.py_spmv_f64_i32(ret, d(pos), d(crd), d(val), spec.ctypes.data_as(ctypes.c_void_p), d(x), d(y))
+        if lib.lapis_last_error() == 0:
+            continue
+        break
+    assert lib.lapis_last_error() in (5, 3)
+    assert y[0] == 0.0
+
+
+def test_backend_classifies_on_path_modules():
+    enc = KB._parse_encodings(mm.pcg())
+    funcs = KB._parse_functions(mm.pcg(), enc)
+    by = {f["name"]: f for f in funcs}
+    assert set(by) == {"spmv", "dot", "axpby", "mult", "pcg"}
+    assert by["spmv"]["private"] and not by["pcg"]["private"]
+    assert KB._classify(by["pcg"], by)[:2] == ("pcg", "i32")
+    for text, want in ((mm.spmv(mm.CSR32), ("spmv", "i32")), (mm.spmv(mm.CSR64), ("spmv", "i64")),
+                       (mm.spmv(mm.CSRIDX), ("spmv", "i64")), (mm.spmm(), ("spmm", "i64")),
+                       (mm.MATMUL, ("matmul", "")), (mm.BATCH_MATMUL, ("batch_matmul", ""))):
+        enc = KB._parse_encodings(text)
+        funcs = KB._parse_functions(text, enc)
+        public = [f for f in funcs if not f["private"]]
+        assert len(public) == 1
+        assert KB._classify(public[0], {f["name"]: f for f in funcs})[:2] == want
+
+
+def test_backend_rejects_off_path_modules():
+    with pytest.raises(Exception, match="not on the accelerated path"):
+        KB.KokkosBackend().compile(mm.UNSUPPORTED)
+    with pytest.raises(Exception, match="decompose_tensors"):
+        KB.KokkosBackend(decompose_tensors=False).compile(mm.spmv())
+    with pytest.raises(Exception, match="parallelization strategy"):
+        KB.KokkosBackend(parallel_strategy="bogus")
+
+
+@pytest.mark.parametrize("G", [1, 2, 4, 8])
+def test_partition_rows_matches_oracle(G):
+    rng = np.random.default_rng(G)
+    lens = rng.integers(0, 30, 5000)
+    lens[100:400] = 0
+    lens[2500] = 4096
+    for dt in (np.int32, np.int64):
+        pos = np.zeros(5001, dtype=dt)
+        pos[1:] = np.cumsum(lens)
+        got = partition.partition_rows(pos, G)
+        assert np.array_equal(got, oracle.partition_rows(pos, G))
+        assert np.array_equal(got, oracle.partition_rows_numpy(pos, G))
+        # a slice with a non-zero base partitions like the rebased slice
+        sub = pos[1000:3001]
+        assert np.array_equal(partition.partition_rows(np.ascontiguousarray(sub), G),
+                              oracle.partition_rows_numpy(sub - sub[0], G))
+
+
+def test_exchange_plan_and_windows():
+    from lapis_b200 import workloads as w
+    pos, crd, val = w.laplacian_2d(16)
+    bounds = partition.partition_rows(pos, 4)
+    from lapis_b200.dist import all_windows
+    wins = all_windows(pos, crd, bounds)
+    recv, send = partition.exchange_plan(bounds, wins)
+    for g in range(4):
+        r0, r1 = bounds[g], bounds[g + 1]
+        c0, c1 = wins[g]
+        assert c0 == max(0, r0 - 16) and c1 == min(256, r1 + 16)
+        covered = sum(e - s for _, s, e in recv[g]) + (r1 - r0)
+        assert covered == c1 - c0
+        for (o, s, e) in recv[g]:
+            assert bounds[o] <= s < e <= bounds[o + 1]
+            assert (g, s, e) in send[o]
+    lpos, lcrd, lval = partition.row_block(pos, crd, val, int(bounds[1]), int(bounds[2]))
+    assert lpos[0] == 0 and lpos[-1] == len(lcrd) == len(lval)

@@ -1,0 +1,342 @@
+"""Parity of the CUDA path with the CPU oracle, through the C ABI (needs a B200).
+
+Tolerances.  Integer work (offsets, partition bounds) is bit-exact.  Kernels that keep
+the reference's summation order -- SpMM, the general-shape matmul, axpby, mult -- are
+compared bit for bit.  SpMV and dot sum a row / vector in a different (fixed) order than
+the sequential CPU loop, so they are held to 1e-12 relative to the magnitude of the terms
+that were summed, TOL_F64 below; every such kernel must also give identical bits when run
+twice (no atomics anywhere).
+"""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from lapis_b200 import KokkosBackend as KB
+from lapis_b200 import workloads as w
+from oracle import oracle
+from tests import mlir_modules as mm
+
+pytestmark = pytest.mark.gpu
+
+TOL_F64 = 1e-12
+
+
+def _dev():
+    if not torch.cuda.is_available():
+        pytest.fail("no CUDA device: the gpu-marked tests must run on a GPU box")
+    return torch.device("cuda:0")
+
+
+def _spec(pos, crd, val, shape):
+    return (shape, (len(pos), len(crd), len(val)))
+
+
+def _row_scale(pos, crd, val, x, y_in):
+    """|y_in| + sum_j |val_j x_j| per row: the magnitude the rounding errors scale with."""
+    absprod = np.abs(val) * np.abs(x[crd])
+    return oracle.spmv(pos, crd, absprod, np.ones_like(x), np.abs(y_in))
+
+
+def _assert_spmv_close(y, ref, scale):
+    err = np.abs(y - ref)
+    bound = TOL_F64 * np.maximum(scale, np.finfo(np.float64).tiny)
+    assert np.all(err <= bound), f"max err/scale = {np.max(err / np.maximum(scale, 1e-300)):.3e}"
+
+
+def _random_csr(rng, lens, ncols, idx):
+    pos, crd = w.random_csr_from_lengths(lens, ncols, rng, idx)
+    return pos, crd, rng.uniform(-1, 1, crd.size)
+
+
+# ---------------------------------------------------------------------------
+# SpMV
+# ---------------------------------------------------------------------------
+def test_spmv_known_answer_through_backend(golden_dir):
+    # examples/spmv_noalloc.py:16-37 in the LAPIS project
+    _dev()
+    g = np.load(os.path.join(golden_dir, "spmv_noalloc.npz"))
+    module = KB.KokkosBackend(decompose_tensors=True).compile(mm.spmv(mm.CSR32))
+    y = np.zeros(5)
+    out = module.spmv(g["rowptrs"], g["colinds"], g["values"], ((5, 5), (6, 8, 8)), np.ones(5), y)
+    assert np.allclose(y, g["ycorrect"]) and out is y
+    assert np.array_equal(y, oracle.spmv(g["rowptrs"], g["colinds"], g["values"], np.ones(5), np.zeros(5)))
+    # accumulates into y
+    module.spmv(g["rowptrs"], g["colinds"], g["values"], ((5, 5), (6, 8, 8)), np.ones(5), y)
+    assert np.allclose(y, 2 * g["ycorrect"])
+
+
+@pytest.mark.parametrize("idx", [np.int32, np.int64])
+@pytest.mark.parametrize("case", ["uniform10", "powerlaw", "ragged", "empty_rows", "one_huge_row", "all_empty", "dense_rows"])
+def test_spmv_matches_oracle(idx, case):
+    from lapis_b200.device import CsrMatrix
+    dev = _dev()
+    rng = np.random.default_rng(sum(map(ord, case)))
+    if case == "uniform10":      # config 1 of the benchmark
+        d = w.spmv_uniform(10_000, 10, idx)
+        pos, crd, val, ncols = d["pos"], d["crd"], d["val"], 10_000
+    elif case == "powerlaw":     # config 2 at 1/64 size
+        d = w.spmv_power_law(1 << 17, idx_dtype=idx)
+        pos, crd, val, ncols = d["pos"], d["crd"], d["val"], 1 << 17
+    elif case == "ragged":       # rows % 32 != 0, lengths 0..70
+        lens = rng.integers(0, 70, 1237)
+        ncols = 999
+        pos, crd, val = _random_csr(rng, lens, ncols, idx)
+    elif case == "empty_rows":   # long runs of empty rows, also at both ends
+        lens = rng.integers(0, 6, 50_000)
+        lens[:3000] = 0
+        lens[20_000:26_000] = 0
+        lens[-2500:] = 0
+        ncols = 50_000
+        pos, crd, val = _random_csr(rng, lens, ncols, idx)
+    elif case == "one_huge_row":  # a row spanning many tiles among short rows
+        lens = rng.integers(1, 5, 3000)
+        lens[1500] = 40_000
+        lens[7] = 4096
+        ncols = 50_000
+        pos, crd, val = _random_csr(rng, lens, ncols, idx)
+    elif case == "all_empty":
+        lens = np.zeros(777, dtype=np.int64)
+        ncols = 10
+        pos, crd, val = _random_csr(rng, lens, ncols, idx)
+    else:                        # every row longer than a tile's average threshold
+        lens = np.full(300, 700)
+        ncols = 4000
+        pos, crd, val = _random_csr(rng, lens, ncols, idx)
+    nrows = len(pos) - 1
+    x = rng.uniform(-1, 1, ncols)
+    y0 = rng.uniform(-1, 1, nrows)
+    A = CsrMatrix.from_host(pos, crd, val, (nrows, ncols), dev)
+    assert A.nnz == len(crd)
+    xd = torch.as_tensor(x).to(dev)
+    for accumulate in (True, False):
+        yd = torch.as_tensor(y0).to(dev)
+        A.spmv(xd, yd, accumulate=accumulate)
+        y = yd.cpu().numpy()
+        y_in = y0 if accumulate else np.zeros(nrows)
+        ref = oracle.spmv(pos, crd, val, x, y_in)
+        _assert_spmv_close(y, ref, _row_scale(pos, crd, val, x, y_in))
+        yd2 = torch.as_tensor(y0).to(dev)
+        A.spmv(xd, yd2, accumulate=accumulate)
+        assert torch.equal(yd, yd2), "SpMV is not run-to-run deterministic"
+    # rows with at most one entry involve no reordering: identical bits
+    short = np.flatnonzero(np.diff(pos) <= 1)
+    if short.size:
+        yd = torch.as_tensor(y0).to(dev)
+        A.spmv(xd, yd, accumulate=True)
+        assert np.array_equal(yd.cpu().numpy()[short], oracle.spmv(pos, crd, val, x, y0)[short])
+
+
+def test_spmv_row_block_in_place():
+    """A handle over rows [r0, r1) of a larger matrix (non-zero pos[0]) gives that slice of y."""
+    from lapis_b200.device import CsrMatrix
+    dev = _dev()
+    d = w.spmv_power_law(1 << 14, idx_dtype=np.int64)
+    pos, crd, val, x = d["pos"], d["crd"], d["val"], d["x"]
+    n = len(pos) - 1
+    ref = oracle.spmv(pos, crd, val, x, np.zeros(n))
+    pos_d, crd_d, val_d = (torch.as_tensor(a).to(dev) for a in (pos, crd, val))
+    xd = torch.as_tensor(x).to(dev)
+    r0, r1 = 3001, 11_111
+    A = CsrMatrix(pos_d[r0:r1 + 1], crd_d, val_d, (r1 - r0, n))
+    assert A.nnz == pos[r1] - pos[r0]
+    yd = torch.zeros(r1 - r0, dtype=torch.float64, device=dev)
+    A.spmv(xd, yd, accumulate=False)
+    scale = _row_scale(pos, crd, val, x, np.zeros(n))[r0:r1]
+    _assert_spmv_close(yd.cpu().numpy(), ref[r0:r1], scale)
+
+
+def test_spmv_full_size_properties():
+    """Config 2 at full size (2^23 rows, ~1.34e8 entries): linearity and a row-sum identity,
+    which need no CPU pass over the whole matrix."""
+    from lapis_b200.device import CsrMatrix
+    dev = _dev()
+    d = w.spmv_power_law()
+    pos, crd, val, x = d["pos"], d["crd"], d["val"], d["x"]
+    n = len(pos) - 1
+    A = CsrMatrix.from_host(pos, crd, val, (n, n), dev)
+    xd = torch.as_tensor(x).to(dev)
+    y1 = torch.zeros(n, dtype=torch.float64, device=dev)
+    A.spmv(xd, y1, accumulate=False)
+    # A(2x) = 2 A x exactly (scaling by 2 is exact in binary floating point)
+    y2 = torch.zeros(n, dtype=torch.float64, device=dev)
+    A.spmv(2.0 * xd, y2, accumulate=False)
+    assert torch.equal(y2, 2.0 * y1)
+    # accumulate: y1 + A x == 2 A x up to one rounding of the final add
+    y3 = y1.clone()
+    A.spmv(xd, y3, accumulate=True)
+    assert torch.allclose(y3, 2.0 * y1, rtol=1e-15, atol=0)
+    # x = 1: y = row sums of val, checked against numpy's reduceat on the host
+    ones = torch.ones(n, dtype=torch.float64, device=dev)
+    ys = torch.zeros(n, dtype=torch.float64, device=dev)
+    A.spmv(ones, ys, accumulate=False)
+    rowsum = np.add.reduceat(val, pos[:-1].astype(np.int64))
+    absum = np.add.reduceat(np.abs(val), pos[:-1].astype(np.int64))
+    assert np.all(np.abs(ys.cpu().numpy() - rowsum) <= TOL_F64 * absum)
+    # a sample of rows against the oracle
+    rows = np.random.default_rng(5).integers(0, n, 2000)
+    yh = y1.cpu().numpy()
+    for r in rows:
+        lo, hi = int(pos[r]), int(pos[r + 1])
+        ref = oracle.spmv(np.array([0, hi - lo], dtype=np.int64), crd[lo:hi], val[lo:hi], x, np.zeros(1))[0]
+        assert abs(yh[r] - ref) <= TOL_F64 * np.sum(np.abs(val[lo:hi] * x[crd[lo:hi]]))
+
+
+# ---------------------------------------------------------------------------
+# SpMM
+# ---------------------------------------------------------------------------
+@pytest.mark.parametrize("idx", [np.int32, np.int64])
+@pytest.mark.parametrize("k", [64, 5, 130, 2])
+def test_spmm_bit_exact(idx, k):
+    from lapis_b200.device import CsrMatrix
+    dev = _dev()
+    rng = np.random.default_rng(k)
+    lens = rng.integers(0, 80, 2001)
+    lens[11] = 0
+    lens[500] = 900
+    ncols = 1500
+    pos, crd, val = _random_csr(rng, lens, ncols, idx)
+    B = rng.uniform(-1, 1, (ncols, k))
+    C0 = rng.uniform(-1, 1, (2001, k))
+    A = CsrMatrix.from_host(pos, crd, val, (2001, ncols), dev)
+    Bd = torch.as_tensor(B).to(dev)
+    for accumulate in (True, False):
+        Cd = torch.as_tensor(C0).to(dev)
+        A.spmm(Bd, Cd, accumulate=accumulate)
+        ref = oracle.spmm(pos, crd, val, B, C0 if accumulate else np.zeros_like(C0))
+        assert np.array_equal(Cd.cpu().numpy(), ref)
+
+
+def test_spmm_config3_shape_through_backend():
+    """Config 3 at 1/256 size (8192 rows, 32 per row, k = 64) through py_spmm with host buffers."""
+    _dev()
+    d = w.spmm_uniform(1 << 13)
+    n = 1 << 13
+    module = KB.KokkosBackend(decompose_tensors=True).compile(mm.spmm(mm.CSR64))
+    C = np.zeros((n, 64))
+    out = module.spmm(d["pos"], d["crd"], d["val"], _spec(d["pos"], d["crd"], d["val"], (n, n)), d["B"], C)
+    assert out is C
+    assert np.array_equal(C, oracle.spmm(d["pos"], d["crd"], d["val"], d["B"], np.zeros((n, 64))))
+
+
+# ---------------------------------------------------------------------------
+# dense / batched matmul
+# ---------------------------------------------------------------------------
+def test_matmul_examples_through_backend(golden_dir):
+    _dev()
+    g = np.load(os.path.join(golden_dir, "gemm.npz"))             # examples/gemm_no_alloc.py
+    module = KB.KokkosBackend().compile(mm.MATMUL)
+    c = torch.zeros((8, 9))
+    module.forward(torch.as_tensor(g["a"]), torch.as_tensor(g["b"]), c)   # CPU torch tensors, updated in place
+    assert np.allclose(c.numpy(), g["c"])
+    assert np.array_equal(c.numpy(), oracle.gemm(g["a"], g["b"], np.zeros((8, 9), dtype=np.float32)))
+    g = np.load(os.path.join(golden_dir, "batched_gemm.npz"))     # examples/batched_gemm_no_alloc.py
+    module = KB.KokkosBackend().compile(mm.BATCH_MATMUL)
+    c = np.zeros((64, 5, 5), dtype=np.float32)
+    module.forward(g["a"], g["b"], c)
+    assert np.array_equal(c, g["c"])
+    with pytest.raises(Exception, match="contracting"):
+        KB.KokkosBackend().compile(mm.MATMUL).forward(np.zeros((4, 3), np.float32), np.zeros((5, 2), np.float32),
+                                                     np.zeros((4, 2), np.float32))
+
+
+@pytest.mark.parametrize("shape", [(1, 33, 17, 65), (7, 31, 32, 33), (3, 64, 64, 8), (1, 1, 1, 1), (2, 100, 3, 257)])
+def test_bgemm_general_shapes_bit_exact(shape):
+    from lapis_b200.device import bgemm
+    dev = _dev()
+    b, M, N, K = shape
+    rng = np.random.default_rng(M * N + K)
+    A = rng.uniform(-1, 1, (b, M, K)).astype(np.float32)
+    B = rng.uniform(-1, 1, (b, K, N)).astype(np.float32)
+    C0 = rng.uniform(-1, 1, (b, M, N)).astype(np.float32)
+    Cd = torch.as_tensor(C0).to(dev)
+    bgemm(torch.as_tensor(A).to(dev), torch.as_tensor(B).to(dev), Cd)
+    assert np.array_equal(Cd.cpu().numpy(), oracle.bgemm(A, B, C0))
+
+
+# ---------------------------------------------------------------------------
+# vector kernels and PCG
+# ---------------------------------------------------------------------------
+def test_vector_kernels():
+    from lapis_b200 import device as D
+    dev = _dev()
+    rng = np.random.default_rng(1)
+    for n in (1, 1000, 1 << 20, (1 << 20) + 77):
+        x, y = rng.uniform(-1, 1, n), rng.uniform(-1, 1, n)
+        xd, yd = torch.as_tensor(x).to(dev), torch.as_tensor(y).to(dev)
+        dst = torch.empty_like(xd)
+        assert np.array_equal(D.axpby(0.3, xd, -1.7, yd, dst).cpu().numpy(), oracle.axpby(0.3, x, -1.7, y))
+        assert np.array_equal(D.mult(xd, yd, dst).cpu().numpy(), oracle.mult(x, y))
+        got = float(D.dot(xd, yd).item())
+        assert abs(got - oracle.dot(x, y)) <= TOL_F64 * float(np.sum(np.abs(x * y)))
+        assert got == float(D.dot(xd, yd).item())
+
+
+def test_pcg_nos4_through_backend(golden_dir):
+    # examples/pcg_solve.py:106-141 in the LAPIS project
+    _dev()
+    g = np.load(os.path.join(golden_dir, "pcg_nos4.npz"))
+    n = len(g["b"])
+    module = KB.KokkosBackend(decompose_tensors=True).compile(mm.pcg(mm.CSR32))
+    spec = ((n, n), (n + 1, len(g["indices"]), len(g["data"])))
+    x, iters, relres = module.pcg(g["indptr"], g["indices"], g["data"], spec, g["b"], g["dinv"],
+                                  float(g["reltol"]), int(g["maxiter"]))
+    assert np.allclose(x, g["x_scipy"])                       # the reference's own check
+    xo, io, ro = oracle.pcg(g["indptr"], g["indices"], g["data"], g["b"], g["dinv"], float(g["reltol"]),
+                            int(g["maxiter"]))
+    assert iters == io == 40
+    assert np.max(np.abs(x - xo)) <= 1e-10 * np.max(np.abs(xo))
+    assert abs(relres - ro) <= 1e-8 * ro
+    # converges when allowed to
+    x, iters, relres = module.pcg(g["indptr"], g["indices"], g["data"], spec, g["b"], g["dinv"], 1e-10, 400)
+    xo, io, ro = oracle.pcg(g["indptr"], g["indices"], g["data"], g["b"], g["dinv"], 1e-10, 400)
+    assert relres <= 1e-10 and abs(iters - io) <= 1
+    assert np.max(np.abs(x - 1.0)) < 1e-8
+    # iteration-count semantics (i starts at 1; tol = 0 runs exactly maxiter iterations)
+    for m in (1, 2, 17):
+        _, iters, _ = module.pcg(g["indptr"], g["indices"], g["data"], spec, g["b"], g["dinv"], 0.0, m)
+        assert iters == m
+
+
+def test_pcg_step_parity_laplacian():
+    """One iteration from the oracle's state reproduces the oracle's next state: the passes are
+    checked without CG's amplification of rounding differences (config 5 at 128x128)."""
+    from lapis_b200.device import CsrMatrix
+    from lapis_b200.dist import DistPcg
+    dev = _dev()
+    d = w.pcg_laplacian(128)
+    n = d["shape"][0]
+    pos, crd, val, b, dinv = d["pos"], d["crd"], d["val"], d["b"], d["dinv"]
+    # the first k iterations: per-iteration scalars against the oracle's trace
+    xo, io, ro, tr = oracle.pcg(pos, crd, val, b, dinv, 0.0, 25, trace=True)
+    solver = DistPcg(pos, crd, val, (n, n), b, dinv, dev, use_graph=False)
+    x, iters, relres = solver.solve(0.0, 25, check_every=1)
+    assert iters == io == 25
+    assert abs(relres - ro) <= 1e-9 * ro
+    assert np.max(np.abs(x.cpu().numpy() - xo)) <= 1e-9 * np.max(np.abs(xo))
+    # a single iteration (maxiter = 1) differs from the oracle only by the dot summation order
+    x1o, _, r1o, tr1 = oracle.pcg(pos, crd, val, b, dinv, 0.0, 1, trace=True)
+    A = CsrMatrix.from_host(pos, crd, val, (n, n), dev)
+    x1, it1, r1 = A.pcg(torch.as_tensor(b).to(dev), torch.as_tensor(dinv).to(dev), 0.0, 1)
+    assert it1 == 1
+    assert np.max(np.abs(x1.cpu().numpy() - x1o)) <= 1e-13 * np.max(np.abs(x1o))
+    assert abs(r1 - r1o) <= 1e-13 * r1o
+
+
+def test_pcg_laplacian_converges_and_graph_matches_eager():
+    from lapis_b200.dist import DistPcg
+    dev = _dev()
+    d = w.pcg_laplacian(96, idx_dtype=np.int64)
+    n = d["shape"][0]
+    args = (d["pos"], d["crd"], d["val"], (n, n), d["b"], d["dinv"], dev)
+    xe, ie, re_ = DistPcg(*args, use_graph=False).solve(1e-8, 2000, check_every=10)
+    xg, ig, rg = DistPcg(*args, use_graph=True).solve(1e-8, 2000, check_every=10)
+    assert ie == ig and re_ == rg and torch.equal(xe, xg)     # same kernels, same order: same bits
+    assert re_ <= 1e-8 and ie < 2000
+    xo, io, ro = oracle.pcg(d["pos"], d["crd"], d["val"], d["b"], d["dinv"], 1e-8, 2000)
+    assert abs(ie - io) <= 2
+    assert np.max(np.abs(xe.cpu().numpy() - xo)) <= 1e-6 * np.max(np.abs(xo))
+    # the solution satisfies the system
+    res = oracle.spmv(d["pos"], d["crd"], d["val"], xe.cpu().numpy(), -d["b"])
+    assert np.linalg.norm(res) <= 2e-8 * np.linalg.norm(d["b"])
