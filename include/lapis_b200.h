@@ -132,6 +132,22 @@ int64_t lapis_b200_csr_nnz(lapis_b200_csr_t h);
  * callers put in front of it (examples/pcg_solve.py:13-20). */
 int lapis_b200_spmv_f64(lapis_b200_csr_t h, const double *d_x, double *d_y, int accumulate, void *stream);
 
+/* The same SpMV for callers that must not allocate device memory in the call -- code
+ * running inside a pool that already owns the whole GPU, or a steady-state loop where
+ * a cudaMalloc could stall the device or fail.  No counterpart in the reference (its
+ * emitted kernels need no plan).  Takes the raw CSR arrays instead of a handle and
+ * keeps the streaming plan in a fixed 2 MiB array inside the library's device image,
+ * so it calls neither cudaMalloc nor cudaFree.
+ *   - Limit: 2^29 (536,870,912) stored entries; larger matrices get LAPIS_ETOOBIG.
+ *   - The first call on a device looks the array's address up (cudaGetSymbolAddress);
+ *     make that first call before any stream capture on that device.
+ *   - All calls on a device share the one array: calls that can overlap on the GPU
+ *     (different streams, no ordering between them) race.  Calls on one stream are safe.
+ *   - Reads pos[0] and pos[nrows] back, which synchronises `stream` once per call.
+ * Arguments as lapis_b200_csr_create followed by lapis_b200_spmv_f64. */
+int lapis_b200_spmv_f64_noalloc(int idx_bytes, int64_t nrows, int64_t ncols, const void *d_pos, const void *d_crd,
+                                const double *d_val, const double *d_x, double *d_y, int accumulate, void *stream);
+
 /* C = (accumulate ? C : 0) + A B with dense row-major B (ncols x k), C (nrows x k). */
 int lapis_b200_spmm_f64(lapis_b200_csr_t h, int64_t k, const double *d_B, double *d_C, int accumulate,
                         void *stream);

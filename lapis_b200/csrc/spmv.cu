@@ -482,3 +482,101 @@ extern "C" int lapis_b200_spmm_f64(lapis_b200_csr_t h, int64_t k, const double *
   if (h->idx_bytes == 4) return launch_spmm<int32_t>(h, k, d_B, d_C, accumulate, as_stream(stream));
   return launch_spmm<int64_t>(h, k, d_B, d_C, accumulate, as_stream(stream));
 }
+
+// ---------------------------------------------------------------------------
+// SpMV without any allocation.
+//
+// Some callers must not allocate device memory when they call in: a solver that
+// runs inside a memory pool another component has already sized to the whole GPU,
+// or a service whose steady state is forbidden to touch the allocator because a
+// cudaMalloc may synchronise the device or fail long after start-up.
+// lapis_b200_csr_create allocates the streaming plan (8 bytes per 2048 stored
+// entries); this entry point keeps that plan in a fixed array in the library's own
+// device image instead.  The price is a size limit and one shared buffer: every
+// GPU that loads the library holds the array until exit, every call overwrites all
+// entries it uses (nothing needs to start at zero), and two calls in flight on the
+// same device at the same time would overwrite each other's plan.
+// ---------------------------------------------------------------------------
+constexpr int64_t NOALLOC_MAX_TILES = 1 << 18;  // 2 MiB of plan: matrices of up to 2^29 stored entries
+static __device__ __align__(256) int64_t g_noalloc_plan[NOALLOC_MAX_TILES + 1];
+
+// Device address of g_noalloc_plan per device.  In host code the array's name is only a
+// handle for the runtime, not an address a kernel may use; cudaGetSymbolAddress returns the
+// address in the device that is current when it is called.
+static int64_t *g_noalloc_plan_addr[64] = {nullptr};
+
+static int noalloc_plan_ptr(int64_t **out) {
+  int dev = 0;
+  LAPIS_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return lapis_b200::fail(LAPIS_EBADARG, "spmv_noalloc: device index %d not supported", dev);
+  if (g_noalloc_plan_addr[dev] == nullptr) {
+    void *p = nullptr;
+    LAPIS_CUDA_TRY(cudaGetSymbolAddress(&p, g_noalloc_plan));
+    g_noalloc_plan_addr[dev] = static_cast<int64_t *>(p);
+  }
+  *out = g_noalloc_plan_addr[dev];
+  return LAPIS_OK;
+}
+
+extern "C" int lapis_b200_spmv_f64_noalloc(int idx_bytes, int64_t nrows, int64_t ncols, const void *d_pos,
+                                           const void *d_crd, const double *d_val, const double *d_x, double *d_y,
+                                           int accumulate, void *stream) {
+  clear_error();
+  if (idx_bytes != 4 && idx_bytes != 8) return fail(LAPIS_EBADARG, "spmv_noalloc: idx_bytes must be 4 or 8");
+  if (nrows < 0 || ncols < 0) return fail(LAPIS_EBADSHAPE, "spmv_noalloc: negative dimension");
+  if (d_pos == nullptr) return fail(LAPIS_EBADARG, "spmv_noalloc: pos is null");
+  if ((reinterpret_cast<uintptr_t>(d_val) % 16) || (reinterpret_cast<uintptr_t>(d_crd) % 16))
+    return fail(LAPIS_EBADARG, "spmv_noalloc: val and crd must be 16-byte aligned");
+  if (nrows == 0) return LAPIS_OK;
+  if (d_y == nullptr) return fail(LAPIS_EBADARG, "spmv_noalloc: y is null");
+  cudaStream_t st = as_stream(stream);
+  int64_t *plan = nullptr;
+  LAPIS_TRY(noalloc_plan_ptr(&plan));
+
+  // pos[0] and pos[nrows] (copied into host variables: no allocation involved)
+  int64_t ends[2] = {0, 0};
+  if (idx_bytes == 4) {
+    int32_t e32[2] = {0, 0};
+    LAPIS_CUDA_TRY(cudaMemcpyAsync(&e32[0], d_pos, 4, cudaMemcpyDeviceToHost, st));
+    LAPIS_CUDA_TRY(cudaMemcpyAsync(&e32[1], static_cast<const int32_t *>(d_pos) + nrows, 4, cudaMemcpyDeviceToHost, st));
+    LAPIS_CUDA_TRY(cudaStreamSynchronize(st));
+    ends[0] = e32[0];
+    ends[1] = e32[1];
+  } else {
+    LAPIS_CUDA_TRY(cudaMemcpyAsync(&ends[0], d_pos, 8, cudaMemcpyDeviceToHost, st));
+    LAPIS_CUDA_TRY(cudaMemcpyAsync(&ends[1], static_cast<const int64_t *>(d_pos) + nrows, 8, cudaMemcpyDeviceToHost, st));
+    LAPIS_CUDA_TRY(cudaStreamSynchronize(st));
+  }
+  if (ends[1] < ends[0] || ends[0] < 0) return fail(LAPIS_EBADSHAPE, "spmv_noalloc: pos is not non-decreasing");
+  const int64_t nnz = ends[1] - ends[0];
+  if (nnz > 0 && (d_crd == nullptr || d_val == nullptr || d_x == nullptr))
+    return fail(LAPIS_EBADARG, "spmv_noalloc: crd/val/x null");
+  int64_t nblk = (nnz + SPMV_TILE - 1) / SPMV_TILE;
+  if (nblk < 1) nblk = 1;
+  if (nblk > NOALLOC_MAX_TILES)
+    return fail(LAPIS_ETOOBIG,
+                "spmv_noalloc: %lld stored entries exceed the fixed plan buffer (limit %lld entries); "
+                "use lapis_b200_csr_create + lapis_b200_spmv_f64 for larger matrices",
+                (long long)nnz, (long long)(NOALLOC_MAX_TILES * (int64_t)SPMV_TILE));
+
+  lapis_b200_csr h;
+  h.idx_bytes = idx_bytes;
+  h.nrows = nrows;
+  h.ncols = ncols;
+  h.nnz = nnz;
+  h.base = ends[0];
+  h.pos = d_pos;
+  h.crd = d_crd;
+  h.val = d_val;
+  h.nblk = nblk;
+  h.blk_row = plan;
+  h.blk_partial = nullptr;
+  h.device = 0;
+  const unsigned pgrid = (unsigned)((nblk + 1 + 255) / 256);
+  if (idx_bytes == 4)
+    spmv_plan_kernel<int32_t><<<pgrid, 256, 0, st>>>(static_cast<const int32_t *>(d_pos), nrows, nblk, plan);
+  else
+    spmv_plan_kernel<int64_t><<<pgrid, 256, 0, st>>>(static_cast<const int64_t *>(d_pos), nrows, nblk, plan);
+  LAPIS_CUDA_TRY(cudaGetLastError());
+  return spmv_launch(&h, d_x, d_y, accumulate, nullptr, nullptr, nullptr, st);
+}
