@@ -133,15 +133,15 @@ def oracle_native():
 # ---------------------------------------------------------------------------
 # workloads: each returns host data + byte/flop accounting
 # ---------------------------------------------------------------------------
-def make_workload(name: str, small: bool):
+def make_workload(name: str, small: bool, shrink: int = 0):
     from lapis_b200 import workloads as w
     if name == "spmv":
-        d = w.spmv_power_law(1 << 16 if small else 1 << 23)
+        d = w.spmv_power_law(1 << 16 if small else (1 << 23) >> shrink)
         n, nnz = d["shape"][0], int(d["crd"].size)
         d.update(unit="GB/s", metric="csr_spmv_hbm_gbs", dtype="f64", unit_scale=1e-9,
                  work=w.spmv_bytes(n, n, nnz, 8), label=f"CSR SpMV fp64 power-law rows (config 2): {n} rows, {nnz} nnz, int64 indices")
     elif name == "spmm":
-        d = w.spmm_uniform(1 << 13 if small else 1 << 21)
+        d = w.spmm_uniform(1 << 13 if small else (1 << 21) >> shrink)
         n, nnz = d["shape"][0], int(d["crd"].size)
         d.update(unit="GB/s", metric="csr_spmm_hbm_gbs", dtype="f64", unit_scale=1e-9,
                  work=w.spmm_bytes(n, n, nnz, 64, 8), label=f"CSR SpMM fp64 (config 3): {n} rows, 32 nnz/row, k=64, int64 indices")
@@ -362,8 +362,9 @@ def run_ours(args, d, rank, world, local_rank):
 
         h2d = sum(int(t.numel() * t.element_size()) for t in pinned) + int(out.numel() * 8)
         d2h = int(out.numel() * 8)
-        e2e_steps = max(1, min(args.steps, 3))
-        e2e_step()
+        e2e_steps = 0 if args.no_e2e else max(1, min(args.steps, 3))
+        if e2e_steps:
+            e2e_step()
         if world > 1:
             dist.barrier()
         t0 = time.perf_counter()
@@ -374,9 +375,10 @@ def run_ours(args, d, rank, world, local_rank):
             t = torch.tensor([t_e2e], dtype=torch.float64, device=dev)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             t_e2e = float(t.item())
-        e2e = {"value": d["work"] * e2e_steps / t_e2e * d["unit_scale"], "unit": d["unit"],
-               "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps,
-               "api": f"KokkosBackend.compile(...).{name} -> py_{name}_f64_i64, pinned host buffers"}
+        if e2e_steps:
+            e2e = {"value": d["work"] * e2e_steps / t_e2e * d["unit_scale"], "unit": d["unit"],
+                   "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps,
+                   "api": f"KokkosBackend.compile(...).{name} -> py_{name}_f64_i64, pinned host buffers"}
         del pinned, out
         algo_bytes_rank = (len(lcrd) * 16 + len(lpos) * 8 + (8 * n + 8 * (r1 - r0)) * (1 if name == "spmv" else 64))
     elif name == "pcg":
@@ -537,6 +539,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--small", action="store_true", help="reduced sizes (for profiler captures and quick checks)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiler captures)")
+    ap.add_argument("--shrink", type=int, default=0, help="divide the SpMV/SpMM row count by 2^SHRINK (profiler captures)")
     args = ap.parse_args()
     defaults = {"spmv": (500, 10), "spmm": (50, 5), "pcg": (200, 5), "bgemm": (200, 10), "gemm": (20, 3)}
     if args.steps is None:
@@ -551,7 +555,7 @@ def main():
     if args.impl == "reference":
         if rank != 0:
             return 0
-        d = make_workload(args.workload, args.small)
+        d = make_workload(args.workload, args.small, args.shrink)
         run_reference(args, d)
         return 0
 
@@ -563,7 +567,7 @@ def main():
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         torch.cuda.set_device(local_rank)
         dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local_rank}"))
-    d = make_workload(args.workload, args.small)
+    d = make_workload(args.workload, args.small, args.shrink)
     try:
         run_ours(args, d, rank, world, local_rank)
     finally:

@@ -41,10 +41,13 @@ struct lapis_b200_csr {
   int64_t nrows, ncols, nnz, base;  // base = pos[0]
   const void *pos, *crd;
   const double *val;
-  // Streaming plan: thread block b of the SpMV kernel owns the rows whose start
-  // offset lies in [base + b*TILE, base + (b+1)*TILE); blk_row has nblk+1 entries.
+  // Streaming plan: thread block b of the SpMV kernel processes the stored entries
+  // [abase + b*TILE, abase + (b+1)*TILE), abase = base & ~1; blk_row[b] is the first row
+  // that ends inside that chunk (nblk+1 entries).  carry[b] receives the partial sum of
+  // the row that runs past chunk b.
   int64_t nblk;
   int64_t *blk_row;
+  double *carry;
   // Scratch for the fused dot product of the PCG SpMV pass (one double per block).
   double *blk_partial;
   int device;

@@ -5,54 +5,64 @@
 // mlir/lib/Target/KokkosCpp/TranslateToKokkosCpp.cpp:1966-2064 and :1692-1845):
 // one row per Kokkos thread with a vector length taken from the *average* row
 // length.  That shape streams val/crd uncoalesced for short rows and serialises
-// long ones.  Here the nonzeros are the unit of work instead:
+// long ones.  Here the stored entries are the unit of work instead:
 //
-//   * The nnz range is cut into tiles of SPMV_TILE entries.  Thread block b owns
-//     the rows whose start offset falls into tile b (found once per matrix by a
-//     binary-search kernel; 8 bytes of plan per block).  A block therefore
-//     streams ~SPMV_TILE consecutive (val, crd) pairs with 16-byte loads that are
-//     fully coalesced whatever the row lengths are, gathers x through the
-//     read-only path, and parks the products in shared memory.
-//   * The rows overlapping the tile are then reduced out of shared memory by
-//     groups of L lanes (L = 1..32 chosen per tile from its average row length)
-//     with warp shuffles.  A row longer than a tile is carried from tile to tile
-//     inside the block; no atomics, so results are run-to-run identical.
+//   * The entry range is cut into chunks of a fixed size T (2048 by default); thread
+//     block b processes exactly chunk b, so every block streams T consecutive
+//     (val, crd) pairs with aligned 16-byte loads that are fully coalesced whatever
+//     the row lengths are, gathers x through the read-only path, and parks the
+//     products in shared memory.  All in-chunk indexing is 32-bit.
+//   * A per-matrix plan (8 bytes per chunk, one binary search each) gives the first
+//     row that ends inside each chunk.  Rows that end in the chunk are reduced out
+//     of shared memory: rows of up to 32 entries by groups of L lanes (L = 1..8 from
+//     the chunk's average row length) with warp shuffles, longer rows by a whole warp
+//     in a second pass, so one long row among short ones does not serialise a thread.
+//   * A row that runs past the end of its chunk leaves its partial sum in carry[b];
+//     a tiny second kernel adds the carries to the row's y in chunk order.  No
+//     atomics on the data path: results are run-to-run identical.
 //
 // Arithmetic: products and sums use explicit round-to-nearest multiplies and adds
 // (no FMA contraction), as the emitted code has separate arith.mulf / arith.addf.
-// The summation order inside a row differs from the sequential CPU order when
-// L > 1 (documented tolerance 1e-12 of the row's magnitude); with L == 1 the
-// result is bit-identical to the sequential order.
+// The summation order inside a row differs from the sequential CPU order when more
+// than one lane or chunk takes part (documented tolerance 1e-12 of the row's
+// magnitude); a row summed by one lane inside one chunk is bit-identical to it.
+#include <cstdlib>
+
 #include "common.h"
 
 namespace lapis_b200 {
 
-constexpr int SPMV_THREADS = 256;
-constexpr int SPMV_TILE = 2048;       // nonzeros per tile (products staged in 16 KB of shared memory)
+constexpr int SPMV_TILE = 2048;       // stored entries per chunk == per thread block (part of the plan's meaning)
 constexpr int SPMV_POS_CACHE = 1024;  // row offsets staged per block; further rows read global memory
+constexpr int SPMV_LONG_ROW = 32;     // rows with more in-chunk entries than this are reduced by a whole warp
 
 // ---------------------------------------------------------------------------
-// Plan: blk_row[b] = first row r in [0, nrows] with pos[r] >= pos[0] + b*TILE.
+// Plan: plan[b] = first row r with pos[r+1] > abase + b*TILE (the row holding the
+// chunk's first entry), plan[0] = 0, plan[nblk] = nrows; abase = pos[0] & ~1.
 // ---------------------------------------------------------------------------
 template <typename I>
 __global__ void spmv_plan_kernel(const I *__restrict__ pos, int64_t nrows, int64_t nblk,
-                                 int64_t *__restrict__ blk_row) {
+                                 int64_t *__restrict__ plan) {
   int64_t b = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (b > nblk) return;
   if (b == nblk) {
-    blk_row[b] = nrows;
+    plan[b] = nrows;
     return;
   }
-  const int64_t target = (int64_t)pos[0] + b * (int64_t)SPMV_TILE;
+  if (b == 0) {
+    plan[0] = 0;
+    return;
+  }
+  const int64_t c0 = ((int64_t)pos[0] & ~(int64_t)1) + b * (int64_t)SPMV_TILE;
   int64_t lo = 0, hi = nrows;
   while (lo < hi) {
     int64_t mid = lo + ((hi - lo) >> 1);
-    if ((int64_t)pos[mid] < target)
-      lo = mid + 1;
-    else
+    if ((int64_t)pos[mid + 1] > c0)
       hi = mid;
+    else
+      lo = mid + 1;
   }
-  blk_row[b] = lo;
+  plan[b] = lo;
 }
 
 template <typename I>
@@ -82,169 +92,211 @@ __device__ __forceinline__ double block_sum(double v, double *s_red) {
   return t;  // valid in thread 0
 }
 
-// Reduces the rows [ra, rb] that overlap the current tile out of s_prod with L
-// lanes per row.  Returns this thread's contribution to the fused dot product.
-template <typename I, int L, bool FUSE_DOT>
-__device__ __forceinline__ double spmv_reduce_tile(
-    const I *__restrict__ pos, const I *s_pos, int64_t r0, int ncached, const double *s_prod,
-    int64_t ra, int64_t rb, int64_t tile_lo, int64_t tile_hi, double carry_in, double *carry_out,
-    double *__restrict__ y, int accumulate, const double *__restrict__ dotvec) {
+// x is re-read by every block: ask L2 to keep it (evict_last) while the streamed
+// val/crd entries, read once, are marked evict_first by ld.global.cs.
+__device__ __forceinline__ double load_x(const double *p, uint64_t policy, bool hint) {
+  if (!hint) return __ldg(p);
+  double v;
+  asm volatile("ld.global.nc.L2::cache_hint.f64 %0, [%1], %2;" : "=d"(v) : "l"(p), "l"(policy));
+  return v;
+}
+
+struct ChunkCtx {
+  int64_t row0;      // first row looked at by this block
+  int nr;            // rows looked at (the last one may only leave a carry)
+  int len;           // entries in the chunk
+  int ncached;       // entries of s_rel that are valid
+  bool has_tail;     // row row0 + nr - 1 runs past the chunk (or starts beyond it)
+  int64_t c0;
+};
+
+// Chunk-relative start offset of local row i, clamped to [0, len].
+template <typename I>
+__device__ __forceinline__ int rel_at(const ChunkCtx &c, const int *s_rel, const I *__restrict__ pos, int i) {
+  if (i < c.ncached) return s_rel[i];
+  int64_t d = (int64_t)pos[c.row0 + i] - c.c0;
+  d = d < 0 ? 0 : d;
+  return (int)(d > c.len ? c.len : d);
+}
+
+// Stores one finished in-chunk row sum: y for rows ending here, carry for the tail row.
+template <bool FUSE_DOT>
+__device__ __forceinline__ void finish_row(const ChunkCtx &c, int i, int s, double acc, double yin,
+                                           double *__restrict__ y, double *__restrict__ carry,
+                                           const double *__restrict__ dotvec, double &dot_local) {
+  const int64_t r = c.row0 + i;
+  if (c.has_tail && i == c.nr - 1) {
+    if (s >= c.len) return;  // the row starts beyond this chunk: not ours
+    carry[blockIdx.x] = acc;
+  } else {
+    y[r] = __dadd_rn(acc, yin);
+  }
+  if (FUSE_DOT) dot_local = __dadd_rn(dot_local, __dmul_rn(acc, dotvec[r]));
+}
+
+template <typename I, int THREADS, int L, bool FUSE_DOT>
+__device__ __forceinline__ void reduce_short_rows(const ChunkCtx &c, const int *s_rel, const I *__restrict__ pos,
+                                                  const double *s_prod, int *s_long, int *s_nlong,
+                                                  double *__restrict__ y, int accumulate, double *__restrict__ carry,
+                                                  const double *__restrict__ dotvec, double &dot_local) {
   const int tid = threadIdx.x;
   const int grp = tid / L, lane = tid % L;
-  constexpr int NGRP = SPMV_THREADS / L;
-  double dot_local = 0.0;
-  for (int64_t rbase = ra; rbase <= rb; rbase += NGRP) {
-    const int64_t r = rbase + grp;
-    const bool valid = r <= rb;
+  constexpr int NGRP = THREADS / L;
+  for (int ib = 0; ib < c.nr; ib += NGRP) {
+    const int i = ib + grp;
+    const bool valid = i < c.nr;
     double acc = 0.0, yin = 0.0;
-    int64_t s = 0, e = 0;
+    int s = 0, e = 0;
+    bool is_long = false;
     if (valid) {
-      const int64_t i = r - r0;
-      s = (i < ncached) ? (int64_t)s_pos[i] : (int64_t)pos[r];
-      e = (i + 1 < ncached) ? (int64_t)s_pos[i + 1] : (int64_t)pos[r + 1];
-      if (accumulate && lane == 0 && e <= tile_hi) yin = y[r];
-      const int64_t sc = s > tile_lo ? s : tile_lo;
-      const int64_t ec = e < tile_hi ? e : tile_hi;
-      const double *p = s_prod - tile_lo;
-#pragma unroll 4
-      for (int64_t j = sc + lane; j < ec; j += L) acc = __dadd_rn(acc, p[j]);
+      s = rel_at<I>(c, s_rel, pos, i);
+      e = rel_at<I>(c, s_rel, pos, i + 1);
+      is_long = (e - s) > SPMV_LONG_ROW;
+      if (accumulate && lane == 0 && !is_long && !(c.has_tail && i == c.nr - 1)) yin = y[c.row0 + i];
+      if (!is_long)
+        for (int j = s + lane; j < e; j += L) acc = __dadd_rn(acc, s_prod[j]);
     }
 #pragma unroll
     for (int off = L / 2; off > 0; off >>= 1) acc = __dadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, off));
     if (valid && lane == 0) {
-      if (s < tile_lo) acc = __dadd_rn(carry_in, acc);  // the row began in an earlier tile
-      if (e > tile_hi) {
-        *carry_out = acc;  // continues in the next tile (at most one such row per tile)
-      } else {
-        const double out = __dadd_rn(acc, yin);
-        y[r] = out;
-        if (FUSE_DOT) dot_local = __dadd_rn(dot_local, __dmul_rn(out, dotvec[r]));
-      }
+      if (is_long)
+        s_long[atomicAdd(s_nlong, 1)] = i;  // order of the list does not matter: rows are independent
+      else
+        finish_row<FUSE_DOT>(c, i, s, acc, yin, y, carry, dotvec, dot_local);
     }
   }
-  return dot_local;
 }
 
-// y = (accumulate ? y : 0) + A x.  With FUSE_DOT, blk_partial[b] receives this
-// block's part of sum_r y[r] * dotvec[r] (the p.Ap of a PCG iteration).
-template <typename I, bool FUSE_DOT>
-__global__ void __launch_bounds__(SPMV_THREADS, 4)
-spmv_stream_kernel(const I *__restrict__ pos, const I *__restrict__ crd, const double *__restrict__ val,
-                   const int64_t *__restrict__ blk_row, int64_t nnz_end, const double *__restrict__ x,
-                   double *__restrict__ y, int accumulate, const double *__restrict__ dotvec,
-                   double *__restrict__ blk_partial, const int *__restrict__ skip_flag) {
-  __shared__ __align__(16) double s_prod[SPMV_TILE];
-  __shared__ I s_pos[SPMV_POS_CACHE + 1];
-  __shared__ double s_carry[2];
-  __shared__ double s_red[SPMV_THREADS / 32];
+// y = (accumulate ? y : 0) + A x for the rows ending in chunk blockIdx.x; carry[b] for the row
+// running past it.  With FUSE_DOT, blk_partial[b] = sum over this chunk of (row partial) * dotvec[row].
+template <typename I, int THREADS, int MINB, bool FUSE_DOT, bool HINT>
+__global__ void __launch_bounds__(THREADS, MINB)
+spmv_chunk_kernel(const I *__restrict__ pos, const I *__restrict__ crd, const double *__restrict__ val,
+                  const int64_t *__restrict__ plan, int64_t abase, int64_t nnz_end, int64_t nrows,
+                  const double *__restrict__ x, double *__restrict__ y, int accumulate,
+                  double *__restrict__ carry, const double *__restrict__ dotvec,
+                  double *__restrict__ blk_partial, const int *__restrict__ skip_flag) {
+  constexpr int T = SPMV_TILE;
+  constexpr int PAIRS = T / (2 * THREADS);
+  __shared__ __align__(16) double s_prod[T];
+  __shared__ int s_rel[SPMV_POS_CACHE + 2];
+  __shared__ int s_long[T / SPMV_LONG_ROW];
+  __shared__ int s_nlong;
+  __shared__ double s_red[THREADS / 32];
   using Pair = typename IndexPair<I>::type;
 
   if (skip_flag != nullptr && *skip_flag != 0) return;
 
   const int tid = threadIdx.x;
-  const int64_t r0 = blk_row[blockIdx.x], r1 = blk_row[blockIdx.x + 1];
+  ChunkCtx c;
+  c.c0 = abase + (int64_t)blockIdx.x * T;
+  const int64_t left = nnz_end - c.c0;
+  c.len = (int)(left < T ? (left < 0 ? 0 : left) : T);
+  c.row0 = plan[blockIdx.x];
+  const int64_t rn = plan[blockIdx.x + 1];
+  c.has_tail = rn < nrows;
+  const int64_t nr64 = rn - c.row0 + (c.has_tail ? 1 : 0);
+  c.nr = (int)(nr64 > 0x7fffffff ? 0x7fffffff : nr64);
+  c.ncached = (int)(nr64 + 1 < SPMV_POS_CACHE + 2 ? nr64 + 1 : SPMV_POS_CACHE + 2);
+
+  uint64_t policy = 0;
+  if (HINT) asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(policy));
+
+  // ---- stream phase: aligned 16-byte loads, gather x, stage products ------------------
+  const double *vb = val + c.c0;
+  const I *cb = crd + c.c0;
+  double2 v[PAIRS];
+  Pair ci[PAIRS];
+#pragma unroll
+  for (int k = 0; k < PAIRS; ++k) {
+    const int j = 2 * (tid + k * THREADS);
+    v[k] = make_double2(0.0, 0.0);
+    ci[k].x = 0;
+    ci[k].y = 0;
+    if (j + 1 < c.len) {
+      v[k] = __ldcs(reinterpret_cast<const double2 *>(vb + j));
+      ci[k] = __ldcs(reinterpret_cast<const Pair *>(cb + j));
+    } else if (j < c.len) {  // odd tail of the last chunk
+      v[k].x = __ldcs(vb + j);
+      ci[k].x = __ldcs(cb + j);
+    }
+  }
+  // row offsets of this block, chunk-relative and clamped, while the loads are in flight
+  for (int i = tid; i < c.ncached; i += THREADS) {
+    int64_t d = (int64_t)pos[c.row0 + i] - c.c0;
+    d = d < 0 ? 0 : d;
+    s_rel[i] = (int)(d > c.len ? c.len : d);
+  }
+  if (tid == 0) s_nlong = 0;
+#pragma unroll
+  for (int k = 0; k < PAIRS; ++k) {
+    const int j = 2 * (tid + k * THREADS);
+    if (j < c.len) {
+      double2 p;
+      p.x = __dmul_rn(v[k].x, load_x(x + ci[k].x, policy, HINT));
+      p.y = (j + 1 < c.len) ? __dmul_rn(v[k].y, load_x(x + ci[k].y, policy, HINT)) : 0.0;
+      *reinterpret_cast<double2 *>(s_prod + j) = p;
+    }
+  }
+  __syncthreads();
+
+  // ---- pass 1: rows of up to SPMV_LONG_ROW in-chunk entries, L lanes per row --------
   double dot_local = 0.0;
-
-  if (r0 < r1) {
-    const int64_t nrows_b = r1 - r0;
-    const int ncached = (int)(nrows_b < SPMV_POS_CACHE ? nrows_b : SPMV_POS_CACHE) + 1;
-    for (int i = tid; i < ncached; i += SPMV_THREADS) s_pos[i] = pos[r0 + i];
-    const int64_t lo = (int64_t)pos[r0], hi = (int64_t)pos[r1];
-
-    int64_t tile_lo = lo & ~(int64_t)1;  // even offset: 16-byte aligned val/crd pairs
-    int64_t ra = r0;                     // first row that can overlap the current tile
-    int parity = 0;
-    if (tid == 0) s_carry[0] = 0.0;
-    do {
-      const bool last = tile_lo + SPMV_TILE >= hi;
-      const int64_t tile_hi = last ? hi : tile_lo + SPMV_TILE;
-
-      // ---- stream phase: coalesced 16-byte loads, gather x, stage products --------
-      double2 v[SPMV_TILE / (2 * SPMV_THREADS)];
-      Pair c[SPMV_TILE / (2 * SPMV_THREADS)];
-#pragma unroll
-      for (int k = 0; k < SPMV_TILE / (2 * SPMV_THREADS); ++k) {
-        const int64_t j = tile_lo + 2 * (int64_t)(tid + k * SPMV_THREADS);
-        v[k] = make_double2(0.0, 0.0);
-        c[k].x = 0;
-        c[k].y = 0;
-        if (j < tile_hi) {
-          if (j + 1 < nnz_end) {
-            v[k] = __ldcs(reinterpret_cast<const double2 *>(val + j));
-            c[k] = __ldcs(reinterpret_cast<const Pair *>(crd + j));
-          } else {  // the very last entry of the arrays
-            v[k].x = __ldcs(val + j);
-            c[k].x = __ldcs(crd + j);
-          }
-        }
-      }
-#pragma unroll
-      for (int k = 0; k < SPMV_TILE / (2 * SPMV_THREADS); ++k) {
-        const int64_t j = tile_lo + 2 * (int64_t)(tid + k * SPMV_THREADS);
-        if (j < tile_hi) {
-          double2 p;
-          p.x = __dmul_rn(v[k].x, __ldg(x + c[k].x));
-          p.y = __dmul_rn(v[k].y, __ldg(x + c[k].y));
-          *reinterpret_cast<double2 *>(s_prod + (j - tile_lo)) = p;
-        }
-      }
-      __syncthreads();  // products and s_pos visible
-
-      // ---- rows overlapping this tile ----------------------------------------------
-      int64_t rb;
-      if (last) {
-        rb = r1 - 1;
-      } else {  // last row whose start offset is below tile_hi
-        int64_t a = ra, b = r1;
-        while (a < b) {
-          const int64_t mid = a + ((b - a) >> 1);
-          const int64_t i = mid - r0;
-          const int64_t pm = (i < ncached) ? (int64_t)s_pos[i] : (int64_t)pos[mid];
-          if (pm < tile_hi)
-            a = mid + 1;
-          else
-            b = mid;
-        }
-        rb = a - 1;
-      }
-      const int64_t nrows_t = rb - ra + 1;
-      const int64_t avg = (tile_hi - tile_lo) / (nrows_t > 0 ? nrows_t : 1);
-      const double carry_in = s_carry[parity];
-      double *carry_out = &s_carry[parity ^ 1];
-#define LAPIS_REDUCE(LANES)                                                                          \
-  dot_local = __dadd_rn(dot_local, spmv_reduce_tile<I, LANES, FUSE_DOT>(                             \
-                                       pos, s_pos, r0, ncached, s_prod, ra, rb, tile_lo, tile_hi,    \
-                                       carry_in, carry_out, y, accumulate, dotvec))
-      if (avg <= 2)
-        LAPIS_REDUCE(1);
-      else if (avg <= 4)
-        LAPIS_REDUCE(2);
-      else if (avg <= 8)
-        LAPIS_REDUCE(4);
-      else if (avg <= 16)
-        LAPIS_REDUCE(8);
-      else if (avg <= 32)
-        LAPIS_REDUCE(16);
-      else
-        LAPIS_REDUCE(32);
+  const int avg = c.len / (c.nr > 0 ? c.nr : 1);
+#define LAPIS_REDUCE(LANES)                                                                                   \
+  reduce_short_rows<I, THREADS, LANES, FUSE_DOT>(c, s_rel, pos, s_prod, s_long, &s_nlong, y, accumulate, carry, \
+                                                 dotvec, dot_local)
+  if (avg <= 4)
+    LAPIS_REDUCE(1);
+  else if (avg <= 8)
+    LAPIS_REDUCE(2);
+  else if (avg <= 16)
+    LAPIS_REDUCE(4);
+  else
+    LAPIS_REDUCE(8);
 #undef LAPIS_REDUCE
-      if (!last) {
-        // the row that crosses tile_hi (if any) is reduced again in the next tile
-        const int64_t i = rb + 1 - r0;
-        const int64_t e = (i < ncached) ? (int64_t)s_pos[i] : (int64_t)pos[rb + 1];
-        ra = e > tile_hi ? rb : rb + 1;
-      }
-      parity ^= 1;
-      tile_lo += SPMV_TILE;
-      __syncthreads();  // s_prod is overwritten by the next tile; carry_out visible
-      if (last) break;
-    } while (true);
+  __syncthreads();
+
+  // ---- pass 2: long rows, one warp each -------------------------------------------------
+  const int nlong = s_nlong;
+  const int warp = tid >> 5, lane = tid & 31;
+  for (int q = warp; q < nlong; q += THREADS / 32) {
+    const int i = s_long[q];
+    const int s = rel_at<I>(c, s_rel, pos, i), e = rel_at<I>(c, s_rel, pos, i + 1);
+    double yin = 0.0;
+    if (accumulate && lane == 0 && !(c.has_tail && i == c.nr - 1)) yin = y[c.row0 + i];
+    double acc = 0.0;
+    for (int j = s + lane; j < e; j += 32) acc = __dadd_rn(acc, s_prod[j]);
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) acc = __dadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, off));
+    if (lane == 0) finish_row<FUSE_DOT>(c, i, s, acc, yin, y, carry, dotvec, dot_local);
   }
 
   if (FUSE_DOT) {
     const double t = block_sum(dot_local, s_red);
     if (tid == 0) blk_partial[blockIdx.x] = t;
   }
+}
+
+// Adds the carries to their rows.  Chunk b left a carry iff row q = plan[b+1] exists and starts
+// before the chunk's end; consecutive chunks carrying into the same row form a run that the
+// thread of its first chunk adds up in chunk order.
+template <typename I>
+__global__ void spmv_fixup_kernel(const I *__restrict__ pos, const int64_t *__restrict__ plan, int64_t abase,
+                                  int64_t nblk, int64_t nrows, const double *__restrict__ carry,
+                                  double *__restrict__ y, const int *__restrict__ skip_flag) {
+  if (skip_flag != nullptr && *skip_flag != 0) return;
+  const int64_t b = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= nblk - 1) return;
+  const int64_t q = plan[b + 1];
+  if (q >= nrows) return;
+  const int64_t start = (int64_t)pos[q];
+  const int64_t c0 = abase + b * (int64_t)SPMV_TILE;
+  if (start >= c0 + SPMV_TILE) return;             // row q starts in a later chunk: nothing carried
+  if (b > 0 && plan[b] == q && start < c0) return;  // chunk b-1 carried into q too: not the head of the run
+  double acc = carry[b];
+  for (int64_t b2 = b + 1; b2 < nblk - 1 && plan[b2 + 1] == q; ++b2) acc = __dadd_rn(acc, carry[b2]);
+  y[q] = __dadd_rn(y[q], acc);
 }
 
 // ---------------------------------------------------------------------------
@@ -334,20 +386,67 @@ spmm_row_kernel(const I *__restrict__ pos, const I *__restrict__ crd, const doub
 // ---------------------------------------------------------------------------
 // Host side
 // ---------------------------------------------------------------------------
+// Kernel variant used by spmv_launch: "threads,minblocks,hint" from LAPIS_B200_SPMV (tuning aid).
+struct SpmvVariant {
+  int threads, minb, hint;
+};
+static SpmvVariant spmv_variant() {
+  static SpmvVariant v = [] {
+    SpmvVariant d{256, 4, 1};
+    if (const char *e = std::getenv("LAPIS_B200_SPMV")) {
+      int t = 0, m = 0, h = 0;
+      if (sscanf(e, "%d,%d,%d", &t, &m, &h) == 3) d = SpmvVariant{t, m, h};
+    }
+    return d;
+  }();
+  return v;
+}
+
+template <typename I, int THREADS, int MINB, bool HINT>
+static void launch_chunks(const lapis_b200_csr *h, const double *x, double *y, int accumulate, const double *dotvec,
+                          double *blk_partial, const int *skip_flag, cudaStream_t st) {
+  const I *pos = static_cast<const I *>(h->pos);
+  const I *crd = static_cast<const I *>(h->crd);
+  const int64_t abase = h->base & ~(int64_t)1, nnz_end = h->base + h->nnz;
+  if (dotvec != nullptr)
+    spmv_chunk_kernel<I, THREADS, MINB, true, HINT><<<(unsigned)h->nblk, THREADS, 0, st>>>(
+        pos, crd, h->val, h->blk_row, abase, nnz_end, h->nrows, x, y, accumulate, h->carry, dotvec, blk_partial,
+        skip_flag);
+  else
+    spmv_chunk_kernel<I, THREADS, MINB, false, HINT><<<(unsigned)h->nblk, THREADS, 0, st>>>(
+        pos, crd, h->val, h->blk_row, abase, nnz_end, h->nrows, x, y, accumulate, h->carry, nullptr, nullptr,
+        skip_flag);
+}
+
 template <typename I>
 static int launch_spmv(const lapis_b200_csr *h, const double *x, double *y, int accumulate,
                        const double *dotvec, double *blk_partial, const int *skip_flag,
                        cudaStream_t st) {
-  const I *pos = static_cast<const I *>(h->pos);
-  const I *crd = static_cast<const I *>(h->crd);
-  const int64_t nnz_end = h->base + h->nnz;
-  if (dotvec != nullptr)
-    spmv_stream_kernel<I, true><<<(unsigned)h->nblk, SPMV_THREADS, 0, st>>>(
-        pos, crd, h->val, h->blk_row, nnz_end, x, y, accumulate, dotvec, blk_partial, skip_flag);
-  else
-    spmv_stream_kernel<I, false><<<(unsigned)h->nblk, SPMV_THREADS, 0, st>>>(
-        pos, crd, h->val, h->blk_row, nnz_end, x, y, accumulate, nullptr, nullptr, skip_flag);
+  const SpmvVariant v = spmv_variant();
+#define LAPIS_V(T, M)                                                                                     \
+  if (v.threads == T && v.minb == M) {                                                                    \
+    if (v.hint)                                                                                           \
+      launch_chunks<I, T, M, true>(h, x, y, accumulate, dotvec, blk_partial, skip_flag, st);              \
+    else                                                                                                  \
+      launch_chunks<I, T, M, false>(h, x, y, accumulate, dotvec, blk_partial, skip_flag, st);             \
+  } else
+  LAPIS_V(256, 6)
+  LAPIS_V(256, 4)
+  LAPIS_V(256, 8)
+  LAPIS_V(128, 8)
+  LAPIS_V(128, 12)
+  LAPIS_V(512, 3)
+  LAPIS_V(512, 4)
+  LAPIS_V(1024, 2)
+  { return fail(LAPIS_EBADARG, "LAPIS_B200_SPMV names an unknown kernel variant"); }
+#undef LAPIS_V
   LAPIS_CUDA_TRY(cudaGetLastError());
+  if (h->nblk > 1) {
+    const I *pos = static_cast<const I *>(h->pos);
+    spmv_fixup_kernel<I><<<(unsigned)((h->nblk - 1 + 255) / 256), 256, 0, st>>>(
+        pos, h->blk_row, h->base & ~(int64_t)1, h->nblk, h->nrows, h->carry, y, skip_flag);
+    LAPIS_CUDA_TRY(cudaGetLastError());
+  }
   return LAPIS_OK;
 }
 
@@ -412,9 +511,9 @@ extern "C" int lapis_b200_csr_create(lapis_b200_csr_t *out, int idx_bytes, int64
   if (ends[1] < ends[0] || ends[0] < 0) return fail(LAPIS_EBADSHAPE, "csr_create: pos is not non-decreasing");
   const int64_t nnz = ends[1] - ends[0];
   if (nnz > 0 && (d_crd == nullptr || d_val == nullptr)) return fail(LAPIS_EBADARG, "csr_create: crd/val null");
-  int64_t nblk = (nnz + SPMV_TILE - 1) / SPMV_TILE;
+  int64_t nblk = (ends[1] - (ends[0] & ~(int64_t)1) + SPMV_TILE - 1) / SPMV_TILE;
   if (nblk < 1) nblk = 1;
-  if (nblk > 0x7fffffffLL) return fail(LAPIS_ETOOBIG, "csr_create: more than 2^31 tiles");
+  if (nblk > 0x7fffffffLL) return fail(LAPIS_ETOOBIG, "csr_create: more than 2^31 chunks");
 
   lapis_b200_csr *h = new lapis_b200_csr();
   h->idx_bytes = idx_bytes;
@@ -428,11 +527,14 @@ extern "C" int lapis_b200_csr_create(lapis_b200_csr_t *out, int idx_bytes, int64
   h->nblk = nblk;
   h->blk_row = nullptr;
   h->blk_partial = nullptr;
+  h->carry = nullptr;
   h->device = dev;
   cudaError_t e = cudaMalloc(&h->blk_row, (size_t)(nblk + 1) * sizeof(int64_t));
   if (e == cudaSuccess) e = cudaMalloc(&h->blk_partial, (size_t)nblk * sizeof(double));
+  if (e == cudaSuccess) e = cudaMalloc(&h->carry, (size_t)nblk * sizeof(double));
   if (e != cudaSuccess) {
     cudaFree(h->blk_row);
+    cudaFree(h->blk_partial);
     delete h;
     return fail(LAPIS_ECUDA, "csr_create: cudaMalloc failed: %s", cudaGetErrorString(e));
   }
@@ -445,6 +547,7 @@ extern "C" int lapis_b200_csr_create(lapis_b200_csr_t *out, int idx_bytes, int64
   if (e != cudaSuccess) {
     cudaFree(h->blk_row);
     cudaFree(h->blk_partial);
+    cudaFree(h->carry);
     delete h;
     return fail(LAPIS_ECUDA, "csr_create: plan kernel launch failed: %s", cudaGetErrorString(e));
   }
@@ -457,6 +560,7 @@ extern "C" int lapis_b200_csr_destroy(lapis_b200_csr_t h) {
   if (h == nullptr) return LAPIS_OK;
   cudaFree(h->blk_row);
   cudaFree(h->blk_partial);
+  cudaFree(h->carry);
   delete h;
   return LAPIS_OK;
 }
@@ -497,8 +601,9 @@ extern "C" int lapis_b200_spmm_f64(lapis_b200_csr_t h, int64_t k, const double *
 // entries it uses (nothing needs to start at zero), and two calls in flight on the
 // same device at the same time would overwrite each other's plan.
 // ---------------------------------------------------------------------------
-constexpr int64_t NOALLOC_MAX_TILES = 1 << 18;  // 2 MiB of plan: matrices of up to 2^29 stored entries
-static __device__ __align__(256) int64_t g_noalloc_plan[NOALLOC_MAX_TILES + 1];
+constexpr int64_t NOALLOC_MAX_TILES = 1 << 18;  // matrices of up to 2^29 stored entries
+// [0, MAX]: the plan (int64); (MAX, 2*MAX]: the per-chunk carries (doubles, same width).  4 MiB.
+static __device__ __align__(256) int64_t g_noalloc_plan[2 * NOALLOC_MAX_TILES + 1];
 
 // Device address of g_noalloc_plan per device.  In host code the array's name is only a
 // handle for the runtime, not an address a kernel may use; cudaGetSymbolAddress returns the
@@ -551,13 +656,13 @@ extern "C" int lapis_b200_spmv_f64_noalloc(int idx_bytes, int64_t nrows, int64_t
   const int64_t nnz = ends[1] - ends[0];
   if (nnz > 0 && (d_crd == nullptr || d_val == nullptr || d_x == nullptr))
     return fail(LAPIS_EBADARG, "spmv_noalloc: crd/val/x null");
-  int64_t nblk = (nnz + SPMV_TILE - 1) / SPMV_TILE;
+  int64_t nblk = (ends[1] - (ends[0] & ~(int64_t)1) + SPMV_TILE - 1) / SPMV_TILE;
   if (nblk < 1) nblk = 1;
   if (nblk > NOALLOC_MAX_TILES)
     return fail(LAPIS_ETOOBIG,
                 "spmv_noalloc: %lld stored entries exceed the fixed plan buffer (limit %lld entries); "
                 "use lapis_b200_csr_create + lapis_b200_spmv_f64 for larger matrices",
-                (long long)nnz, (long long)(NOALLOC_MAX_TILES * (int64_t)SPMV_TILE));
+                (long long)nnz, (long long)(NOALLOC_MAX_TILES * (int64_t)SPMV_TILE - 1));
 
   lapis_b200_csr h;
   h.idx_bytes = idx_bytes;
@@ -571,6 +676,7 @@ extern "C" int lapis_b200_spmv_f64_noalloc(int idx_bytes, int64_t nrows, int64_t
   h.nblk = nblk;
   h.blk_row = plan;
   h.blk_partial = nullptr;
+  h.carry = reinterpret_cast<double *>(plan + NOALLOC_MAX_TILES + 1);
   h.device = 0;
   const unsigned pgrid = (unsigned)((nblk + 1 + 255) / 256);
   if (idx_bytes == 4)
