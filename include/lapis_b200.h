@@ -156,6 +156,12 @@ int lapis_b200_spmm_f64(lapis_b200_csr_t h, int64_t k, const double *d_B, double
 int lapis_b200_bgemm_f32(int64_t batch, int64_t M, int64_t N, int64_t K, const float *d_A, const float *d_B,
                          float *d_C, void *stream);
 
+/* Tile-aligned problems (M, N multiples of 128, K of 32) run on the tensor cores, whose kernel
+ * bounds every internal wait and records a flag instead of hanging.  This reads and clears
+ * that flag after synchronising `stream`: LAPIS_OK, or LAPIS_ECUDA when the last launches on
+ * this device did not complete normally (their output is then invalid). */
+int lapis_b200_bgemm_status(void *stream);
+
 /* Vector kernels of examples/pcg_solve.py:22-48.  dot writes its result to *d_out. */
 int lapis_b200_dot_f64(int64_t n, const double *d_x, const double *d_y, double *d_out, void *stream);
 int lapis_b200_axpby_f64(int64_t n, double a, const double *d_x, double b, const double *d_y, double *d_dst,

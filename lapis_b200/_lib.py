@@ -40,6 +40,7 @@ _PROTOS = {
     "lapis_b200_spmv_f64_noalloc": (c_int, [c_int, c_i64, c_i64, c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_vp]),
     "lapis_b200_spmm_f64": (c_int, [c_vp, c_i64, c_vp, c_vp, c_int, c_vp]),
     "lapis_b200_bgemm_f32": (c_int, [c_i64, c_i64, c_i64, c_i64, c_vp, c_vp, c_vp, c_vp]),
+    "lapis_b200_bgemm_status": (c_int, [c_vp]),
     "lapis_b200_dot_f64": (c_int, [c_i64, c_vp, c_vp, c_vp, c_vp]),
     "lapis_b200_axpby_f64": (c_int, [c_i64, c_dbl, c_vp, c_dbl, c_vp, c_vp, c_vp]),
     "lapis_b200_mult_f64": (c_int, [c_i64, c_vp, c_vp, c_vp, c_vp]),

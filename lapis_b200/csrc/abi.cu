@@ -209,6 +209,7 @@ static int gemm_host(int64_t batch, int64_t M, int64_t N, int64_t K, const float
   LAPIS_CUDA_TRY(cudaMemcpyAsync(dC.p, C, bC, cudaMemcpyHostToDevice, st));
   LAPIS_TRY(lapis_b200_bgemm_f32(batch, M, N, K, static_cast<const float *>(dA.p), static_cast<const float *>(dB.p),
                                  static_cast<float *>(dC.p), st));
+  LAPIS_TRY(lapis_b200_bgemm_status(st));
   LAPIS_CUDA_TRY(cudaMemcpyAsync(C, dC.p, bC, cudaMemcpyDeviceToHost, st));
   LAPIS_CUDA_TRY(cudaStreamSynchronize(st));
   return LAPIS_OK;

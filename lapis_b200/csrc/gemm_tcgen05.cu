@@ -1,13 +1,392 @@
-// tcgen05 / TMEM fp32 matmul (3xTF32).  Placeholder until the kernel lands: no shape
-// is claimed, so every problem takes the general-shape kernel in gemm.cu.
+// fp32 matmul on the 5th-generation tensor cores (tcgen05 + TMEM), fp32 emulated with
+// three TF32 products:  C[b] = C_in[b] + A[b] B[b]  for tile-aligned shapes.
+//
+// The emitted loop nest (tests/Dialect/Kokkos/linalg_to_loops_3.mlir.gold:6-20) does one
+// output element per Kokkos thread with no reuse.  Here one CTA owns a 128 x 128 tile of C,
+// accumulated in tensor memory (128 lanes x 128 fp32 columns), and walks K in blocks of 32:
+//
+//   warp 0      TMA producer: cp.async.bulk.tensor loads of the A block (128 x 32, K-major,
+//               128-byte swizzle) and the B block (32 x 128, N-major, as four 32 x 32 boxes,
+//               128-byte swizzle with 32-byte atoms) into a 3-stage shared-memory ring,
+//               completion on an mbarrier.
+//   warps 2-5   split: x = hi + lo with hi = the TF32 the tensor core reads from the raw
+//               fp32 (its top 19 bits) and lo = x - hi (exact), written to a second pair of
+//               buffers; fence.proxy.async, then arrive.
+//   warp 1      MMA issuer: per 8-wide k step three tcgen05.mma.kind::tf32 into the same
+//               accumulator: hi*hi + lo*hi + hi*lo (the lo*lo term is below fp32 rounding);
+//               tcgen05.commit releases the stage to the producer.
+//   warps 2-5   epilogue: tcgen05.ld the accumulator, add C_in, store C.
+//
+// Every mbarrier wait is bounded: after WAIT_LIMIT polls the thread records an error code
+// in a global flag and stops waiting, the block still frees its tensor memory and exits,
+// and the host turns the flag into LAPIS_ECUDA.
+#include <cuda.h>
+
 #include "common.h"
 
 namespace lapis_b200 {
 
-int bgemm_tcgen05_supported(int64_t, int64_t, int64_t, int64_t) { return 0; }
+namespace tc {
 
-int bgemm_tcgen05_launch(int64_t, int64_t, int64_t, int64_t, const float *, const float *, float *, cudaStream_t) {
-  return fail(LAPIS_EBADSHAPE, "bgemm: tcgen05 path not available for this shape");
+constexpr int BM = 128, BN = 128, BK = 32, STAGES = 3;
+constexpr int A_BYTES = BM * BK * 4;       // 16 KB, rows of 128 B
+constexpr int B_BYTES = BK * BN * 4;       // 16 KB, four boxes of 32 k-rows x 128 B
+constexpr int BOX_BYTES = BK * 32 * 4;     // one B box: 32 k-rows x 32 columns
+constexpr int STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES;
+constexpr int THREADS = 192;
+constexpr uint32_t WAIT_LIMIT = 1u << 22;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+
+// instruction descriptor: D = f32, A = B = tf32, A K-major, B MN-major, N = 128, M = 128
+constexpr uint32_t IDESC = (1u << 4) | (2u << 7) | (2u << 10) | (0u << 15) | (1u << 16) |
+                           ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// Bounded wait: false when the phase did not complete within WAIT_LIMIT polls.
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
+  const uint32_t addr = smem_u32(bar);
+  for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(addr), "r"(parity)
+        : "memory");
+    if (done) return true;
+  }
+  return false;
+}
+
+__device__ __forceinline__ void tma_load_3d(void *dst, const CUtensorMap *map, uint64_t *bar, int x, int y, int z) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z)
+      : "memory");
+}
+
+// K-major operand, 128-byte swizzle: rows 128 B apart, 8-row groups 1024 B apart.
+__device__ __forceinline__ uint64_t desc_kmajor(uint32_t saddr) {
+  return (uint64_t)((saddr >> 4) & 0x3FFF) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+// MN-major 32-bit operand: the only layout the tensor core accepts is the 128-byte swizzle with
+// 32-byte atoms (layout type 1; TMA mode SWIZZLE_128B_ATOM_32B): 32-column blocks BOX_BYTES
+// apart (leading offset), groups of 4 k-rows 512 B apart (stride offset).
+__device__ __forceinline__ uint64_t desc_mnmajor(uint32_t saddr) {
+  return (uint64_t)((saddr >> 4) & 0x3FFF) | ((uint64_t)(BOX_BYTES >> 4) << 16) | (32ull << 32) | (1ull << 46) |
+         (1ull << 61);
+}
+
+__device__ __forceinline__ void mma_tf32(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
+      ::"r"(tmem_d), "l"(da), "l"(db), "r"(IDESC), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
+      : "memory");
+}
+
+__device__ __forceinline__ void split_tf32(float4 &hi_lo_in_out, float4 &lo) {
+  float4 x = hi_lo_in_out;
+  lo.x = x.x - __uint_as_float(__float_as_uint(x.x) & 0xFFFFE000u);
+  lo.y = x.y - __uint_as_float(__float_as_uint(x.y) & 0xFFFFE000u);
+  lo.z = x.z - __uint_as_float(__float_as_uint(x.z) & 0xFFFFE000u);
+  lo.w = x.w - __uint_as_float(__float_as_uint(x.w) & 0xFFFFE000u);
+}
+
+#ifdef LAPIS_TC_DEBUG
+__device__ float g_tc_dbg[4096];
+__device__ int g_tc_mode;
+__device__ __forceinline__ void mma_tf32_idesc(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
+      ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
+      : "memory");
+}
+#endif
+
+__global__ void __launch_bounds__(THREADS, 1)
+bgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                     float *__restrict__ C, int M, int N, int K, int *__restrict__ error_flag) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint64_t *bars = reinterpret_cast<uint64_t *>(smem + STAGES * STAGE_BYTES);
+  uint64_t *full = bars, *conv = bars + STAGES, *empty = bars + 2 * STAGES, *accum = bars + 3 * STAGES;
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 3 * STAGES + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = blockIdx.x * BN, m0 = blockIdx.y * BM, batch = blockIdx.z;
+  const int nk = K / BK;
+
+  auto stage_a = [&](int s) { return smem + s * STAGE_BYTES; };
+  auto stage_alo = [&](int s) { return smem + s * STAGE_BYTES + A_BYTES; };
+  auto stage_b = [&](int s) { return smem + s * STAGE_BYTES + 2 * A_BYTES; };
+  auto stage_blo = [&](int s) { return smem + s * STAGE_BYTES + 2 * A_BYTES + B_BYTES; };
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&conv[s], 128);
+      mbar_init(&empty[s], 1);
+    }
+    mbar_init(accum, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {  // tensor memory: 128 columns of fp32 accumulators
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(128u)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      for (int kb = 0; kb < nk; ++kb) {
+        const int s = kb % STAGES;
+        if (!mbar_wait(&empty[s], ((kb / STAGES) & 1) ^ 1)) {
+          atomicExch(error_flag, 1);
+          break;
+        }
+        mbar_expect_tx(&full[s], A_BYTES + B_BYTES);
+        tma_load_3d(stage_a(s), &map_a, &full[s], kb * BK, m0, batch);
+#pragma unroll
+        for (int j = 0; j < BN / 32; ++j)
+          tma_load_3d(stage_b(s) + j * BOX_BYTES, &map_b, &full[s], n0 + 32 * j, kb * BK, batch);
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      bool ok = true;
+      for (int kb = 0; kb < nk && ok; ++kb) {
+        const int s = kb % STAGES;
+        ok = mbar_wait(&conv[s], (kb / STAGES) & 1);
+        if (!ok) {
+          atomicExch(error_flag, 2);
+          break;
+        }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t a = smem_u32(stage_a(s)), alo = smem_u32(stage_alo(s));
+        const uint32_t b = smem_u32(stage_b(s)), blo = smem_u32(stage_blo(s));
+#ifdef LAPIS_TC_DEBUG
+        if (g_tc_mode == 1) {  // D = A A^T, both operands K-major
+          const uint32_t idesc_kk = IDESC & ~(1u << 16);
+          for (int ks = 0; ks < BK / 8; ++ks)
+            mma_tf32_idesc(tmem_base, desc_kmajor(a + ks * 32), desc_kmajor(a + ks * 32), idesc_kk, (kb > 0 || ks > 0) ? 1u : 0u);
+        } else if (g_tc_mode == 2) {  // only hi*hi
+          for (int ks = 0; ks < BK / 8; ++ks)
+            mma_tf32(tmem_base, desc_kmajor(a + ks * 32), desc_mnmajor(b + ks * 1024), (kb > 0 || ks > 0) ? 1u : 0u);
+        } else
+#endif
+#pragma unroll
+        for (int ks = 0; ks < BK / 8; ++ks) {
+          const uint64_t da = desc_kmajor(a + ks * 32), dalo = desc_kmajor(alo + ks * 32);
+          const uint64_t db = desc_mnmajor(b + ks * 1024), dblo = desc_mnmajor(blo + ks * 1024);
+          mma_tf32(tmem_base, dalo, db, (kb > 0 || ks > 0) ? 1u : 0u);
+          mma_tf32(tmem_base, da, dblo, 1u);
+          mma_tf32(tmem_base, da, db, 1u);
+        }
+        // releases the stage once the MMAs above have read it
+        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(&empty[s]))
+                     : "memory");
+      }
+      asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(accum))
+                   : "memory");
+    }
+  } else {
+    // ---------------- split (hi, lo), then epilogue ----------------
+    const int t = threadIdx.x - 64;  // 0..127
+    bool ok = true;
+    for (int kb = 0; kb < nk && ok; ++kb) {
+      const int s = kb % STAGES;
+      ok = mbar_wait(&full[s], (kb / STAGES) & 1);
+      if (!ok) {
+        atomicExch(error_flag, 3);
+        break;
+      }
+      const float4 *a = reinterpret_cast<const float4 *>(stage_a(s));
+      float4 *alo = reinterpret_cast<float4 *>(stage_alo(s));
+      const float4 *b = reinterpret_cast<const float4 *>(stage_b(s));
+      float4 *blo = reinterpret_cast<float4 *>(stage_blo(s));
+#pragma unroll
+      for (int i = 0; i < A_BYTES / 16 / 128; ++i) {
+        float4 x = a[t + 128 * i], lo;
+        split_tf32(x, lo);
+        alo[t + 128 * i] = lo;
+      }
+#pragma unroll
+      for (int i = 0; i < B_BYTES / 16 / 128; ++i) {
+        float4 x = b[t + 128 * i], lo;
+        split_tf32(x, lo);
+        blo[t + 128 * i] = lo;
+      }
+#ifdef LAPIS_TC_DEBUG
+      if (kb == 0 && blockIdx.x == 0 && blockIdx.y == 0) {
+        const float *af = reinterpret_cast<const float *>(stage_a(s));
+        const float *bf = reinterpret_cast<const float *>(stage_b(s));
+        for (int i = t; i < 1024; i += 128) {
+          g_tc_dbg[1024 + i] = af[i];
+          g_tc_dbg[2048 + i] = bf[i];
+        }
+        if (t == 0) g_tc_dbg[0] = __uint_as_float(tmem_base);
+      }
+#endif
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> tensor-core reads
+      mbar_arrive(&conv[s]);
+    }
+    // epilogue: accumulator row = TMEM lane; this warp may touch lanes 32*(warp%4)..+31
+    if (ok) ok = mbar_wait(accum, 0);
+    if (!ok) atomicExch(error_flag, 4);
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    if (ok) {
+      const int q = warp & 3;
+      const int row = m0 + 32 * q + lane;
+      float *crow = C + ((size_t)batch * M + row) * (size_t)N + n0;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        const uint32_t taddr = tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)(32 * c);
+        asm volatile(
+            "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+            "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+            "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+            : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+              "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+              "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+              "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+            : "r"(taddr));
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#ifdef LAPIS_TC_DEBUG
+        if (t == 0 && c == 0 && blockIdx.x == 0 && blockIdx.y == 0)
+          for (int i = 0; i < 32; ++i) g_tc_dbg[32 + i] = __uint_as_float(r[i]);
+#endif
+        float4 *dst = reinterpret_cast<float4 *>(crow + 32 * c);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          float4 cin = dst[i];
+          cin.x = __fadd_rn(__uint_as_float(r[4 * i + 0]), cin.x);
+          cin.y = __fadd_rn(__uint_as_float(r[4 * i + 1]), cin.y);
+          cin.z = __fadd_rn(__uint_as_float(r[4 * i + 2]), cin.z);
+          cin.w = __fadd_rn(__uint_as_float(r[4 * i + 3]), cin.w);
+          dst[i] = cin;
+        }
+      }
+    }
+  }
+
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(128u) : "memory");
+  }
+}
+
+// ---- host side ------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = [] {
+    void *p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    // resolved through the runtime so that the library does not link libcuda directly
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      p = nullptr;
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  return fn;
+}
+
+// Row-major [batch][rows][cols] fp32 tensor, box = box_rows x 32 columns (128 bytes), swizzled.
+static int make_map(CUtensorMap *map, const float *base, int64_t batch, int64_t rows, int64_t cols, int box_rows,
+                    CUtensorMapSwizzle swizzle) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) return fail(LAPIS_ECUDA, "bgemm: cuTensorMapEncodeTiled is not available from the driver");
+  cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)rows, (cuuint64_t)batch};
+  cuuint64_t strides[2] = {(cuuint64_t)cols * 4, (cuuint64_t)cols * rows * 4};
+  cuuint32_t box[3] = {32, (cuuint32_t)box_rows, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float *>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(LAPIS_ECUDA, "bgemm: cuTensorMapEncodeTiled failed with code %d", (int)r);
+  return LAPIS_OK;
+}
+
+}  // namespace tc
+
+static int *error_flag[64] = {nullptr};
+static bool attr_set[64] = {false};
+
+int bgemm_tcgen05_supported(int64_t batch, int64_t M, int64_t N, int64_t K) {
+  return batch >= 1 && batch <= 65535 && M >= tc::BM && N >= tc::BN && K >= tc::BK && M % tc::BM == 0 &&
+         N % tc::BN == 0 && K % tc::BK == 0 && M <= (1 << 30) && N <= (1 << 30) && K <= (1 << 30) &&
+         M / tc::BM <= 65535;
+}
+
+int bgemm_tcgen05_launch(int64_t batch, int64_t M, int64_t N, int64_t K, const float *A, const float *B, float *C,
+                         cudaStream_t st) {
+  if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) % 16)
+    return fail(LAPIS_EBADARG, "bgemm: operands must be 16-byte aligned");
+  CUtensorMap map_a, map_b;
+  LAPIS_TRY(tc::make_map(&map_a, A, batch, M, K, tc::BM, CU_TENSOR_MAP_SWIZZLE_128B));
+  LAPIS_TRY(tc::make_map(&map_b, B, batch, K, N, tc::BK, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B));
+  int dev = 0;
+  LAPIS_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return fail(LAPIS_EBADARG, "bgemm: device index %d not supported", dev);
+  if (error_flag[dev] == nullptr) {
+    LAPIS_CUDA_TRY(cudaMalloc(&error_flag[dev], sizeof(int)));
+    LAPIS_CUDA_TRY(cudaMemset(error_flag[dev], 0, sizeof(int)));
+  }
+  if (!attr_set[dev]) {
+    LAPIS_CUDA_TRY(cudaFuncSetAttribute(tc::bgemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        tc::SMEM_BYTES));
+    attr_set[dev] = true;
+  }
+  dim3 grid((unsigned)(N / tc::BN), (unsigned)(M / tc::BM), (unsigned)batch);
+  tc::bgemm_tcgen05_kernel<<<grid, tc::THREADS, tc::SMEM_BYTES, st>>>(map_a, map_b, C, (int)M, (int)N, (int)K,
+                                                                    error_flag[dev]);
+  LAPIS_CUDA_TRY(cudaGetLastError());
+  return LAPIS_OK;
 }
 
 }  // namespace lapis_b200
+
+// Reads and clears the tensor-core kernel's error flag; synchronises `stream`.  A non-zero flag
+// means a bounded wait inside the kernel gave up (1 producer, 2 MMA issuer, 3 split warps,
+// 4 epilogue) and the output of that launch is not valid.
+extern "C" int lapis_b200_bgemm_status(void *stream) {
+  using namespace lapis_b200;
+  clear_error();
+  int dev = 0;
+  LAPIS_CUDA_TRY(cudaGetDevice(&dev));
+  LAPIS_CUDA_TRY(cudaStreamSynchronize(as_stream(stream)));
+  if (dev < 0 || dev >= 64 || error_flag[dev] == nullptr) return LAPIS_OK;
+  int flag = 0;
+  LAPIS_CUDA_TRY(cudaMemcpy(&flag, error_flag[dev], sizeof(int), cudaMemcpyDeviceToHost));
+  if (flag != 0) {
+    cudaMemset(error_flag[dev], 0, sizeof(int));
+    return fail(LAPIS_ECUDA, "bgemm: tensor-core kernel gave up waiting (role %d)", flag);
+  }
+  return LAPIS_OK;
+}

@@ -119,6 +119,11 @@ def bgemm(A: torch.Tensor, B: torch.Tensor, C: torch.Tensor) -> torch.Tensor:
     return C
 
 
+def bgemm_status() -> None:
+    """Synchronises and raises if the tensor-core matmul kernel reported a failed wait."""
+    check(load().lapis_b200_bgemm_status(_stream()))
+
+
 def dot(x: torch.Tensor, y: torch.Tensor) -> torch.Tensor:
     _f64(x, "x"), _f64(y, "y")
     out = torch.empty(1, dtype=torch.float64, device=x.device)

@@ -256,6 +256,35 @@ def test_bgemm_general_shapes_bit_exact(shape):
     assert np.array_equal(Cd.cpu().numpy(), oracle.bgemm(A, B, C0))
 
 
+@pytest.mark.parametrize("shape", [(1, 128, 128, 32), (1, 128, 128, 256), (3, 128, 128, 128), (2, 256, 384, 96),
+                                   (1, 512, 512, 1024)])
+def test_bgemm_tensor_core_path(shape):
+    """Tile-aligned shapes run on tcgen05 with fp32 emulated by three TF32 products.  The bar is
+    norm-wise against a product accumulated in double: no worse than max(1e-5 * |C|_max, the error
+    of the reference's own sequential fp32 loop)."""
+    from lapis_b200.device import bgemm, bgemm_status
+    dev = _dev()
+    b, M, N, K = shape
+    rng = np.random.default_rng(M + N + K)
+    A = rng.uniform(-1, 1, (b, M, K)).astype(np.float32)
+    B = rng.uniform(-1, 1, (b, K, N)).astype(np.float32)
+    C0 = rng.uniform(-1, 1, (b, M, N)).astype(np.float32)
+    Cd = torch.as_tensor(C0).to(dev)
+    bgemm(torch.as_tensor(A).to(dev), torch.as_tensor(B).to(dev), Cd)
+    bgemm_status()
+    got = Cd.cpu().numpy().astype(np.float64)
+    exact = oracle.bgemm_acc64(A, B, C0)
+    ref_err = np.max(np.abs(oracle.bgemm(A, B, C0).astype(np.float64) - exact))
+    err = np.max(np.abs(got - exact))
+    scale = np.max(np.abs(exact))
+    assert err <= max(1e-5 * scale, ref_err), f"err {err:.3e}, fp32 loop err {ref_err:.3e}, |C| {scale:.3e}"
+    # identical bits from run to run
+    Cd2 = torch.as_tensor(C0).to(dev)
+    bgemm(torch.as_tensor(A).to(dev), torch.as_tensor(B).to(dev), Cd2)
+    bgemm_status()
+    assert torch.equal(Cd, Cd2)
+
+
 # ---------------------------------------------------------------------------
 # vector kernels and PCG
 # ---------------------------------------------------------------------------
