@@ -568,12 +568,14 @@ def main():
         torch.cuda.set_device(local_rank)
         dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local_rank}"))
     d = make_workload(args.workload, args.small, args.shrink)
-    try:
-        run_ours(args, d, rank, world, local_rank)
-    finally:
-        if world > 1:
-            dist.barrier()
-            dist.destroy_process_group()
+    run_ours(args, d, rank, world, local_rank)
+    if world > 1:
+        # All ranks have reported; leave without communicator teardown (destroy_process_group() has
+        # been seen to block when captured graphs still hold NCCL work).
+        dist.barrier()
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        os._exit(0)
     return 0
 
 

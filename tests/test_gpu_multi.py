@@ -1,0 +1,87 @@
+"""Row-partitioned SpMV and PCG on two GPUs (one process per GPU, NCCL).  Skipped on a box with
+a single GPU; the same schedule is covered on CPU ranks by tests/test_dist_gloo.py."""
+import os
+import socket
+import sys
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, out_dir):
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    dev = torch.device(f"cuda:{rank}")
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    from lapis_b200 import workloads as w
+    from lapis_b200.dist import DistPcg, ShardedSpmv
+
+    # SpMV: rows split by nnz, x replicated, no exchange
+    d = w.spmv_power_law(1 << 15)
+    n = d["shape"][0]
+    sh = ShardedSpmv(d["pos"], d["crd"], d["val"], d["shape"], rank, world, dev)
+    y = torch.zeros(sh.r1 - sh.r0, dtype=torch.float64, device=dev)
+    sh.spmv(torch.as_tensor(d["x"]).to(dev), y, accumulate=False)
+    np.save(os.path.join(out_dir, f"y{rank}.npy"), np.concatenate([[sh.r0, sh.r1], y.cpu().numpy()]))
+
+    # PCG: halo exchange of p, two allreduces per iteration, one iteration per CUDA graph replay
+    p = w.pcg_laplacian(96)
+    m = p["shape"][0]
+    for use_graph in (False, True):
+        solver = DistPcg(p["pos"], p["crd"], p["val"], (m, m), p["b"], p["dinv"], dev, use_graph=use_graph)
+        x, iters, relres = solver.solve(0.0, 40, check_every=10)
+        np.savez(os.path.join(out_dir, f"pcg{rank}_{int(use_graph)}.npz"), x=x.cpu().numpy(), r0=solver.halo.r0,
+                 r1=solver.halo.r1, iters=iters, relres=relres)
+    dist.barrier()
+    torch.cuda.synchronize()
+    # Leave without tearing the communicator down: with captured graphs that hold NCCL work,
+    # destroy_process_group() has been seen to block; the results are already on disk.
+    sys.stdout.flush()
+    os._exit(0)
+
+
+def test_two_gpu_spmv_and_pcg(tmp_path):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    from lapis_b200 import workloads as w
+    from oracle import oracle
+    world = 2
+    mp.spawn(_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+
+    d = w.spmv_power_law(1 << 15)
+    n = d["shape"][0]
+    ref = oracle.spmv(d["pos"], d["crd"], d["val"], d["x"], np.zeros(n))
+    scale = oracle.spmv(d["pos"], d["crd"], np.abs(d["val"]), np.abs(d["x"]), np.zeros(n))
+    covered = 0
+    for rank in range(world):
+        a = np.load(tmp_path / f"y{rank}.npy")
+        r0, r1 = int(a[0]), int(a[1])
+        covered += r1 - r0
+        assert np.all(np.abs(a[2:] - ref[r0:r1]) <= 1e-12 * np.maximum(scale[r0:r1], 1e-300))
+    assert covered == n
+
+    p = w.pcg_laplacian(96)
+    xo, io, ro = oracle.pcg(p["pos"], p["crd"], p["val"], p["b"], p["dinv"], 0.0, 40)
+    for g in (0, 1):
+        x = np.zeros(96 * 96)
+        for rank in range(world):
+            f = np.load(tmp_path / f"pcg{rank}_{g}.npz")
+            x[int(f["r0"]):int(f["r1"])] = f["x"]
+            assert int(f["iters"]) == io == 40
+            assert abs(float(f["relres"]) - ro) <= 1e-9 * ro
+        assert np.max(np.abs(x - xo)) <= 1e-9 * np.max(np.abs(xo))
