@@ -146,7 +146,7 @@ def make_workload(name: str, small: bool, shrink: int = 0):
         d.update(unit="GB/s", metric="csr_spmm_hbm_gbs", dtype="f64", unit_scale=1e-9,
                  work=w.spmm_bytes(n, n, nnz, 64, 8), label=f"CSR SpMM fp64 (config 3): {n} rows, 32 nnz/row, k=64, int64 indices")
     elif name == "pcg":
-        g = 256 if small else 4096
+        g = 256 if small else 4096 >> shrink
         d = w.pcg_laplacian(g)
         n, nnz = d["shape"][0], int(d["crd"].size)
         d.update(unit="it/s", metric="pcg_iterations_per_s", dtype="f64", unit_scale=1.0, work=1,
@@ -332,9 +332,10 @@ def run_ours(args, d, rank, world, local_rank):
         bounds = part.partition_rows(pos, world)
         r0, r1 = int(bounds[rank]), int(bounds[rank + 1])
         lpos, lcrd, lval = part.row_block(pos, crd, val, r0, r1)
-        A = D.CsrMatrix.from_host(lpos, lcrd, lval, (r1 - r0, n), dev)
+        A = D.CsrMatrix.from_host(lpos, lcrd, lval, (r1 - r0, n), dev, tune=True)
+        extra_cfg_kernel = A.tune()
         extra_cfg = {"partition": "contiguous row blocks, equal nnz", "rows_rank0": int(bounds[1] - bounds[0]),
-                     "replicated": "x" if name == "spmv" else "B"}
+                     "replicated": "x" if name == "spmv" else "B", "spmv_kernel_tuned": list(extra_cfg_kernel)}
         if name == "spmv":
             xd = torch.as_tensor(d["x"]).to(dev)
             yd = torch.zeros(r1 - r0, dtype=torch.float64, device=dev)

@@ -132,6 +132,23 @@ int64_t lapis_b200_csr_nnz(lapis_b200_csr_t h);
  * callers put in front of it (examples/pcg_solve.py:13-20). */
 int lapis_b200_spmv_f64(lapis_b200_csr_t h, const double *d_x, double *d_y, int accumulate, void *stream);
 
+/* Two SpMV kernels exist: one chunk of 2048 stored entries per thread block (threads, blocks
+ * per SM in {(256,4), (256,6), (512,3)}), and a persistent kernel that stages chunks with bulk
+ * asynchronous copies (threads = -256 or -512, blocks_per_sm resident blocks per SM).  Which is
+ * faster depends on the matrix: the persistent one when x is served from cache (banded
+ * matrices), the other when the gathers of x dominate.  lapis_b200_csr_tune times the
+ * candidates on the matrix (a few SpMV launches into scratch buffers it allocates and frees;
+ * synchronises `stream`) and stores the winner in the handle; untuned handles use (256,4).
+ * lapis_b200_spmv_select_kernel forces one variant process-wide (threads = 0 returns to the
+ * handles' own choice); the environment variable LAPIS_B200_SPMV="threads,blocks,l2_hint" does
+ * the same from outside.  l2_hint marks x evict-last in L2. */
+int lapis_b200_csr_tune(lapis_b200_csr_t h, void *stream);
+int lapis_b200_csr_tuned_kernel(lapis_b200_csr_t h, int *threads, int *blocks_per_sm);
+int lapis_b200_spmv_select_kernel(int threads, int blocks_per_sm, int l2_hint);
+/* The persistent kernel bounds its waits on the bulk copies; this synchronises `stream` and
+ * returns LAPIS_ECUDA if a block gave up (then y of that launch is invalid), clearing the flag. */
+int lapis_b200_spmv_status(void *stream);
+
 /* The same SpMV for callers that must not allocate device memory in the call -- code
  * running inside a pool that already owns the whole GPU, or a steady-state loop where
  * a cudaMalloc could stall the device or fail.  No counterpart in the reference (its

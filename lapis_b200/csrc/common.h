@@ -50,5 +50,7 @@ struct lapis_b200_csr {
   double *carry;
   // Scratch for the fused dot product of the PCG SpMV pass (one double per block).
   double *blk_partial;
+  // Kernel variant chosen by lapis_b200_csr_tune (tuned_threads == 0: not tuned).
+  int tuned_threads, tuned_minb, tuned_hint;
   int device;
 };

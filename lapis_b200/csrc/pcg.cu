@@ -382,6 +382,8 @@ extern "C" int lapis_b200_pcg_f64(lapis_b200_csr_t h, const double *d_b, const d
     if (relres) *relres = NAN;
     return LAPIS_OK;
   }
+  // a solve runs the SpMV pass many times: pick the kernel variant for this matrix first
+  if (h->tuned_threads == 0 && (maxiter == 0 || maxiter >= 16)) LAPIS_TRY(lapis_b200_csr_tune(h, st));
   void *work = nullptr;
   LAPIS_CUDA_TRY(cudaMalloc(&work, (size_t)lapis_b200_pcg_workspace_bytes(n, n)));
   int status = lapis_b200_pcg_init(work, n, n, 0, d_b, d_dinv, d_x, 1, st);

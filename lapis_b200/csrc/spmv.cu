@@ -38,7 +38,7 @@ constexpr int SPMV_LONG_ROW = 32;     // rows with more in-chunk entries than th
 
 // ---------------------------------------------------------------------------
 // Plan: plan[b] = first row r with pos[r+1] > abase + b*TILE (the row holding the
-// chunk's first entry), plan[0] = 0, plan[nblk] = nrows; abase = pos[0] & ~1.
+// chunk's first entry), plan[0] = 0, plan[nblk] = nrows; abase = pos[0] & ~3.
 // ---------------------------------------------------------------------------
 template <typename I>
 __global__ void spmv_plan_kernel(const I *__restrict__ pos, int64_t nrows, int64_t nblk,
@@ -53,7 +53,7 @@ __global__ void spmv_plan_kernel(const I *__restrict__ pos, int64_t nrows, int64
     plan[0] = 0;
     return;
   }
-  const int64_t c0 = ((int64_t)pos[0] & ~(int64_t)1) + b * (int64_t)SPMV_TILE;
+  const int64_t c0 = ((int64_t)pos[0] & ~(int64_t)3) + b * (int64_t)SPMV_TILE;
   int64_t lo = 0, hi = nrows;
   while (lo < hi) {
     int64_t mid = lo + ((hi - lo) >> 1);
@@ -123,11 +123,11 @@ __device__ __forceinline__ int rel_at(const ChunkCtx &c, const int *s_rel, const
 template <bool FUSE_DOT>
 __device__ __forceinline__ void finish_row(const ChunkCtx &c, int i, int s, double acc, double yin,
                                            double *__restrict__ y, double *__restrict__ carry,
-                                           const double *__restrict__ dotvec, double &dot_local) {
+                                           const double *__restrict__ dotvec, double &dot_local, int chunk) {
   const int64_t r = c.row0 + i;
   if (c.has_tail && i == c.nr - 1) {
     if (s >= c.len) return;  // the row starts beyond this chunk: not ours
-    carry[blockIdx.x] = acc;
+    carry[chunk] = acc;
   } else {
     y[r] = __dadd_rn(acc, yin);
   }
@@ -138,7 +138,7 @@ template <typename I, int THREADS, int L, bool FUSE_DOT>
 __device__ __forceinline__ void reduce_short_rows(const ChunkCtx &c, const int *s_rel, const I *__restrict__ pos,
                                                   const double *s_prod, int *s_long, int *s_nlong,
                                                   double *__restrict__ y, int accumulate, double *__restrict__ carry,
-                                                  const double *__restrict__ dotvec, double &dot_local) {
+                                                  const double *__restrict__ dotvec, double &dot_local, int chunk) {
   const int tid = threadIdx.x;
   const int grp = tid / L, lane = tid % L;
   constexpr int NGRP = THREADS / L;
@@ -162,7 +162,7 @@ __device__ __forceinline__ void reduce_short_rows(const ChunkCtx &c, const int *
       if (is_long)
         s_long[atomicAdd(s_nlong, 1)] = i;  // order of the list does not matter: rows are independent
       else
-        finish_row<FUSE_DOT>(c, i, s, acc, yin, y, carry, dotvec, dot_local);
+        finish_row<FUSE_DOT>(c, i, s, acc, yin, y, carry, dotvec, dot_local, chunk);
     }
   }
 }
@@ -245,7 +245,7 @@ spmv_chunk_kernel(const I *__restrict__ pos, const I *__restrict__ crd, const do
   const int avg = c.len / (c.nr > 0 ? c.nr : 1);
 #define LAPIS_REDUCE(LANES)                                                                                   \
   reduce_short_rows<I, THREADS, LANES, FUSE_DOT>(c, s_rel, pos, s_prod, s_long, &s_nlong, y, accumulate, carry, \
-                                                 dotvec, dot_local)
+                                                 dotvec, dot_local, (int)blockIdx.x)
   if (avg <= 4)
     LAPIS_REDUCE(1);
   else if (avg <= 8)
@@ -269,13 +269,211 @@ spmv_chunk_kernel(const I *__restrict__ pos, const I *__restrict__ crd, const do
     for (int j = s + lane; j < e; j += 32) acc = __dadd_rn(acc, s_prod[j]);
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) acc = __dadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, off));
-    if (lane == 0) finish_row<FUSE_DOT>(c, i, s, acc, yin, y, carry, dotvec, dot_local);
+    if (lane == 0) finish_row<FUSE_DOT>(c, i, s, acc, yin, y, carry, dotvec, dot_local, (int)blockIdx.x);
   }
 
   if (FUSE_DOT) {
     const double t = block_sum(dot_local, s_red);
     if (tid == 0) blk_partial[blockIdx.x] = t;
   }
+}
+
+
+// ---------------------------------------------------------------------------
+// Persistent variant: each block walks chunks b, b + grid, ... and keeps the next
+// chunk's val/crd in flight with bulk asynchronous copies (cp.async.bulk, completion
+// on an mbarrier) into a second shared-memory stage while it gathers and reduces the
+// current one, so the streamed entries bypass the load/store unit and registers.
+// Products overwrite val in place.  Every barrier wait is bounded; a block that gives
+// up records g_spmv_error and leaves the loop.
+// ---------------------------------------------------------------------------
+__device__ int g_spmv_error;
+constexpr uint32_t SPMV_WAIT_LIMIT = 1u << 24;
+
+__device__ __forceinline__ uint32_t smem_addr(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ bool spmv_mbar_wait(uint64_t *bar, uint32_t parity) {
+  const uint32_t addr = smem_addr(bar);
+  for (uint32_t i = 0; i < SPMV_WAIT_LIMIT; ++i) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(addr), "r"(parity)
+        : "memory");
+    if (done) return true;
+  }
+  return false;
+}
+
+// Streamed once: the copy carries an evict-first L2 policy so that it does not push x out of L2.
+__device__ __forceinline__ void bulk_load(void *dst, const void *src, uint32_t bytes, uint64_t *bar, uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;" ::"r"(
+          smem_addr(dst)),
+      "l"(src), "r"(bytes), "r"(smem_addr(bar)), "l"(policy)
+      : "memory");
+}
+
+template <typename I, int THREADS, bool FUSE_DOT, bool HINT>
+__global__ void __launch_bounds__(THREADS)
+spmv_pipe_kernel(const I *__restrict__ pos, const I *__restrict__ crd, const double *__restrict__ val,
+                 const int64_t *__restrict__ plan, int64_t abase, int64_t nnz_end, int64_t nrows, int64_t nblk,
+                 const double *__restrict__ x, double *__restrict__ y, int accumulate, double *__restrict__ carry,
+                 const double *__restrict__ dotvec, double *__restrict__ blk_partial,
+                 const int *__restrict__ skip_flag) {
+  constexpr int T = SPMV_TILE;
+  constexpr int PER = T / THREADS;
+  extern __shared__ __align__(128) uint8_t pipe_smem[];
+  double *s_val0 = reinterpret_cast<double *>(pipe_smem);      // two stages of T values
+  I *s_crd0 = reinterpret_cast<I *>(pipe_smem + 2 * T * 8);    // two stages of T column indices
+  uint8_t *tail = pipe_smem + 2 * T * 8 + 2 * T * sizeof(I);
+  int *s_rel = reinterpret_cast<int *>(tail);
+  int *s_long = s_rel + SPMV_POS_CACHE + 2;
+  int *s_nlong = s_long + T / SPMV_LONG_ROW;
+  double *s_red = reinterpret_cast<double *>(s_nlong + 2);
+  uint64_t *full = reinterpret_cast<uint64_t *>(s_red + THREADS / 32);
+
+  if (skip_flag != nullptr && *skip_flag != 0) return;
+  const int tid = threadIdx.x;
+  if (tid == 0) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_addr(&full[0])));
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_addr(&full[1])));
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+
+  uint64_t policy = 0, stream_policy = 0;
+  if (HINT) asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(policy));
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(stream_policy));
+
+  // entries of chunk b moved by the bulk copies: whole groups of 4 (16-byte multiples for both arrays)
+  auto chunk_len = [&](int64_t b) {
+    const int64_t left = nnz_end - (abase + b * T);
+    return (int)(left < T ? (left < 0 ? 0 : left) : T);
+  };
+  auto issue = [&](int64_t b, int s) {
+    const int len4 = chunk_len(b) & ~3;
+    if (len4 > 0) {
+      const int64_t c0 = abase + b * T;
+      const uint32_t bytes = (uint32_t)len4 * (8u + (uint32_t)sizeof(I));
+      asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(&full[s])), "r"(bytes)
+                   : "memory");
+      bulk_load(s_val0 + s * T, val + c0, (uint32_t)len4 * 8u, &full[s], stream_policy);
+      bulk_load(s_crd0 + s * T, crd + c0, (uint32_t)len4 * (uint32_t)sizeof(I), &full[s], stream_policy);
+    } else {
+      asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(&full[s])) : "memory");
+    }
+  };
+
+  double dot_local = 0.0;
+  int it = 0;
+  if (tid == 0 && (int64_t)blockIdx.x < nblk) issue(blockIdx.x, 0);
+  for (int64_t b = blockIdx.x; b < nblk; b += gridDim.x, ++it) {
+    const int s = it & 1;
+    const int64_t bn = b + gridDim.x;
+    if (tid == 0 && bn < nblk) issue(bn, s ^ 1);  // stage s^1 was released by the barrier ending the last pass
+
+    ChunkCtx c;
+    c.c0 = abase + b * T;
+    c.len = chunk_len(b);
+    c.row0 = plan[b];
+    const int64_t rn = plan[b + 1];
+    c.has_tail = rn < nrows;
+    const int64_t nr64 = rn - c.row0 + (c.has_tail ? 1 : 0);
+    c.nr = (int)(nr64 > 0x7fffffff ? 0x7fffffff : nr64);
+    c.ncached = (int)(nr64 + 1 < SPMV_POS_CACHE + 2 ? nr64 + 1 : SPMV_POS_CACHE + 2);
+    for (int i = tid; i < c.ncached; i += THREADS) {
+      int64_t d = (int64_t)pos[c.row0 + i] - c.c0;
+      d = d < 0 ? 0 : d;
+      s_rel[i] = (int)(d > c.len ? c.len : d);
+    }
+    if (tid == 0) *s_nlong = 0;
+
+    const bool landed = spmv_mbar_wait(&full[s], (uint32_t)(it >> 1) & 1u);
+    if (!__syncthreads_and(landed ? 1 : 0)) {  // also orders s_rel / s_nlong before their readers
+      if (tid == 0) atomicExch(&g_spmv_error, 1);
+      break;
+    }
+
+    // ---- gather x and turn val into products, in place ----------------------------------
+    const int len4 = c.len & ~3;
+    double *prod = s_val0 + s * T;
+    const I *cs = s_crd0 + s * T;
+    I ci[PER];
+    double xv[PER];
+#pragma unroll
+    for (int k = 0; k < PER; ++k) {
+      const int j = tid + k * THREADS;
+      ci[k] = 0;
+      if (j < len4)
+        ci[k] = cs[j];
+      else if (j < c.len)
+        ci[k] = crd[c.c0 + j];  // up to three entries at the very end of the arrays
+    }
+#pragma unroll
+    for (int k = 0; k < PER; ++k) {
+      const int j = tid + k * THREADS;
+      xv[k] = (j < c.len) ? load_x(x + ci[k], policy, HINT) : 0.0;
+    }
+#pragma unroll
+    for (int k = 0; k < PER; ++k) {
+      const int j = tid + k * THREADS;
+      if (j < len4)
+        prod[j] = __dmul_rn(prod[j], xv[k]);
+      else if (j < c.len)
+        prod[j] = __dmul_rn(val[c.c0 + j], xv[k]);
+    }
+    __syncthreads();
+
+    // ---- rows ending in this chunk (same two passes as the one-chunk-per-block kernel) ------
+    const int avg = c.len / (c.nr > 0 ? c.nr : 1);
+#define LAPIS_REDUCE(LANES)                                                                               \
+  reduce_short_rows<I, THREADS, LANES, FUSE_DOT>(c, s_rel, pos, prod, s_long, s_nlong, y, accumulate, carry, \
+                                                 dotvec, dot_local, (int)b)
+    if (avg <= 4)
+      LAPIS_REDUCE(1);
+    else if (avg <= 8)
+      LAPIS_REDUCE(2);
+    else if (avg <= 16)
+      LAPIS_REDUCE(4);
+    else
+      LAPIS_REDUCE(8);
+#undef LAPIS_REDUCE
+    __syncthreads();
+    const int nlong = *s_nlong;
+    const int warp = tid >> 5, lane = tid & 31;
+    for (int q = warp; q < nlong; q += THREADS / 32) {
+      const int i = s_long[q];
+      const int s0 = rel_at<I>(c, s_rel, pos, i), e0 = rel_at<I>(c, s_rel, pos, i + 1);
+      double yin = 0.0;
+      if (accumulate && lane == 0 && !(c.has_tail && i == c.nr - 1)) yin = y[c.row0 + i];
+      double acc = 0.0;
+      for (int j = s0 + lane; j < e0; j += 32) acc = __dadd_rn(acc, prod[j]);
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) acc = __dadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, off));
+      if (lane == 0) finish_row<FUSE_DOT>(c, i, s0, acc, yin, y, carry, dotvec, dot_local, (int)b);
+    }
+    // the next bulk copy into this stage must not overtake these shared-memory accesses
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    __syncthreads();
+  }
+
+  if (FUSE_DOT) {
+    // one partial per block; the blocks past the grid size contribute nothing
+    const double t = block_sum(dot_local, s_red);
+    if (tid == 0) blk_partial[blockIdx.x] = t;
+    for (int64_t e = gridDim.x + (int64_t)blockIdx.x * THREADS + tid; e < nblk; e += (int64_t)gridDim.x * THREADS)
+      blk_partial[e] = 0.0;
+  }
+}
+
+template <typename I>
+constexpr int spmv_pipe_smem_bytes(int threads) {
+  return 2 * SPMV_TILE * 8 + 2 * SPMV_TILE * (int)sizeof(I) + (SPMV_POS_CACHE + 2) * 4 + (SPMV_TILE / SPMV_LONG_ROW) * 4 +
+         8 + (threads / 32) * 8 + 16 + 64;
 }
 
 // Adds the carries to their rows.  Chunk b left a carry iff row q = plan[b+1] exists and starts
@@ -386,13 +584,19 @@ spmm_row_kernel(const I *__restrict__ pos, const I *__restrict__ crd, const doub
 // ---------------------------------------------------------------------------
 // Host side
 // ---------------------------------------------------------------------------
-// Kernel variant used by spmv_launch: "threads,minblocks,hint" from LAPIS_B200_SPMV (tuning aid).
+// Kernel variant: {threads, blocks per SM, L2 hint}.  threads > 0: one chunk per block;
+// threads < 0: the persistent bulk-copy kernel with |threads| threads.  Which one is faster
+// depends on the matrix (the persistent kernel wins when x is served from L1/L2, as for banded
+// matrices; the one-chunk kernel when the gathers of x dominate), so lapis_b200_csr_tune times
+// the candidates on the matrix itself and stores the winner in the handle.  A process-wide
+// override (LAPIS_B200_SPMV="threads,blocks,hint" or lapis_b200_spmv_select_kernel) beats both.
 struct SpmvVariant {
   int threads, minb, hint;
 };
-static SpmvVariant spmv_variant() {
+constexpr SpmvVariant SPMV_DEFAULT{256, 4, 1};
+static SpmvVariant &spmv_override() {  // threads == 0: no override
   static SpmvVariant v = [] {
-    SpmvVariant d{256, 4, 1};
+    SpmvVariant d{0, 0, 0};
     if (const char *e = std::getenv("LAPIS_B200_SPMV")) {
       int t = 0, m = 0, h = 0;
       if (sscanf(e, "%d,%d,%d", &t, &m, &h) == 3) d = SpmvVariant{t, m, h};
@@ -401,13 +605,17 @@ static SpmvVariant spmv_variant() {
   }();
   return v;
 }
+static bool spmv_variant_known(int threads, int minb) {
+  if (threads == -256 || threads == -512) return minb >= 1 && minb <= 8;
+  return (threads == 256 && (minb == 4 || minb == 6)) || (threads == 512 && minb == 3);
+}
 
 template <typename I, int THREADS, int MINB, bool HINT>
 static void launch_chunks(const lapis_b200_csr *h, const double *x, double *y, int accumulate, const double *dotvec,
                           double *blk_partial, const int *skip_flag, cudaStream_t st) {
   const I *pos = static_cast<const I *>(h->pos);
   const I *crd = static_cast<const I *>(h->crd);
-  const int64_t abase = h->base & ~(int64_t)1, nnz_end = h->base + h->nnz;
+  const int64_t abase = h->base & ~(int64_t)3, nnz_end = h->base + h->nnz;
   if (dotvec != nullptr)
     spmv_chunk_kernel<I, THREADS, MINB, true, HINT><<<(unsigned)h->nblk, THREADS, 0, st>>>(
         pos, crd, h->val, h->blk_row, abase, nnz_end, h->nrows, x, y, accumulate, h->carry, dotvec, blk_partial,
@@ -418,11 +626,54 @@ static void launch_chunks(const lapis_b200_csr *h, const double *x, double *y, i
         skip_flag);
 }
 
+template <typename I, int THREADS, bool HINT>
+static int launch_pipe(const lapis_b200_csr *h, int ctas_per_sm, const double *x, double *y, int accumulate,
+                       const double *dotvec, double *blk_partial, const int *skip_flag, cudaStream_t st) {
+  const I *pos = static_cast<const I *>(h->pos);
+  const I *crd = static_cast<const I *>(h->crd);
+  const int64_t abase = h->base & ~(int64_t)3, nnz_end = h->base + h->nnz;
+  constexpr int smem = spmv_pipe_smem_bytes<I>(THREADS);
+  static bool attr_done[2] = {false, false};
+  int64_t grid = (int64_t)sm_count() * ctas_per_sm;
+  if (grid > h->nblk) grid = h->nblk;
+  if (dotvec != nullptr) {
+    auto k = spmv_pipe_kernel<I, THREADS, true, HINT>;
+    if (!attr_done[1]) {
+      LAPIS_CUDA_TRY(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+      attr_done[1] = true;
+    }
+    k<<<(unsigned)grid, THREADS, smem, st>>>(pos, crd, h->val, h->blk_row, abase, nnz_end, h->nrows, h->nblk, x, y,
+                                             accumulate, h->carry, dotvec, blk_partial, skip_flag);
+  } else {
+    auto k = spmv_pipe_kernel<I, THREADS, false, HINT>;
+    if (!attr_done[0]) {
+      LAPIS_CUDA_TRY(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+      attr_done[0] = true;
+    }
+    k<<<(unsigned)grid, THREADS, smem, st>>>(pos, crd, h->val, h->blk_row, abase, nnz_end, h->nrows, h->nblk, x, y,
+                                             accumulate, h->carry, nullptr, nullptr, skip_flag);
+  }
+  return LAPIS_OK;
+}
+
 template <typename I>
 static int launch_spmv(const lapis_b200_csr *h, const double *x, double *y, int accumulate,
                        const double *dotvec, double *blk_partial, const int *skip_flag,
                        cudaStream_t st) {
-  const SpmvVariant v = spmv_variant();
+  SpmvVariant v = spmv_override();
+  if (v.threads == 0) v = h->tuned_threads != 0 ? SpmvVariant{h->tuned_threads, h->tuned_minb, h->tuned_hint} : SPMV_DEFAULT;
+  if (v.threads < 0) {  // persistent bulk-copy kernel: threads = -256 or -512, minb = blocks per SM
+    int rc;
+    if (v.threads == -256)
+      rc = v.hint ? launch_pipe<I, 256, true>(h, v.minb, x, y, accumulate, dotvec, blk_partial, skip_flag, st)
+                  : launch_pipe<I, 256, false>(h, v.minb, x, y, accumulate, dotvec, blk_partial, skip_flag, st);
+    else if (v.threads == -512)
+      rc = v.hint ? launch_pipe<I, 512, true>(h, v.minb, x, y, accumulate, dotvec, blk_partial, skip_flag, st)
+                  : launch_pipe<I, 512, false>(h, v.minb, x, y, accumulate, dotvec, blk_partial, skip_flag, st);
+    else
+      return fail(LAPIS_EBADARG, "LAPIS_B200_SPMV names an unknown kernel variant");
+    LAPIS_TRY(rc);
+  } else
 #define LAPIS_V(T, M)                                                                                     \
   if (v.threads == T && v.minb == M) {                                                                    \
     if (v.hint)                                                                                           \
@@ -432,19 +683,14 @@ static int launch_spmv(const lapis_b200_csr *h, const double *x, double *y, int 
   } else
   LAPIS_V(256, 6)
   LAPIS_V(256, 4)
-  LAPIS_V(256, 8)
-  LAPIS_V(128, 8)
-  LAPIS_V(128, 12)
   LAPIS_V(512, 3)
-  LAPIS_V(512, 4)
-  LAPIS_V(1024, 2)
   { return fail(LAPIS_EBADARG, "LAPIS_B200_SPMV names an unknown kernel variant"); }
 #undef LAPIS_V
   LAPIS_CUDA_TRY(cudaGetLastError());
   if (h->nblk > 1) {
     const I *pos = static_cast<const I *>(h->pos);
     spmv_fixup_kernel<I><<<(unsigned)((h->nblk - 1 + 255) / 256), 256, 0, st>>>(
-        pos, h->blk_row, h->base & ~(int64_t)1, h->nblk, h->nrows, h->carry, y, skip_flag);
+        pos, h->blk_row, h->base & ~(int64_t)3, h->nblk, h->nrows, h->carry, y, skip_flag);
     LAPIS_CUDA_TRY(cudaGetLastError());
   }
   return LAPIS_OK;
@@ -511,7 +757,7 @@ extern "C" int lapis_b200_csr_create(lapis_b200_csr_t *out, int idx_bytes, int64
   if (ends[1] < ends[0] || ends[0] < 0) return fail(LAPIS_EBADSHAPE, "csr_create: pos is not non-decreasing");
   const int64_t nnz = ends[1] - ends[0];
   if (nnz > 0 && (d_crd == nullptr || d_val == nullptr)) return fail(LAPIS_EBADARG, "csr_create: crd/val null");
-  int64_t nblk = (ends[1] - (ends[0] & ~(int64_t)1) + SPMV_TILE - 1) / SPMV_TILE;
+  int64_t nblk = (ends[1] - (ends[0] & ~(int64_t)3) + SPMV_TILE - 1) / SPMV_TILE;
   if (nblk < 1) nblk = 1;
   if (nblk > 0x7fffffffLL) return fail(LAPIS_ETOOBIG, "csr_create: more than 2^31 chunks");
 
@@ -528,6 +774,7 @@ extern "C" int lapis_b200_csr_create(lapis_b200_csr_t *out, int idx_bytes, int64
   h->blk_row = nullptr;
   h->blk_partial = nullptr;
   h->carry = nullptr;
+  h->tuned_threads = h->tuned_minb = h->tuned_hint = 0;
   h->device = dev;
   cudaError_t e = cudaMalloc(&h->blk_row, (size_t)(nblk + 1) * sizeof(int64_t));
   if (e == cudaSuccess) e = cudaMalloc(&h->blk_partial, (size_t)nblk * sizeof(double));
@@ -552,6 +799,88 @@ extern "C" int lapis_b200_csr_create(lapis_b200_csr_t *out, int idx_bytes, int64
     return fail(LAPIS_ECUDA, "csr_create: plan kernel launch failed: %s", cudaGetErrorString(e));
   }
   *out = h;
+  return LAPIS_OK;
+}
+
+extern "C" int lapis_b200_spmv_select_kernel(int threads, int blocks_per_sm, int l2_hint) {
+  clear_error();
+  if (threads == 0) {  // back to automatic: the handle's tuned choice, else the default
+    spmv_override() = SpmvVariant{0, 0, 0};
+    return LAPIS_OK;
+  }
+  if (!spmv_variant_known(threads, blocks_per_sm)) return fail(LAPIS_EBADARG, "spmv_select_kernel: unknown kernel variant");
+  spmv_override() = SpmvVariant{threads, blocks_per_sm, l2_hint ? 1 : 0};
+  return LAPIS_OK;
+}
+
+// Times the candidate kernels on this matrix (y = A x with scratch x = 0, y) and keeps the fastest.
+extern "C" int lapis_b200_csr_tune(lapis_b200_csr_t h, void *stream) {
+  clear_error();
+  if (h == nullptr) return fail(LAPIS_EBADARG, "csr_tune: null matrix handle");
+  if (h->nrows == 0 || h->nnz == 0) return LAPIS_OK;
+  cudaStream_t st = as_stream(stream);
+  double *x = nullptr, *y = nullptr;
+  LAPIS_CUDA_TRY(cudaMalloc(&x, (size_t)(h->ncols > 0 ? h->ncols : 1) * 8));
+  cudaError_t e = cudaMalloc(&y, (size_t)h->nrows * 8);
+  if (e != cudaSuccess) {
+    cudaFree(x);
+    return fail(LAPIS_ECUDA, "csr_tune: cudaMalloc failed: %s", cudaGetErrorString(e));
+  }
+  cudaMemsetAsync(x, 0, (size_t)(h->ncols > 0 ? h->ncols : 1) * 8, st);
+  const int pipe_blocks = h->idx_bytes == 4 ? 4 : 3;  // what fits in shared memory
+  const SpmvVariant cand[] = {{256, 4, 1}, {256, 6, 1}, {512, 3, 1}, {-256, pipe_blocks, 1}};
+  const SpmvVariant saved = spmv_override();
+  cudaEvent_t e0, e1;
+  cudaEventCreate(&e0);
+  cudaEventCreate(&e1);
+  float best = 0.f;
+  int status = LAPIS_OK;
+  for (const SpmvVariant &c : cand) {
+    spmv_override() = c;
+    status = spmv_launch(h, x, y, 0, nullptr, nullptr, nullptr, st);  // warm-up
+    if (status != LAPIS_OK) break;
+    cudaEventRecord(e0, st);
+    for (int r = 0; r < 3 && status == LAPIS_OK; ++r) status = spmv_launch(h, x, y, 0, nullptr, nullptr, nullptr, st);
+    cudaEventRecord(e1, st);
+    if (status != LAPIS_OK || cudaEventSynchronize(e1) != cudaSuccess) {
+      if (status == LAPIS_OK) status = fail(LAPIS_ECUDA, "csr_tune: timing run failed");
+      break;
+    }
+    float ms = 0.f;
+    cudaEventElapsedTime(&ms, e0, e1);
+    if (h->tuned_threads == 0 || ms < best) {
+      best = ms;
+      h->tuned_threads = c.threads;
+      h->tuned_minb = c.minb;
+      h->tuned_hint = c.hint;
+    }
+  }
+  spmv_override() = saved;
+  cudaEventDestroy(e0);
+  cudaEventDestroy(e1);
+  cudaFree(x);
+  cudaFree(y);
+  return status;
+}
+
+extern "C" int lapis_b200_csr_tuned_kernel(lapis_b200_csr_t h, int *threads, int *blocks_per_sm) {
+  if (h == nullptr) return LAPIS_EBADARG;
+  if (threads) *threads = h->tuned_threads;
+  if (blocks_per_sm) *blocks_per_sm = h->tuned_minb;
+  return LAPIS_OK;
+}
+
+// Reads and clears the flag a persistent SpMV block sets when one of its bounded waits gives up.
+extern "C" int lapis_b200_spmv_status(void *stream) {
+  clear_error();
+  LAPIS_CUDA_TRY(cudaStreamSynchronize(as_stream(stream)));
+  int flag = 0;
+  LAPIS_CUDA_TRY(cudaMemcpyFromSymbol(&flag, g_spmv_error, sizeof(int)));
+  if (flag != 0) {
+    const int zero = 0;
+    cudaMemcpyToSymbol(g_spmv_error, &zero, sizeof(int));
+    return fail(LAPIS_ECUDA, "spmv: a bulk copy did not complete within the wait limit; y is not valid");
+  }
   return LAPIS_OK;
 }
 
@@ -656,7 +985,7 @@ extern "C" int lapis_b200_spmv_f64_noalloc(int idx_bytes, int64_t nrows, int64_t
   const int64_t nnz = ends[1] - ends[0];
   if (nnz > 0 && (d_crd == nullptr || d_val == nullptr || d_x == nullptr))
     return fail(LAPIS_EBADARG, "spmv_noalloc: crd/val/x null");
-  int64_t nblk = (ends[1] - (ends[0] & ~(int64_t)1) + SPMV_TILE - 1) / SPMV_TILE;
+  int64_t nblk = (ends[1] - (ends[0] & ~(int64_t)3) + SPMV_TILE - 1) / SPMV_TILE;
   if (nblk < 1) nblk = 1;
   if (nblk > NOALLOC_MAX_TILES)
     return fail(LAPIS_ETOOBIG,
@@ -677,6 +1006,7 @@ extern "C" int lapis_b200_spmv_f64_noalloc(int idx_bytes, int64_t nrows, int64_t
   h.blk_row = plan;
   h.blk_partial = nullptr;
   h.carry = reinterpret_cast<double *>(plan + NOALLOC_MAX_TILES + 1);
+  h.tuned_threads = h.tuned_minb = h.tuned_hint = 0;
   h.device = 0;
   const unsigned pgrid = (unsigned)((nblk + 1 + 255) / 256);
   if (idx_bytes == 4)

@@ -37,7 +37,7 @@ class CsrMatrix:
     ``pos`` may be a slice of a larger offsets array (non-zero ``pos[0]``).
     """
 
-    def __init__(self, pos: torch.Tensor, crd: torch.Tensor, val: torch.Tensor, shape):
+    def __init__(self, pos: torch.Tensor, crd: torch.Tensor, val: torch.Tensor, shape, tune: bool = False):
         if pos.dtype != crd.dtype or pos.dtype not in (torch.int32, torch.int64):
             raise TypeError("pos/crd must both be int32 or both int64")
         for t in (pos, crd, val):
@@ -56,11 +56,22 @@ class CsrMatrix:
                                                   _ptr(pos), _ptr(crd), _ptr(val), _stream()))
         self._h = h
         self.nnz = int(self._lib.lapis_b200_csr_nnz(h))
+        if tune:
+            self.tune()
+
+    def tune(self):
+        """Times the SpMV kernel candidates on this matrix and keeps the fastest; returns
+        (threads, blocks_per_sm) of the winner (negative threads: the persistent kernel)."""
+        with torch.cuda.device(self.pos.device):
+            check(self._lib.lapis_b200_csr_tune(self._h, _stream()))
+        t, b = c_int(0), c_int(0)
+        self._lib.lapis_b200_csr_tuned_kernel(self._h, ctypes.byref(t), ctypes.byref(b))
+        return int(t.value), int(b.value)
 
     @classmethod
-    def from_host(cls, pos, crd, val, shape, device="cuda"):
+    def from_host(cls, pos, crd, val, shape, device="cuda", tune: bool = False):
         return cls(torch.as_tensor(np.ascontiguousarray(pos)).to(device), torch.as_tensor(np.ascontiguousarray(crd)).to(device),
-                   torch.as_tensor(np.ascontiguousarray(val, dtype=np.float64)).to(device), shape)
+                   torch.as_tensor(np.ascontiguousarray(val, dtype=np.float64)).to(device), shape, tune=tune)
 
     @property
     def handle(self):

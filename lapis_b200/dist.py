@@ -93,7 +93,7 @@ class ShardedSpmv:
         from .device import CsrMatrix
         self.bounds, lpos, lcrd, lval = local_block(pos, crd, val, rank, world)
         self.r0, self.r1 = int(self.bounds[rank]), int(self.bounds[rank + 1])
-        self.matrix = CsrMatrix.from_host(lpos, lcrd, lval, (self.r1 - self.r0, shape[1]), device)
+        self.matrix = CsrMatrix.from_host(lpos, lcrd, lval, (self.r1 - self.r0, shape[1]), device, tune=True)
 
     def spmv(self, x, y_local, accumulate=True):
         return self.matrix.spmv(x, y_local, accumulate)
@@ -126,7 +126,7 @@ class DistPcg:
         self.p_off = self.halo.own_offset
         lcrd = (lcrd.astype(np.int64) - self.halo.c0).astype(lcrd.dtype)  # columns index the window
         with torch.cuda.device(self.device):
-            self.matrix = CsrMatrix.from_host(lpos, lcrd, lval, (self.n, self.n_p), self.device)
+            self.matrix = CsrMatrix.from_host(lpos, lcrd, lval, (self.n, self.n_p), self.device, tune=True)
             sl = slice(self.halo.r0, self.halo.r1)
             self.b = torch.as_tensor(np.ascontiguousarray(b[sl])).to(self.device)
             self.dinv = torch.as_tensor(np.ascontiguousarray(dinv[sl])).to(self.device)

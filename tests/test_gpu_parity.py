@@ -67,9 +67,19 @@ def test_spmv_known_answer_through_backend(golden_dir):
     assert np.allclose(y, 2 * g["ycorrect"])
 
 
+@pytest.fixture(params=[(256, 4, 1), (-256, 3, 1), (-512, 2, 0)], ids=["chunk", "pipe256", "pipe512"])
+def spmv_kernel(request):
+    """Runs the test once per SpMV kernel variant and restores the default afterwards."""
+    from lapis_b200._lib import check, load
+    check(load().lapis_b200_spmv_select_kernel(*request.param))
+    yield request.param
+    check(load().lapis_b200_spmv_status(None))
+    check(load().lapis_b200_spmv_select_kernel(0, 0, 0))
+
+
 @pytest.mark.parametrize("idx", [np.int32, np.int64])
 @pytest.mark.parametrize("case", ["uniform10", "powerlaw", "ragged", "empty_rows", "one_huge_row", "all_empty", "dense_rows"])
-def test_spmv_matches_oracle(idx, case):
+def test_spmv_matches_oracle(idx, case, spmv_kernel):
     from lapis_b200.device import CsrMatrix
     dev = _dev()
     rng = np.random.default_rng(sum(map(ord, case)))
@@ -128,7 +138,24 @@ def test_spmv_matches_oracle(idx, case):
         assert np.array_equal(yd.cpu().numpy()[short], oracle.spmv(pos, crd, val, x, y0)[short])
 
 
-def test_spmv_row_block_in_place():
+def test_spmv_tuning_keeps_the_bits():
+    """Every kernel variant sums a row in the same order, so the tuned choice changes speed only."""
+    from lapis_b200.device import CsrMatrix
+    dev = _dev()
+    for d in (w.spmv_power_law(1 << 16, idx_dtype=np.int64), w.pcg_laplacian(200)):
+        n = d["shape"][0]
+        x = torch.as_tensor(np.random.default_rng(2).uniform(-1, 1, n)).to(dev)
+        A = CsrMatrix.from_host(d["pos"], d["crd"], d["val"], (n, n), dev)
+        y0 = torch.zeros(n, dtype=torch.float64, device=dev)
+        A.spmv(x, y0, accumulate=False)
+        threads, blocks = A.tune()
+        assert (threads, blocks) in ((256, 4), (256, 6), (512, 3), (-256, 3), (-256, 4))
+        y1 = torch.zeros(n, dtype=torch.float64, device=dev)
+        A.spmv(x, y1, accumulate=False)
+        assert torch.equal(y0, y1)
+
+
+def test_spmv_row_block_in_place(spmv_kernel):
     """A handle over rows [r0, r1) of a larger matrix (non-zero pos[0]) gives that slice of y."""
     from lapis_b200.device import CsrMatrix
     dev = _dev()
@@ -329,7 +356,7 @@ def test_pcg_nos4_through_backend(golden_dir):
         assert iters == m
 
 
-def test_pcg_step_parity_laplacian():
+def test_pcg_step_parity_laplacian(spmv_kernel):
     """One iteration from the oracle's state reproduces the oracle's next state: the passes are
     checked without CG's amplification of rounding differences (config 5 at 128x128)."""
     from lapis_b200.device import CsrMatrix
