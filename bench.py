@@ -322,7 +322,7 @@ def run_ours(args, d, rank, world, local_rank):
             ms = float(t.item())
         return ms, clocks
 
-    launches_per_step = 1
+    launches_per_step = 2 if args.workload == "spmv" else 1  # SpMV: chunk kernel + carry fix-up
     e2e = None
     kernel_name = ""
     extra_cfg = {}
@@ -340,7 +340,7 @@ def run_ours(args, d, rank, world, local_rank):
             xd = torch.as_tensor(d["x"]).to(dev)
             yd = torch.zeros(r1 - r0, dtype=torch.float64, device=dev)
             step = lambda: A.spmv(xd, yd, accumulate=False)
-            kernel_name = "spmv_stream_kernel"
+            kernel_name = "spmv_chunk_kernel"
             host_in = [lpos, lcrd, lval, d["x"]]
             module = KB.KokkosBackend(decompose_tensors=True).compile(mm.spmv(mm.CSR64))
         else:
@@ -395,8 +395,8 @@ def run_ours(args, d, rank, world, local_rank):
         solver_w = DistPcg(d["pos"], d["crd"], d["val"], (n, n), d["b"], d["dinv"], dev, use_graph=True)
         solver_w.solve(0.0, max(1, args.warmup))
         solver.solve(0.0, args.steps)  # captures the graph; timed run below replays it
-        kernel_name = "spmv_stream_kernel + pcg_update_kernel + pcg_direction_kernel"
-        launches_per_step = 5 if world == 1 else 7
+        kernel_name = "spmv_pipe_kernel|spmv_chunk_kernel (pass A) + pcg_update_kernel + pcg_direction_kernel"
+        launches_per_step = 6 if world == 1 else 8
         steps_holder = {"k": args.steps}
         ms, clocks = timed(lambda: solve(steps_holder["k"]), 1, 0)
         it = state["out"][1]
@@ -427,7 +427,7 @@ def run_ours(args, d, rank, world, local_rank):
         Ad, Bd = torch.as_tensor(A_h).to(dev), torch.as_tensor(B_h).to(dev)
         Cd = torch.zeros(A_h.shape[:-1] + (B_h.shape[-1],), dtype=torch.float32, device=dev)
         step = lambda: D.bgemm(Ad, Bd, Cd)
-        kernel_name = "bgemm kernel"
+        kernel_name = "bgemm_tcgen05_kernel"
         module = KB.KokkosBackend().compile(mm.MATMUL if A_h.ndim == 2 else mm.BATCH_MATMUL)
         pa, pb = torch.as_tensor(A_h).pin_memory(), torch.as_tensor(B_h).pin_memory()
         pc = torch.zeros(Cd.shape, dtype=torch.float32).pin_memory()
@@ -454,7 +454,13 @@ def run_ours(args, d, rank, world, local_rank):
 
 # DRAM bytes per launch of the dominant kernel from the committed ncu captures under profiles/
 # (dram__bytes_read.sum + dram__bytes_write.sum, scaled to a full launch by entries processed).
-NCU_TRAFFIC = {}
+NCU_TRAFFIC = {
+    "spmv": 3.325e9,    # profiles/spmv_chunk_kernel_config2.md
+    "spmm": 3.380e10,   # profiles/spmm_row_kernel_config3.md
+    "bgemm": 1.040e9,   # profiles/bgemm_tcgen05_kernel.md (4096 x 128^3)
+    "gemm": 8.426e9,    # profiles/bgemm_tcgen05_kernel.md (8192^3)
+    "pcg": 2.63e9,      # profiles/pcg_iteration_config5.md (all kernels of one iteration)
+}
 
 
 def emit(args, d, value, ms_step, clocks, e2e, launches, kernel_name, algo_bytes_rank, kernel_ms, peaks, peak_kind,
@@ -465,14 +471,15 @@ def emit(args, d, value, ms_step, clocks, e2e, launches, kernel_name, algo_bytes
         achieved = algo_bytes_rank / (kernel_ms * 1e-3) * 1e-9
         peak = float(peaks["hbm_gbs"])
         roof = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                "traffic": NCU_TRAFFIC.get(d["name"]), "kernel": kernel_name, "peak_source": f"{peak_kind} copy bandwidth",
+                "traffic": (NCU_TRAFFIC[d["name"]] / world if d["name"] in NCU_TRAFFIC else None), "kernel": kernel_name,
+                "peak_source": f"{peak_kind} copy bandwidth",
                 "algorithmic_bytes_per_launch": algo_bytes_rank, "frac_of_8TBs": achieved / 8000.0}
     else:
         # 3xTF32: three tensor-core products per fp32 product; dense TF32 peak taken as half the measured bf16 peak
         tf32_peak = float(peaks["bf16_tflops_sustained"]) / 2.0
         achieved = 3.0 * d["work"] / world / (kernel_ms * 1e-3) * 1e-12
         roof = {"bound": "tensor", "achieved": achieved, "peak": tf32_peak, "unit": "TFLOP/s", "frac": achieved / tf32_peak,
-                "traffic": NCU_TRAFFIC.get(d["name"]), "kernel": kernel_name,
+                "traffic": (NCU_TRAFFIC[d["name"]] / world if d["name"] in NCU_TRAFFIC else None), "kernel": kernel_name,
                 "peak_source": f"{peak_kind} bf16 sustained / 2 (TF32); achieved counts the 3 TF32 products per fp32 product"}
     line = {
         "metric": d["metric"], "value": value, "unit": d["unit"], "n_gpus": world, "steps": args.steps,
@@ -531,6 +538,30 @@ def cpu_baseline(d):
             "ms_per_step": el / reps * 1e3}
 
 
+def probe_gather(args, d):
+    """Yardstick for the SpMV: the same 8-byte index stream and the same random gathers of x, with a
+    plain 8-byte store per entry instead of the row reduction (a library kernel, not part of the product)."""
+    import torch
+    dev = torch.device("cuda:0")
+    x = torch.as_tensor(d["x"]).to(dev)
+    idx = torch.as_tensor(d["crd"]).to(dev)
+    out = torch.empty(idx.numel(), dtype=torch.float64, device=dev)
+    for _ in range(max(3, args.warmup)):
+        torch.index_select(x, 0, idx, out=out)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        torch.index_select(x, 0, idx, out=out)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    print(json.dumps({"probe": "gather", "entries": int(idx.numel()), "x_bytes": int(x.numel() * 8), "ms": ms,
+                      "gathers_per_s": idx.numel() / (ms * 1e-3),
+                      "stream_gbs": idx.numel() * 16 / (ms * 1e-3) * 1e-9}), flush=True)
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -541,6 +572,9 @@ def main():
     ap.add_argument("--small", action="store_true", help="reduced sizes (for profiler captures and quick checks)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiler captures)")
+    ap.add_argument("--probe", choices=["gather"], default=None,
+                    help="diagnostic instead of the benchmark: 'gather' times out[j] = x[crd[j]] over the SpMV "
+                         "workload's own index stream (torch.index_select), the cost of the x gathers alone")
     ap.add_argument("--shrink", type=int, default=0, help="divide the SpMV/SpMM row count by 2^SHRINK (profiler captures)")
     args = ap.parse_args()
     defaults = {"spmv": (500, 10), "spmm": (50, 5), "pcg": (200, 5), "bgemm": (200, 10), "gemm": (20, 3)}
@@ -569,6 +603,8 @@ def main():
         torch.cuda.set_device(local_rank)
         dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local_rank}"))
     d = make_workload(args.workload, args.small, args.shrink)
+    if args.probe == "gather":
+        return probe_gather(args, d)
     run_ours(args, d, rank, world, local_rank)
     if world > 1:
         # All ranks have reported; leave without communicator teardown (destroy_process_group() has

@@ -15,7 +15,12 @@
 //   warp 1      MMA issuer: per 8-wide k step three tcgen05.mma.kind::tf32 into the same
 //               accumulator: hi*hi + lo*hi + hi*lo (the lo*lo term is below fp32 rounding);
 //               tcgen05.commit releases the stage to the producer.
-//   warps 2-5   epilogue: tcgen05.ld the accumulator, add C_in, store C.
+//   warps 6-9   epilogue: tcgen05.ld the accumulator, add C_in, store C.
+//
+// Blocks are persistent (one per SM) and walk the output tiles; tensor memory holds two
+// accumulators, so the epilogue of one tile runs while the producer, split and MMA warps are
+// already in the main loop of the next (for the batched 128^3 problems the epilogue traffic is
+// as large as the operand traffic, so this overlap is what keeps HBM busy).
 //
 // Every mbarrier wait is bounded: after WAIT_LIMIT polls the thread records an error code
 // in a global flag and stops waiting, the block still frees its tensor memory and exits,
@@ -33,7 +38,8 @@ constexpr int A_BYTES = BM * BK * 4;       // 16 KB, rows of 128 B
 constexpr int B_BYTES = BK * BN * 4;       // 16 KB, four boxes of 32 k-rows x 128 B
 constexpr int BOX_BYTES = BK * 32 * 4;     // one B box: 32 k-rows x 32 columns
 constexpr int STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES;
-constexpr int THREADS = 192;
+constexpr int THREADS = 320;   // producer, MMA issuer, 4 split warps, 4 epilogue warps
+constexpr int TMEM_COLS = 2 * BN;  // two accumulators: the epilogue of a tile overlaps the next main loop
 constexpr uint32_t WAIT_LIMIT = 1u << 22;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
 
@@ -105,31 +111,34 @@ __device__ __forceinline__ void split_tf32(float4 &hi_lo_in_out, float4 &lo) {
   lo.w = x.w - __uint_as_float(__float_as_uint(x.w) & 0xFFFFE000u);
 }
 
-#ifdef LAPIS_TC_DEBUG
-__device__ float g_tc_dbg[4096];
-__device__ int g_tc_mode;
-__device__ __forceinline__ void mma_tf32_idesc(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
-      ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
-      : "memory");
+// Tile t of the persistent schedule -> (batch, m block, n block).  Within a batch entry the tiles
+// are walked in groups of 8 m-blocks so that the blocks running at the same time share A and B
+// panels in L2.
+struct TileCoord {
+  int batch, m0, n0;
+};
+__device__ __forceinline__ TileCoord tile_coord(int t, int tm, int tn) {
+  constexpr int GROUP = 8;
+  const int per = tm * tn;
+  const int batch = t / per, r = t - batch * per;
+  const int g = r / (GROUP * tn), first_m = g * GROUP;
+  const int gsize = tm - first_m < GROUP ? tm - first_m : GROUP;
+  const int q = r - g * GROUP * tn;
+  return TileCoord{batch, (first_m + q % gsize) * BM, (q / gsize) * BN};
 }
-#endif
 
 __global__ void __launch_bounds__(THREADS, 1)
 bgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                     float *__restrict__ C, int M, int N, int K, int *__restrict__ error_flag) {
+                     float *__restrict__ C, int M, int N, int K, int total_tiles, int *__restrict__ error_flag) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint64_t *bars = reinterpret_cast<uint64_t *>(smem + STAGES * STAGE_BYTES);
-  uint64_t *full = bars, *conv = bars + STAGES, *empty = bars + 2 * STAGES, *accum = bars + 3 * STAGES;
-  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 3 * STAGES + 1);
+  uint64_t *full = bars, *conv = bars + STAGES, *empty = bars + 2 * STAGES;
+  uint64_t *acc_full = bars + 3 * STAGES, *acc_empty = bars + 3 * STAGES + 2;
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 3 * STAGES + 4);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n0 = blockIdx.x * BN, m0 = blockIdx.y * BM, batch = blockIdx.z;
-  const int nk = K / BK;
+  const int nk = K / BK, tm = M / BM, tn = N / BN;
 
   auto stage_a = [&](int s) { return smem + s * STAGE_BYTES; };
   auto stage_alo = [&](int s) { return smem + s * STAGE_BYTES + A_BYTES; };
@@ -142,11 +151,15 @@ bgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
       mbar_init(&conv[s], 128);
       mbar_init(&empty[s], 1);
     }
-    mbar_init(accum, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&acc_full[i], 1);
+      mbar_init(&acc_empty[i], 128);
+    }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 1) {  // tensor memory: 128 columns of fp32 accumulators
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(128u)
+  if (warp == 1) {  // tensor memory: two accumulators of 128 fp32 columns
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"((uint32_t)TMEM_COLS)
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
@@ -156,113 +169,118 @@ bgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp == 0) {
-    // ---------------- TMA producer ----------------
+    // ---------------- TMA producer: runs ahead across tiles ----------------
     if (lane == 0) {
-      for (int kb = 0; kb < nk; ++kb) {
-        const int s = kb % STAGES;
-        if (!mbar_wait(&empty[s], ((kb / STAGES) & 1) ^ 1)) {
+      uint32_t g = 0;  // k blocks issued so far by this CTA
+      for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
+        const TileCoord tc = tile_coord(t, tm, tn);
+        bool ok = true;
+        for (int kb = 0; kb < nk; ++kb, ++g) {
+          const int s = g % STAGES;
+          ok = mbar_wait(&empty[s], ((g / STAGES) & 1) ^ 1);
+          if (!ok) break;
+          mbar_expect_tx(&full[s], A_BYTES + B_BYTES);
+          tma_load_3d(stage_a(s), &map_a, &full[s], kb * BK, tc.m0, tc.batch);
+#pragma unroll
+          for (int j = 0; j < BN / 32; ++j)
+            tma_load_3d(stage_b(s) + j * BOX_BYTES, &map_b, &full[s], tc.n0 + 32 * j, kb * BK, tc.batch);
+        }
+        if (!ok) {
           atomicExch(error_flag, 1);
           break;
         }
-        mbar_expect_tx(&full[s], A_BYTES + B_BYTES);
-        tma_load_3d(stage_a(s), &map_a, &full[s], kb * BK, m0, batch);
-#pragma unroll
-        for (int j = 0; j < BN / 32; ++j)
-          tma_load_3d(stage_b(s) + j * BOX_BYTES, &map_b, &full[s], n0 + 32 * j, kb * BK, batch);
       }
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
+      uint32_t g = 0, it = 0;
       bool ok = true;
-      for (int kb = 0; kb < nk && ok; ++kb) {
-        const int s = kb % STAGES;
-        ok = mbar_wait(&conv[s], (kb / STAGES) & 1);
-        if (!ok) {
-          atomicExch(error_flag, 2);
-          break;
-        }
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++it) {
+        const uint32_t buf = it & 1;
+        ok = mbar_wait(&acc_empty[buf], ((it >> 1) & 1) ^ 1);  // the epilogue has drained this accumulator
+        if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t a = smem_u32(stage_a(s)), alo = smem_u32(stage_alo(s));
-        const uint32_t b = smem_u32(stage_b(s)), blo = smem_u32(stage_blo(s));
-#ifdef LAPIS_TC_DEBUG
-        if (g_tc_mode == 1) {  // D = A A^T, both operands K-major
-          const uint32_t idesc_kk = IDESC & ~(1u << 16);
-          for (int ks = 0; ks < BK / 8; ++ks)
-            mma_tf32_idesc(tmem_base, desc_kmajor(a + ks * 32), desc_kmajor(a + ks * 32), idesc_kk, (kb > 0 || ks > 0) ? 1u : 0u);
-        } else if (g_tc_mode == 2) {  // only hi*hi
-          for (int ks = 0; ks < BK / 8; ++ks)
-            mma_tf32(tmem_base, desc_kmajor(a + ks * 32), desc_mnmajor(b + ks * 1024), (kb > 0 || ks > 0) ? 1u : 0u);
-        } else
-#endif
+        const uint32_t d_tmem = tmem_base + buf * BN;
+        for (int kb = 0; kb < nk; ++kb, ++g) {
+          const int s = g % STAGES;
+          ok = mbar_wait(&conv[s], (g / STAGES) & 1);
+          if (!ok) break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t a = smem_u32(stage_a(s)), alo = smem_u32(stage_alo(s));
+          const uint32_t b = smem_u32(stage_b(s)), blo = smem_u32(stage_blo(s));
 #pragma unroll
-        for (int ks = 0; ks < BK / 8; ++ks) {
-          const uint64_t da = desc_kmajor(a + ks * 32), dalo = desc_kmajor(alo + ks * 32);
-          const uint64_t db = desc_mnmajor(b + ks * 1024), dblo = desc_mnmajor(blo + ks * 1024);
-          mma_tf32(tmem_base, dalo, db, (kb > 0 || ks > 0) ? 1u : 0u);
-          mma_tf32(tmem_base, da, dblo, 1u);
-          mma_tf32(tmem_base, da, db, 1u);
+          for (int ks = 0; ks < BK / 8; ++ks) {
+            const uint64_t da = desc_kmajor(a + ks * 32), dalo = desc_kmajor(alo + ks * 32);
+            const uint64_t db = desc_mnmajor(b + ks * 1024), dblo = desc_mnmajor(blo + ks * 1024);
+            mma_tf32(d_tmem, dalo, db, (kb > 0 || ks > 0) ? 1u : 0u);
+            mma_tf32(d_tmem, da, dblo, 1u);
+            mma_tf32(d_tmem, da, db, 1u);
+          }
+          // releases the stage once the MMAs above have read it
+          asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                           smem_u32(&empty[s]))
+                       : "memory");
         }
-        // releases the stage once the MMAs above have read it
-        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(&empty[s]))
+        if (!ok) break;
+        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                         smem_u32(&acc_full[buf]))
                      : "memory");
       }
-      asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(accum))
-                   : "memory");
+      if (!ok) atomicExch(error_flag, 2);
     }
-  } else {
-    // ---------------- split (hi, lo), then epilogue ----------------
-    const int t = threadIdx.x - 64;  // 0..127
+  } else if (warp < 6) {
+    // ---------------- split x = hi + lo ----------------
+    const int t128 = threadIdx.x - 64;  // 0..127
+    uint32_t g = 0;
     bool ok = true;
-    for (int kb = 0; kb < nk && ok; ++kb) {
-      const int s = kb % STAGES;
-      ok = mbar_wait(&full[s], (kb / STAGES) & 1);
-      if (!ok) {
-        atomicExch(error_flag, 3);
-        break;
-      }
-      const float4 *a = reinterpret_cast<const float4 *>(stage_a(s));
-      float4 *alo = reinterpret_cast<float4 *>(stage_alo(s));
-      const float4 *b = reinterpret_cast<const float4 *>(stage_b(s));
-      float4 *blo = reinterpret_cast<float4 *>(stage_blo(s));
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      for (int kb = 0; kb < nk; ++kb, ++g) {
+        const int s = g % STAGES;
+        ok = mbar_wait(&full[s], (g / STAGES) & 1);
+        if (!ok) break;
+        const float4 *a = reinterpret_cast<const float4 *>(stage_a(s));
+        float4 *alo = reinterpret_cast<float4 *>(stage_alo(s));
+        const float4 *b = reinterpret_cast<const float4 *>(stage_b(s));
+        float4 *blo = reinterpret_cast<float4 *>(stage_blo(s));
 #pragma unroll
-      for (int i = 0; i < A_BYTES / 16 / 128; ++i) {
-        float4 x = a[t + 128 * i], lo;
-        split_tf32(x, lo);
-        alo[t + 128 * i] = lo;
-      }
-#pragma unroll
-      for (int i = 0; i < B_BYTES / 16 / 128; ++i) {
-        float4 x = b[t + 128 * i], lo;
-        split_tf32(x, lo);
-        blo[t + 128 * i] = lo;
-      }
-#ifdef LAPIS_TC_DEBUG
-      if (kb == 0 && blockIdx.x == 0 && blockIdx.y == 0) {
-        const float *af = reinterpret_cast<const float *>(stage_a(s));
-        const float *bf = reinterpret_cast<const float *>(stage_b(s));
-        for (int i = t; i < 1024; i += 128) {
-          g_tc_dbg[1024 + i] = af[i];
-          g_tc_dbg[2048 + i] = bf[i];
+        for (int i = 0; i < A_BYTES / 16 / 128; ++i) {
+          float4 x = a[t128 + 128 * i], lo;
+          split_tf32(x, lo);
+          alo[t128 + 128 * i] = lo;
         }
-        if (t == 0) g_tc_dbg[0] = __uint_as_float(tmem_base);
+#pragma unroll
+        for (int i = 0; i < B_BYTES / 16 / 128; ++i) {
+          float4 x = b[t128 + 128 * i], lo;
+          split_tf32(x, lo);
+          blo[t128 + 128 * i] = lo;
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> tensor-core reads
+        mbar_arrive(&conv[s]);
       }
-#endif
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> tensor-core reads
-      mbar_arrive(&conv[s]);
     }
-    // epilogue: accumulator row = TMEM lane; this warp may touch lanes 32*(warp%4)..+31
-    if (ok) ok = mbar_wait(accum, 0);
-    if (!ok) atomicExch(error_flag, 4);
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    if (ok) {
-      const int q = warp & 3;
-      const int row = m0 + 32 * q + lane;
-      float *crow = C + ((size_t)batch * M + row) * (size_t)N + n0;
+    if (!ok) atomicExch(error_flag, 3);
+  } else {
+    // ---------------- epilogue: overlaps the main loop of the next tile ----------------
+    // accumulator row = TMEM lane; a warp may touch lanes 32*(warp%4)..+31
+    const int q = warp & 3;
+    uint32_t it = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++it) {
+      const TileCoord tc = tile_coord(t, tm, tn);
+      const uint32_t buf = it & 1;
+      float *crow = C + ((size_t)tc.batch * M + tc.m0 + 32 * q + lane) * (size_t)N + tc.n0;
+      ok = mbar_wait(&acc_full[buf], (it >> 1) & 1);
+      if (!ok) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
+        float4 *dst = reinterpret_cast<float4 *>(crow + 32 * c);
+        float4 cin[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) cin[i] = dst[i];  // C_in in flight while the accumulator is read
         uint32_t r[32];
-        const uint32_t taddr = tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)(32 * c);
+        const uint32_t taddr = tmem_base + buf * BN + ((uint32_t)(32 * q) << 16) + (uint32_t)(32 * c);
         asm volatile(
             "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
             "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
@@ -273,29 +291,30 @@ bgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
               "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
             : "r"(taddr));
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#ifdef LAPIS_TC_DEBUG
-        if (t == 0 && c == 0 && blockIdx.x == 0 && blockIdx.y == 0)
-          for (int i = 0; i < 32; ++i) g_tc_dbg[32 + i] = __uint_as_float(r[i]);
-#endif
-        float4 *dst = reinterpret_cast<float4 *>(crow + 32 * c);
+        if (c == BN / 32 - 1) {  // the accumulator is in registers: hand it back to the MMA warp
+          asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+          mbar_arrive(&acc_empty[buf]);
+        }
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-          float4 cin = dst[i];
-          cin.x = __fadd_rn(__uint_as_float(r[4 * i + 0]), cin.x);
-          cin.y = __fadd_rn(__uint_as_float(r[4 * i + 1]), cin.y);
-          cin.z = __fadd_rn(__uint_as_float(r[4 * i + 2]), cin.z);
-          cin.w = __fadd_rn(__uint_as_float(r[4 * i + 3]), cin.w);
-          dst[i] = cin;
+          float4 o = cin[i];
+          o.x = __fadd_rn(__uint_as_float(r[4 * i + 0]), o.x);
+          o.y = __fadd_rn(__uint_as_float(r[4 * i + 1]), o.y);
+          o.z = __fadd_rn(__uint_as_float(r[4 * i + 2]), o.z);
+          o.w = __fadd_rn(__uint_as_float(r[4 * i + 3]), o.w);
+          dst[i] = o;
         }
       }
     }
+    if (!ok) atomicExch(error_flag, 4);
   }
 
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   if (warp == 1) {
     __syncwarp();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(128u) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)TMEM_COLS)
+                 : "memory");
   }
 }
 
@@ -339,9 +358,9 @@ static int *error_flag[64] = {nullptr};
 static bool attr_set[64] = {false};
 
 int bgemm_tcgen05_supported(int64_t batch, int64_t M, int64_t N, int64_t K) {
-  return batch >= 1 && batch <= 65535 && M >= tc::BM && N >= tc::BN && K >= tc::BK && M % tc::BM == 0 &&
-         N % tc::BN == 0 && K % tc::BK == 0 && M <= (1 << 30) && N <= (1 << 30) && K <= (1 << 30) &&
-         M / tc::BM <= 65535;
+  return batch >= 1 && M >= tc::BM && N >= tc::BN && K >= tc::BK && M % tc::BM == 0 && N % tc::BN == 0 &&
+         K % tc::BK == 0 && M <= (1 << 30) && N <= (1 << 30) && K <= (1 << 30) &&
+         batch * (M / tc::BM) * (N / tc::BN) < (1ll << 31) && batch < (1ll << 31);
 }
 
 int bgemm_tcgen05_launch(int64_t batch, int64_t M, int64_t N, int64_t K, const float *A, const float *B, float *C,
@@ -363,9 +382,10 @@ int bgemm_tcgen05_launch(int64_t batch, int64_t M, int64_t N, int64_t K, const f
                                         tc::SMEM_BYTES));
     attr_set[dev] = true;
   }
-  dim3 grid((unsigned)(N / tc::BN), (unsigned)(M / tc::BM), (unsigned)batch);
-  tc::bgemm_tcgen05_kernel<<<grid, tc::THREADS, tc::SMEM_BYTES, st>>>(map_a, map_b, C, (int)M, (int)N, (int)K,
-                                                                    error_flag[dev]);
+  const int64_t total = batch * (M / tc::BM) * (N / tc::BN);
+  const int64_t grid = total < sm_count() ? total : sm_count();  // persistent: one block per SM
+  tc::bgemm_tcgen05_kernel<<<(unsigned)grid, tc::THREADS, tc::SMEM_BYTES, st>>>(map_a, map_b, C, (int)M, (int)N, (int)K,
+                                                                              (int)total, error_flag[dev]);
   LAPIS_CUDA_TRY(cudaGetLastError());
   return LAPIS_OK;
 }
