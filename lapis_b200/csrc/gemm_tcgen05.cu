@@ -41,7 +41,9 @@ constexpr int STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES;
 constexpr int THREADS = 320;   // producer, MMA issuer, 4 split warps, 4 epilogue warps
 constexpr int TMEM_COLS = 2 * BN;  // two accumulators: the epilogue of a tile overlaps the next main loop
 constexpr uint32_t WAIT_LIMIT = 1u << 22;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr int EPI_PITCH = 36;                   // floats per staged epilogue row (conflict-free float4 access)
+constexpr int EPI_BYTES = 4 * 32 * EPI_PITCH * 4;  // one 32 x 32 staging tile per epilogue warp
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/ + EPI_BYTES;
 
 // instruction descriptor: D = f32, A = B = tf32, A K-major, B MN-major, N = 128, M = 128
 constexpr uint32_t IDESC = (1u << 4) | (2u << 7) | (2u << 10) | (0u << 15) | (1u << 16) |
@@ -264,21 +266,23 @@ bgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
     // ---------------- epilogue: overlaps the main loop of the next tile ----------------
     // accumulator row = TMEM lane; a warp may touch lanes 32*(warp%4)..+31
     const int q = warp & 3;
+    float *stile = reinterpret_cast<float *>(smem + STAGES * STAGE_BYTES + 256) + (warp - 6) * 32 * EPI_PITCH;
     uint32_t it = 0;
     bool ok = true;
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++it) {
       const TileCoord tc = tile_coord(t, tm, tn);
       const uint32_t buf = it & 1;
-      float *crow = C + ((size_t)tc.batch * M + tc.m0 + 32 * q + lane) * (size_t)N + tc.n0;
+      float *cwarp = C + ((size_t)tc.batch * M + tc.m0 + 32 * q) * (size_t)N + tc.n0;  // this warp's 32 rows
       ok = mbar_wait(&acc_full[buf], (it >> 1) & 1);
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
-        float4 *dst = reinterpret_cast<float4 *>(crow + 32 * c);
+        // C_in chunk (32 rows x 32 columns), coalesced: 8 lanes cover the 128 bytes of one row
         float4 cin[8];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) cin[i] = dst[i];  // C_in in flight while the accumulator is read
+        for (int i = 0; i < 8; ++i)
+          cin[i] = *reinterpret_cast<const float4 *>(cwarp + (size_t)(4 * i + (lane >> 3)) * N + 32 * c + 4 * (lane & 7));
         uint32_t r[32];
         const uint32_t taddr = tmem_base + buf * BN + ((uint32_t)(32 * q) << 16) + (uint32_t)(32 * c);
         asm volatile(
@@ -295,14 +299,24 @@ bgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
           asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
           mbar_arrive(&acc_empty[buf]);
         }
+        // thread = row in tensor memory; transpose through shared memory so that stores are coalesced
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          *reinterpret_cast<float4 *>(stile + lane * EPI_PITCH + 4 * i) =
+              make_float4(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]), __uint_as_float(r[4 * i + 2]),
+                          __uint_as_float(r[4 * i + 3]));
+        __syncwarp();
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
+          const int row = 4 * i + (lane >> 3);
+          const float4 a = *reinterpret_cast<const float4 *>(stile + row * EPI_PITCH + 4 * (lane & 7));
           float4 o = cin[i];
-          o.x = __fadd_rn(__uint_as_float(r[4 * i + 0]), o.x);
-          o.y = __fadd_rn(__uint_as_float(r[4 * i + 1]), o.y);
-          o.z = __fadd_rn(__uint_as_float(r[4 * i + 2]), o.z);
-          o.w = __fadd_rn(__uint_as_float(r[4 * i + 3]), o.w);
-          dst[i] = o;
+          o.x = __fadd_rn(a.x, o.x);
+          o.y = __fadd_rn(a.y, o.y);
+          o.z = __fadd_rn(a.z, o.z);
+          o.w = __fadd_rn(a.w, o.w);
+          *reinterpret_cast<float4 *>(cwarp + (size_t)row * N + 32 * c + 4 * (lane & 7)) = o;
         }
       }
     }

@@ -503,12 +503,9 @@ __global__ void spmv_fixup_kernel(const I *__restrict__ pos, const int64_t *__re
 // row is fetched as one coalesced 512-byte request and every output element is
 // summed in ascending j by a single lane: bit-identical to the sequential row
 // loop (examples/bspmm.py:15-23, spmm_dcsr_opdsl.py:132-135 outer-loop-only
-// parallelism).  Eight B rows are in flight per warp.
+// parallelism).  Four B rows are in flight per warp.
 // ---------------------------------------------------------------------------
-constexpr int SPMM_WARPS = 8;
-constexpr int SPMM_UNROLL = 8;
-
-template <typename I, bool VEC2>
+template <typename I, bool VEC2, int SPMM_WARPS, int SPMM_UNROLL>
 __global__ void __launch_bounds__(SPMM_WARPS * 32)
 spmm_row_kernel(const I *__restrict__ pos, const I *__restrict__ crd, const double *__restrict__ val,
                 int64_t nrows, int64_t k, const double *__restrict__ B, double *__restrict__ C,
@@ -704,17 +701,35 @@ int spmv_launch(const lapis_b200_csr *h, const double *x, double *y, int accumul
   return launch_spmv<int64_t>(h, x, y, accumulate, dotvec, blk_partial, skip_flag, st);
 }
 
+template <typename I, int WARPS, int UNROLL>
+static void launch_spmm_variant(const lapis_b200_csr *h, int64_t k, const double *B, double *C, int accumulate,
+                                cudaStream_t st) {
+  const I *pos = static_cast<const I *>(h->pos);
+  const I *crd = static_cast<const I *>(h->crd);
+  const unsigned grid = (unsigned)((h->nrows + WARPS - 1) / WARPS);
+  const bool vec2 = (k % 2 == 0) && ((reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) % 16 == 0);
+  if (vec2)
+    spmm_row_kernel<I, true, WARPS, UNROLL><<<grid, WARPS * 32, 0, st>>>(pos, crd, h->val, h->nrows, k, B, C, accumulate);
+  else
+    spmm_row_kernel<I, false, WARPS, UNROLL><<<grid, WARPS * 32, 0, st>>>(pos, crd, h->val, h->nrows, k, B, C, accumulate);
+}
+
+// B rows in flight per warp (UNROLL) against resident warps: LAPIS_B200_SPMM="warps,unroll" picks a variant.
 template <typename I>
 static int launch_spmm(const lapis_b200_csr *h, int64_t k, const double *B, double *C, int accumulate,
                        cudaStream_t st) {
-  const I *pos = static_cast<const I *>(h->pos);
-  const I *crd = static_cast<const I *>(h->crd);
-  const unsigned grid = (unsigned)((h->nrows + SPMM_WARPS - 1) / SPMM_WARPS);
-  const bool vec2 = (k % 2 == 0) && ((reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) % 16 == 0);
-  if (vec2)
-    spmm_row_kernel<I, true><<<grid, SPMM_WARPS * 32, 0, st>>>(pos, crd, h->val, h->nrows, k, B, C, accumulate);
-  else
-    spmm_row_kernel<I, false><<<grid, SPMM_WARPS * 32, 0, st>>>(pos, crd, h->val, h->nrows, k, B, C, accumulate);
+  static const int variant = [] {
+    int w = 8, u = 4;
+    if (const char *e = std::getenv("LAPIS_B200_SPMM")) sscanf(e, "%d,%d", &w, &u);
+    return w * 100 + u;
+  }();
+  // Measured on the 2^21-row, 32-per-row, k = 64 case: (8,4) 6.6 ms, (16,4) 6.7 ms, (8,8) 10.0 ms:
+  // four 512-byte rows in flight per warp at 64 registers (4 blocks per SM) beat eight at 80.
+  switch (variant) {
+    case 808: launch_spmm_variant<I, 8, 8>(h, k, B, C, accumulate, st); break;
+    case 1604: launch_spmm_variant<I, 16, 4>(h, k, B, C, accumulate, st); break;
+    default: launch_spmm_variant<I, 8, 4>(h, k, B, C, accumulate, st); break;
+  }
   LAPIS_CUDA_TRY(cudaGetLastError());
   return LAPIS_OK;
 }
