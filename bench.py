@@ -140,6 +140,11 @@ def make_workload(name: str, small: bool, shrink: int = 0):
         n, nnz = d["shape"][0], int(d["crd"].size)
         d.update(unit="GB/s", metric="csr_spmv_hbm_gbs", dtype="f64", unit_scale=1e-9,
                  work=w.spmv_bytes(n, n, nnz, 8), label=f"CSR SpMV fp64 power-law rows (config 2): {n} rows, {nnz} nnz, int64 indices")
+    elif name == "spmv1":
+        d = w.spmv_uniform(10_000, 10, np.int64)
+        n, nnz = d["shape"][0], int(d["crd"].size)
+        d.update(unit="GB/s", metric="csr_spmv_hbm_gbs", dtype="f64", unit_scale=1e-9, work=w.spmv_bytes(n, n, nnz, 8),
+                 label=f"CSR SpMV fp64 (config 1): {n} rows, 10 nnz/row, int64 indices; 1.84 MB, launch-latency bound")
     elif name == "spmm":
         d = w.spmm_uniform(1 << 13 if small else (1 << 21) >> shrink)
         n, nnz = d["shape"][0], int(d["crd"].size)
@@ -178,13 +183,13 @@ def run_reference(args, d):
     threads = host_threads()
     name = d["name"]
     budget_s = 120.0
-    if name in ("spmv", "spmm"):
+    if name in ("spmv", "spmv1", "spmm"):
         pos, crd, val = d["pos"], d["crd"], d["val"]
         n = len(pos) - 1
 
         def make_step(rows):
             p = np.ascontiguousarray(pos[:rows + 1])
-            if name == "spmv":
+            if name != "spmm":
                 y = np.zeros(rows)
                 return lambda: oracle.spmv_inplace(p, crd, val, d["x"], y, threads, native)
             C = np.zeros((rows, 64))
@@ -322,21 +327,21 @@ def run_ours(args, d, rank, world, local_rank):
             ms = float(t.item())
         return ms, clocks
 
-    launches_per_step = 2 if args.workload == "spmv" else 1  # SpMV: chunk kernel + carry fix-up
+    launches_per_step = 2 if args.workload in ("spmv", "spmv1") else 1  # SpMV: chunk kernel + carry fix-up
     e2e = None
     kernel_name = ""
     extra_cfg = {}
-    if name in ("spmv", "spmm"):
+    if name in ("spmv", "spmv1", "spmm"):
         pos, crd, val = d["pos"], d["crd"], d["val"]
         n = len(pos) - 1
         bounds = part.partition_rows(pos, world)
         r0, r1 = int(bounds[rank]), int(bounds[rank + 1])
         lpos, lcrd, lval = part.row_block(pos, crd, val, r0, r1)
-        A = D.CsrMatrix.from_host(lpos, lcrd, lval, (r1 - r0, n), dev, tune=True)
-        extra_cfg_kernel = A.tune()
+        A = D.CsrMatrix.from_host(lpos, lcrd, lval, (r1 - r0, n), dev)
+        extra_cfg_kernel = A.tune() if name != "spmm" else (0, 0)  # per-matrix choice of the SpMV kernel
         extra_cfg = {"partition": "contiguous row blocks, equal nnz", "rows_rank0": int(bounds[1] - bounds[0]),
-                     "replicated": "x" if name == "spmv" else "B", "spmv_kernel_tuned": list(extra_cfg_kernel)}
-        if name == "spmv":
+                     "replicated": "B" if name == "spmm" else "x", "spmv_kernel_tuned": list(extra_cfg_kernel)}
+        if name != "spmm":
             xd = torch.as_tensor(d["x"]).to(dev)
             yd = torch.zeros(r1 - r0, dtype=torch.float64, device=dev)
             step = lambda: A.spmv(xd, yd, accumulate=False)
@@ -352,11 +357,11 @@ def run_ours(args, d, rank, world, local_rank):
             module = KB.KokkosBackend(decompose_tensors=True).compile(mm.spmm(mm.CSR64))
         # ---- e2e through the emitted-module ABI with pinned host buffers -------------
         pinned = [torch.as_tensor(np.ascontiguousarray(a)).pin_memory() for a in host_in]
-        out_shape = (r1 - r0,) if name == "spmv" else (r1 - r0, 64)
+        out_shape = (r1 - r0, 64) if name == "spmm" else (r1 - r0,)
         out = torch.zeros(out_shape, dtype=torch.float64).pin_memory()
         pnp = [t.numpy() for t in pinned]
         spec = ((r1 - r0, n), (len(lpos), len(lcrd), len(lval)))
-        fn = module.spmv if name == "spmv" else module.spmm
+        fn = module.spmm if name == "spmm" else module.spmv
 
         def e2e_step():
             fn(pnp[0], pnp[1], pnp[2], spec, pnp[3], out.numpy())
@@ -379,9 +384,9 @@ def run_ours(args, d, rank, world, local_rank):
         if e2e_steps:
             e2e = {"value": d["work"] * e2e_steps / t_e2e * d["unit_scale"], "unit": d["unit"],
                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps,
-                   "api": f"KokkosBackend.compile(...).{name} -> py_{name}_f64_i64, pinned host buffers"}
+                   "api": f"KokkosBackend.compile(...).{fn.__name__} -> py_{fn.__name__}_f64_i64, pinned host buffers"}
         del pinned, out
-        algo_bytes_rank = (len(lcrd) * 16 + len(lpos) * 8 + (8 * n + 8 * (r1 - r0)) * (1 if name == "spmv" else 64))
+        algo_bytes_rank = (len(lcrd) * 16 + len(lpos) * 8 + (8 * n + 8 * (r1 - r0)) * (64 if name == "spmm" else 1))
     elif name == "pcg":
         from lapis_b200.dist import DistPcg
         n = d["shape"][0]
@@ -391,10 +396,9 @@ def run_ours(args, d, rank, world, local_rank):
         def solve(k):
             state["out"] = solver.solve(0.0, k, check_every=50)
 
-        # the timed region is one solve of K iterations; warm-up is a solve of W iterations
-        solver_w = DistPcg(d["pos"], d["crd"], d["val"], (n, n), d["b"], d["dinv"], dev, use_graph=True)
-        solver_w.solve(0.0, max(1, args.warmup))
-        solver.solve(0.0, args.steps)  # captures the graph; timed run below replays it
+        # The timed region is one solve of K iterations.  Warm-up is a whole untimed solve with the same
+        # solver (it also captures the CUDA graph of one iteration that the timed solve replays).
+        solver.solve(0.0, args.steps)
         kernel_name = "spmv_pipe_kernel|spmv_chunk_kernel (pass A) + pcg_update_kernel + pcg_direction_kernel"
         launches_per_step = 6 if world == 1 else 8
         steps_holder = {"k": args.steps}
@@ -447,7 +451,7 @@ def run_ours(args, d, rank, world, local_rank):
     ms, clocks = timed(step, args.steps, args.warmup)
     ms_step = ms / args.steps
     value = d["work"] / (ms_step * 1e-3) * d["unit_scale"]
-    bound = "hbm" if name in ("spmv", "spmm", "bgemm") else "tensor"
+    bound = "tensor" if name == "gemm" else "hbm"
     emit(args, d, value, ms_step, clocks, e2e, launches_per_step * args.steps * world, kernel_name, algo_bytes_rank,
          ms_step, peaks, peak_kind, world, rank, extra_cfg, bound=bound)
 
@@ -499,7 +503,7 @@ def cpu_baseline(d):
     threads = host_threads()
     name = d["name"]
     budget = 15.0
-    if name == "spmv":
+    if name in ("spmv", "spmv1"):
         y = np.zeros(len(d["pos"]) - 1)
         step = lambda: oracle.spmv_inplace(d["pos"], d["crd"], d["val"], d["x"], y, threads, native)
         work, sample = d["work"], "the whole matrix, repeated"
@@ -567,7 +571,7 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=None)
     ap.add_argument("--warmup", type=int, default=None)
-    ap.add_argument("--workload", default="spmv", choices=["spmv", "spmm", "pcg", "bgemm", "gemm"])
+    ap.add_argument("--workload", default="spmv", choices=["spmv", "spmv1", "spmm", "pcg", "bgemm", "gemm"])
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--small", action="store_true", help="reduced sizes (for profiler captures and quick checks)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -577,7 +581,7 @@ def main():
                          "workload's own index stream (torch.index_select), the cost of the x gathers alone")
     ap.add_argument("--shrink", type=int, default=0, help="divide the SpMV/SpMM row count by 2^SHRINK (profiler captures)")
     args = ap.parse_args()
-    defaults = {"spmv": (500, 10), "spmm": (50, 5), "pcg": (200, 5), "bgemm": (200, 10), "gemm": (20, 3)}
+    defaults = {"spmv": (500, 10), "spmv1": (1000, 10), "spmm": (50, 5), "pcg": (200, 5), "bgemm": (200, 10), "gemm": (20, 3)}
     if args.steps is None:
         args.steps = defaults[args.workload][0] if args.impl == "ours" else 10
     if args.warmup is None:
