@@ -14,19 +14,22 @@
 //     products in shared memory.  All in-chunk indexing is 32-bit.
 //   * A per-matrix plan (8 bytes per chunk, one binary search each) gives the first
 //     row that ends inside each chunk.  Rows that end in the chunk are reduced out
-//     of shared memory: rows of up to 32 entries by groups of L lanes (L = 1..8 from
-//     the chunk's average row length) with warp shuffles, longer rows by a whole warp
-//     in a second pass, so one long row among short ones does not serialise a thread.
+//     of shared memory: rows of up to 32 in-chunk entries by one lane each, in the
+//     sequential CPU order (measured: more lanes per short row only add instructions),
+//     longer rows by a whole warp in a second pass, so one long row among short ones
+//     does not serialise a thread.
 //   * A row that runs past the end of its chunk leaves its partial sum in carry[b];
 //     a tiny second kernel adds the carries to the row's y in chunk order.  No
 //     atomics on the data path: results are run-to-run identical.
 //
 // Arithmetic: products and sums use explicit round-to-nearest multiplies and adds
 // (no FMA contraction), as the emitted code has separate arith.mulf / arith.addf.
-// The summation order inside a row differs from the sequential CPU order when more
-// than one lane or chunk takes part (documented tolerance 1e-12 of the row's
-// magnitude); a row summed by one lane inside one chunk is bit-identical to it.
+// A row of up to 32 entries that lies inside one chunk is summed exactly like the
+// sequential CPU loop (identical bits).  Rows handled by a warp, and rows cut by a chunk
+// boundary, are summed in another fixed order (documented tolerance 1e-12 of the row's
+// magnitude).
 #include <cstdlib>
+#include <cstring>
 
 #include "common.h"
 
@@ -121,9 +124,9 @@ __device__ __forceinline__ int rel_at(const ChunkCtx &c, const int *s_rel, const
 
 // Stores one finished in-chunk row sum: y for rows ending here, carry for the tail row.
 template <bool FUSE_DOT>
-__device__ __forceinline__ void finish_row(const ChunkCtx &c, int i, int s, double acc, double yin,
+__device__ __forceinline__ void finish_row(const ChunkCtx &c, int i, int s, double acc, double yin, double dv,
                                            double *__restrict__ y, double *__restrict__ carry,
-                                           const double *__restrict__ dotvec, double &dot_local, int chunk) {
+                                           double &dot_local, int chunk) {
   const int64_t r = c.row0 + i;
   if (c.has_tail && i == c.nr - 1) {
     if (s >= c.len) return;  // the row starts beyond this chunk: not ours
@@ -131,7 +134,7 @@ __device__ __forceinline__ void finish_row(const ChunkCtx &c, int i, int s, doub
   } else {
     y[r] = __dadd_rn(acc, yin);
   }
-  if (FUSE_DOT) dot_local = __dadd_rn(dot_local, __dmul_rn(acc, dotvec[r]));
+  if (FUSE_DOT) dot_local = __dadd_rn(dot_local, __dmul_rn(acc, dv));
 }
 
 template <typename I, int THREADS, int L, bool FUSE_DOT>
@@ -145,7 +148,7 @@ __device__ __forceinline__ void reduce_short_rows(const ChunkCtx &c, const int *
   for (int ib = 0; ib < c.nr; ib += NGRP) {
     const int i = ib + grp;
     const bool valid = i < c.nr;
-    double acc = 0.0, yin = 0.0;
+    double acc = 0.0, yin = 0.0, dv = 0.0;
     int s = 0, e = 0;
     bool is_long = false;
     if (valid) {
@@ -153,6 +156,7 @@ __device__ __forceinline__ void reduce_short_rows(const ChunkCtx &c, const int *
       e = rel_at<I>(c, s_rel, pos, i + 1);
       is_long = (e - s) > SPMV_LONG_ROW;
       if (accumulate && lane == 0 && !is_long && !(c.has_tail && i == c.nr - 1)) yin = y[c.row0 + i];
+      if (FUSE_DOT && lane == 0 && !is_long) dv = dotvec[c.row0 + i];  // in flight while the row is summed
       if (!is_long)
         for (int j = s + lane; j < e; j += L) acc = __dadd_rn(acc, s_prod[j]);
     }
@@ -162,7 +166,7 @@ __device__ __forceinline__ void reduce_short_rows(const ChunkCtx &c, const int *
       if (is_long)
         s_long[atomicAdd(s_nlong, 1)] = i;  // order of the list does not matter: rows are independent
       else
-        finish_row<FUSE_DOT>(c, i, s, acc, yin, y, carry, dotvec, dot_local, chunk);
+        finish_row<FUSE_DOT>(c, i, s, acc, yin, dv, y, carry, dot_local, chunk);
     }
   }
 }
@@ -242,19 +246,8 @@ spmv_chunk_kernel(const I *__restrict__ pos, const I *__restrict__ crd, const do
 
   // ---- pass 1: rows of up to SPMV_LONG_ROW in-chunk entries, L lanes per row --------
   double dot_local = 0.0;
-  const int avg = c.len / (c.nr > 0 ? c.nr : 1);
-#define LAPIS_REDUCE(LANES)                                                                                   \
-  reduce_short_rows<I, THREADS, LANES, FUSE_DOT>(c, s_rel, pos, s_prod, s_long, &s_nlong, y, accumulate, carry, \
-                                                 dotvec, dot_local, (int)blockIdx.x)
-  if (avg <= 4)
-    LAPIS_REDUCE(1);
-  else if (avg <= 8)
-    LAPIS_REDUCE(2);
-  else if (avg <= 16)
-    LAPIS_REDUCE(4);
-  else
-    LAPIS_REDUCE(8);
-#undef LAPIS_REDUCE
+  reduce_short_rows<I, THREADS, 1, FUSE_DOT>(c, s_rel, pos, s_prod, s_long, &s_nlong, y, accumulate, carry, dotvec,
+                                             dot_local, (int)blockIdx.x);
   __syncthreads();
 
   // ---- pass 2: long rows, one warp each -------------------------------------------------
@@ -263,13 +256,14 @@ spmv_chunk_kernel(const I *__restrict__ pos, const I *__restrict__ crd, const do
   for (int q = warp; q < nlong; q += THREADS / 32) {
     const int i = s_long[q];
     const int s = rel_at<I>(c, s_rel, pos, i), e = rel_at<I>(c, s_rel, pos, i + 1);
-    double yin = 0.0;
+    double yin = 0.0, dv = 0.0;
     if (accumulate && lane == 0 && !(c.has_tail && i == c.nr - 1)) yin = y[c.row0 + i];
+    if (FUSE_DOT && lane == 0) dv = dotvec[c.row0 + i];
     double acc = 0.0;
     for (int j = s + lane; j < e; j += 32) acc = __dadd_rn(acc, s_prod[j]);
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) acc = __dadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, off));
-    if (lane == 0) finish_row<FUSE_DOT>(c, i, s, acc, yin, y, carry, dotvec, dot_local, (int)blockIdx.x);
+    if (lane == 0) finish_row<FUSE_DOT>(c, i, s, acc, yin, dv, y, carry, dot_local, (int)blockIdx.x);
   }
 
   if (FUSE_DOT) {
@@ -429,32 +423,22 @@ spmv_pipe_kernel(const I *__restrict__ pos, const I *__restrict__ crd, const dou
     __syncthreads();
 
     // ---- rows ending in this chunk (same two passes as the one-chunk-per-block kernel) ------
-    const int avg = c.len / (c.nr > 0 ? c.nr : 1);
-#define LAPIS_REDUCE(LANES)                                                                               \
-  reduce_short_rows<I, THREADS, LANES, FUSE_DOT>(c, s_rel, pos, prod, s_long, s_nlong, y, accumulate, carry, \
-                                                 dotvec, dot_local, (int)b)
-    if (avg <= 4)
-      LAPIS_REDUCE(1);
-    else if (avg <= 8)
-      LAPIS_REDUCE(2);
-    else if (avg <= 16)
-      LAPIS_REDUCE(4);
-    else
-      LAPIS_REDUCE(8);
-#undef LAPIS_REDUCE
+    reduce_short_rows<I, THREADS, 1, FUSE_DOT>(c, s_rel, pos, prod, s_long, s_nlong, y, accumulate, carry, dotvec,
+                                               dot_local, (int)b);
     __syncthreads();
     const int nlong = *s_nlong;
     const int warp = tid >> 5, lane = tid & 31;
     for (int q = warp; q < nlong; q += THREADS / 32) {
       const int i = s_long[q];
       const int s0 = rel_at<I>(c, s_rel, pos, i), e0 = rel_at<I>(c, s_rel, pos, i + 1);
-      double yin = 0.0;
+      double yin = 0.0, dv = 0.0;
       if (accumulate && lane == 0 && !(c.has_tail && i == c.nr - 1)) yin = y[c.row0 + i];
+      if (FUSE_DOT && lane == 0) dv = dotvec[c.row0 + i];
       double acc = 0.0;
       for (int j = s0 + lane; j < e0; j += 32) acc = __dadd_rn(acc, prod[j]);
 #pragma unroll
       for (int off = 16; off > 0; off >>= 1) acc = __dadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, off));
-      if (lane == 0) finish_row<FUSE_DOT>(c, i, s0, acc, yin, y, carry, dotvec, dot_local, (int)b);
+      if (lane == 0) finish_row<FUSE_DOT>(c, i, s0, acc, yin, dv, y, carry, dot_local, (int)b);
     }
     // the next bulk copy into this stage must not overtake these shared-memory accesses
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -900,7 +884,7 @@ extern "C" int lapis_b200_spmv_status(void *stream) {
 }
 
 extern "C" int lapis_b200_csr_destroy(lapis_b200_csr_t h) {
-  clear_error();
+  // does not touch the recorded status: it runs while an error of the enclosing call unwinds
   if (h == nullptr) return LAPIS_OK;
   cudaFree(h->blk_row);
   cudaFree(h->blk_partial);
