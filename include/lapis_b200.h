@@ -219,6 +219,15 @@ int lapis_b200_pcg_step_direction(void *d_work, int64_t n, int64_t n_p, int64_t 
 /* Copies {done, iters, relres} to the host; synchronises `stream`. */
 int lapis_b200_pcg_status(void *d_work, int *done, uint64_t *iters, double *relres, void *stream);
 
+/* MatrixMarket coordinate file -> CSR on the host (ascending columns per row, duplicates summed,
+ * symmetric / skew-symmetric storage expanded, pattern entries = 1): the format step in front of the
+ * SpMV path, done in the reference's benchmark by the KokkosSparse reader vendored beside
+ * benchmarks/spmv/main.cpp (:36-38).  The three arrays are allocated here; release each with
+ * lapis_b200_mm_free. */
+int lapis_b200_read_matrix_market(const char *path, int idx_bytes, int64_t *nrows, int64_t *ncols, int64_t *nnz,
+                                  void **pos, void **crd, double **val);
+void lapis_b200_mm_free(void *p);
+
 /* nnz-balanced contiguous row partition of a CSR matrix over G devices (host
  * arrays): bounds[g] = first row whose start offset is >= pos[0] + g*nnz/G,
  * bounds[G] = nrows.  The reference has no multi-device path; this is the

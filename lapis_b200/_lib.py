@@ -58,6 +58,10 @@ _PROTOS = {
     "lapis_b200_pcg_step_update": (c_int, [c_vp, c_i64, c_i64, c_i64, c_vp, c_vp, c_int, c_dbl, c_u64, c_vp]),
     "lapis_b200_pcg_step_direction": (c_int, [c_vp, c_i64, c_i64, c_i64, c_vp]),
     "lapis_b200_pcg_status": (c_int, [c_vp, ctypes.POINTER(c_int), ctypes.POINTER(c_u64), ctypes.POINTER(c_dbl), c_vp]),
+    "lapis_b200_read_matrix_market": (c_int, [ctypes.c_char_p, c_int, ctypes.POINTER(c_i64), ctypes.POINTER(c_i64),
+                                              ctypes.POINTER(c_i64), ctypes.POINTER(c_vp), ctypes.POINTER(c_vp),
+                                              ctypes.POINTER(c_vp)]),
+    "lapis_b200_mm_free": (None, [c_vp]),
     "lapis_b200_partition_rows": (c_int, [c_int, c_i64, c_vp, c_int, c_vp]),
 }
 

@@ -145,6 +145,32 @@ def test_spmv_matches_oracle(idx, case, spmv_kernel):
         assert np.array_equal(yd.cpu().numpy()[short], oracle.spmv(pos, crd, val, x, y0)[short])
 
 
+def test_spmv_random_shapes_property():
+    """Random small CSR shapes (hypothesis): empty rows, rows longer than a warp's threshold, rows cut by the
+    2048-entry chunk boundary, ncols == 1, int32 and int64 -- all against the oracle."""
+    from hypothesis import given, settings, strategies as st
+    from lapis_b200.device import CsrMatrix
+    dev = _dev()
+
+    @settings(max_examples=40, deadline=None)
+    @given(lens=st.lists(st.one_of(st.integers(0, 6), st.integers(0, 90), st.just(2500)), min_size=1, max_size=400),
+           ncols=st.sampled_from([1, 7, 64, 3000]), wide=st.booleans(), seed=st.integers(0, 2 ** 16), acc=st.booleans())
+    def run(lens, ncols, wide, seed, acc):
+        rng = np.random.default_rng(seed)
+        lens = np.minimum(np.array(lens, dtype=np.int64), ncols)
+        idx = np.int64 if wide else np.int32
+        pos, crd, val = _random_csr(rng, lens, ncols, idx)
+        x = rng.uniform(-1, 1, ncols)
+        y0 = rng.uniform(-1, 1, len(lens))
+        A = CsrMatrix.from_host(pos, crd, val, (len(lens), ncols), dev)
+        yd = torch.as_tensor(y0).to(dev)
+        A.spmv(torch.as_tensor(x).to(dev), yd, accumulate=acc)
+        y_in = y0 if acc else np.zeros(len(lens))
+        _assert_spmv_close(yd.cpu().numpy(), oracle.spmv(pos, crd, val, x, y_in), _row_scale(pos, crd, val, x, y_in))
+
+    run()
+
+
 def test_spmv_tuning_keeps_the_bits():
     """Every kernel variant sums a row in the same order, so the tuned choice changes speed only."""
     from lapis_b200.device import CsrMatrix
