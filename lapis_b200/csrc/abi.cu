@@ -133,13 +133,21 @@ template <typename I>
 static int upload_csr(const lapis_memref1 *pos, const lapis_memref1 *crd, const lapis_memref1 *val, const CsrArgs &a,
                       DeviceCsr *d, cudaStream_t st) {
   const I *hpos = elem_ptr<I>(pos);
-  LAPIS_TRY(check_pos_host<I>(hpos, a.nrows, a.nnz));
   LAPIS_TRY(d->pos.alloc((size_t)a.npos * sizeof(I)));
   LAPIS_TRY(d->crd.alloc((size_t)a.nnz * sizeof(I)));
   LAPIS_TRY(d->val.alloc((size_t)a.nnz * sizeof(double)));
   LAPIS_CUDA_TRY(cudaMemcpyAsync(d->pos.p, hpos, (size_t)a.npos * sizeof(I), cudaMemcpyHostToDevice, st));
   LAPIS_CUDA_TRY(cudaMemcpyAsync(d->crd.p, elem_ptr<I>(crd), (size_t)a.nnz * sizeof(I), cudaMemcpyHostToDevice, st));
   LAPIS_CUDA_TRY(cudaMemcpyAsync(d->val.p, elem_ptr<double>(val), (size_t)a.nnz * sizeof(double), cudaMemcpyHostToDevice, st));
+  // validated on the host while the copies are in flight (they are asynchronous from pinned memory);
+  // no kernel has been given the offsets yet
+  if (check_pos_host<I>(hpos, a.nrows, a.nnz) != LAPIS_OK) {
+    const int code = lapis_last_error();
+    char msg[512];
+    snprintf(msg, sizeof(msg), "%s", lapis_last_error_message());
+    cudaStreamSynchronize(st);
+    return fail(code, "%s", msg);
+  }
   return lapis_b200_csr_create(&d->h, (int)sizeof(I), a.nrows, a.ncols, d->pos.p, d->crd.p,
                                static_cast<const double *>(d->val.p), st);
 }

@@ -13,7 +13,8 @@
 //               fp32 (its top 19 bits) and lo = x - hi (exact), written to a second pair of
 //               buffers; fence.proxy.async, then arrive.
 //   warp 1      MMA issuer: per 8-wide k step three tcgen05.mma.kind::tf32 into the same
-//               accumulator: hi*hi + lo*hi + hi*lo (the lo*lo term is below fp32 rounding);
+//               accumulator: hi*hi (issued as soon as TMA has landed, overlapping the split),
+//               then lo*hi and hi*lo (the lo*lo term is below fp32 rounding);
 //               tcgen05.commit releases the stage to the producer.
 //   warps 6-9   epilogue: tcgen05.ld the accumulator, add C_in, store C.
 //
@@ -27,27 +28,44 @@
 // and the host turns the flag into LAPIS_ECUDA.
 #include <cuda.h>
 
+#include <cstdlib>
+
 #include "common.h"
 
 namespace lapis_b200 {
 
 namespace tc {
 
-constexpr int BM = 128, BN = 128, BK = 32, STAGES = 3;
-constexpr int A_BYTES = BM * BK * 4;       // 16 KB, rows of 128 B
-constexpr int B_BYTES = BK * BN * 4;       // 16 KB, four boxes of 32 k-rows x 128 B
-constexpr int BOX_BYTES = BK * 32 * 4;     // one B box: 32 k-rows x 32 columns
-constexpr int STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES;
-constexpr int THREADS = 320;   // producer, MMA issuer, 4 split warps, 4 epilogue warps
-constexpr int TMEM_COLS = 2 * BN;  // two accumulators: the epilogue of a tile overlaps the next main loop
+constexpr int BM = 128;
+constexpr int THREADS = 320;  // producer, MMA issuer, 4 split warps, 4 epilogue warps
 constexpr uint32_t WAIT_LIMIT = 1u << 22;
-constexpr int EPI_PITCH = 36;                   // floats per staged epilogue row (conflict-free float4 access)
+constexpr int EPI_PITCH = 36;                      // floats per staged epilogue row (conflict-free float4 access)
 constexpr int EPI_BYTES = 4 * 32 * EPI_PITCH * 4;  // one 32 x 32 staging tile per epilogue warp
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/ + EPI_BYTES;
 
-// instruction descriptor: D = f32, A = B = tf32, A K-major, B MN-major, N = 128, M = 128
-constexpr uint32_t IDESC = (1u << 4) | (2u << 7) | (2u << 10) | (0u << 15) | (1u << 16) |
-                           ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+// Tile configuration.  <128, 32, 3>: 128 x 128 tiles, k blocks of 32 (A rows of 128 B, 128-byte swizzle),
+// three 64 KB stages -- used for the batched 128^3 problems and whenever N is not a multiple of 256.
+// <256, 16, 4>: 128 x 256 tiles, k blocks of 16 (A rows of 64 B, 64-byte swizzle), four 48 KB stages --
+// per MMA the tensor core reads 4 KB of A and 8 KB of B from shared memory for twice the flops, which
+// matters because 3xTF32 from fp32 operands is shared-memory-bandwidth bound.
+template <int BN_, int BK_, int STAGES_>
+struct Cfg {
+  static constexpr int BN = BN_, BK = BK_, STAGES = STAGES_;
+  static constexpr int A_BYTES = BM * BK * 4;
+  static constexpr int B_BYTES = BK * BN * 4;
+  static constexpr int BOX_BYTES = BK * 32 * 4;  // one B box: BK k-rows x 32 columns (128 B)
+  static constexpr int STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES;
+  static constexpr int TMEM_COLS = 2 * BN;  // two accumulators: the epilogue of a tile overlaps the next main loop
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/ + EPI_BYTES;
+  // instruction descriptor: D = f32, A = B = tf32, A K-major, B MN-major, N = BN, M = 128
+  static constexpr uint32_t IDESC = (1u << 4) | (2u << 7) | (2u << 10) | (0u << 15) | (1u << 16) |
+                                    ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+  // A rows are BK*4 bytes: 128-byte swizzle (layout type 2, 8-row groups 1024 B apart) or 64-byte swizzle
+  // (layout type 4, 8-row groups 512 B apart)
+  static constexpr uint64_t A_LAYOUT = BK == 32 ? 2 : 4;
+  static constexpr uint64_t A_SBO = (8 * BK * 4) >> 4;
+  static_assert(BK == 32 || BK == 16, "A tile rows must be 128 or 64 bytes");
+  static_assert(TMEM_COLS <= 512 && SMEM_BYTES <= 232448, "tile configuration does not fit");
+};
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -84,24 +102,23 @@ __device__ __forceinline__ void tma_load_3d(void *dst, const CUtensorMap *map, u
       : "memory");
 }
 
-// K-major operand, 128-byte swizzle: rows 128 B apart, 8-row groups 1024 B apart.
-__device__ __forceinline__ uint64_t desc_kmajor(uint32_t saddr) {
-  return (uint64_t)((saddr >> 4) & 0x3FFF) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+// K-major operand, swizzled rows: 8-row groups `sbo` (16-byte units) apart.
+__device__ __forceinline__ uint64_t desc_kmajor(uint32_t saddr, uint64_t sbo, uint64_t layout) {
+  return (uint64_t)((saddr >> 4) & 0x3FFF) | (1ull << 16) | (sbo << 32) | (1ull << 46) | (layout << 61);
 }
 // MN-major 32-bit operand: the only layout the tensor core accepts is the 128-byte swizzle with
 // 32-byte atoms (layout type 1; TMA mode SWIZZLE_128B_ATOM_32B): 32-column blocks BOX_BYTES
 // apart (leading offset), groups of 4 k-rows 512 B apart (stride offset).
-__device__ __forceinline__ uint64_t desc_mnmajor(uint32_t saddr) {
-  return (uint64_t)((saddr >> 4) & 0x3FFF) | ((uint64_t)(BOX_BYTES >> 4) << 16) | (32ull << 32) | (1ull << 46) |
-         (1ull << 61);
+__device__ __forceinline__ uint64_t desc_mnmajor(uint32_t saddr, uint64_t box_bytes) {
+  return (uint64_t)((saddr >> 4) & 0x3FFF) | ((box_bytes >> 4) << 16) | (32ull << 32) | (1ull << 46) | (1ull << 61);
 }
 
-__device__ __forceinline__ void mma_tf32(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t accumulate) {
+__device__ __forceinline__ void mma_tf32(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
       "setp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
-      ::"r"(tmem_d), "l"(da), "l"(db), "r"(IDESC), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
+      ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
       : "memory");
 }
 
@@ -119,19 +136,24 @@ __device__ __forceinline__ void split_tf32(float4 &hi_lo_in_out, float4 &lo) {
 struct TileCoord {
   int batch, m0, n0;
 };
-__device__ __forceinline__ TileCoord tile_coord(int t, int tm, int tn) {
+__device__ __forceinline__ TileCoord tile_coord(int t, int tm, int tn, int bn) {
   constexpr int GROUP = 8;
   const int per = tm * tn;
   const int batch = t / per, r = t - batch * per;
   const int g = r / (GROUP * tn), first_m = g * GROUP;
   const int gsize = tm - first_m < GROUP ? tm - first_m : GROUP;
   const int q = r - g * GROUP * tn;
-  return TileCoord{batch, (first_m + q % gsize) * BM, (q / gsize) * BN};
+  return TileCoord{batch, (first_m + q % gsize) * BM, (q / gsize) * bn};
 }
 
+template <typename C_>
 __global__ void __launch_bounds__(THREADS, 1)
 bgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                      float *__restrict__ C, int M, int N, int K, int total_tiles, int *__restrict__ error_flag) {
+  constexpr int BN = C_::BN, BK = C_::BK, STAGES = C_::STAGES, A_BYTES = C_::A_BYTES, B_BYTES = C_::B_BYTES,
+                BOX_BYTES = C_::BOX_BYTES, STAGE_BYTES = C_::STAGE_BYTES, TMEM_COLS = C_::TMEM_COLS;
+  constexpr uint32_t IDESC = C_::IDESC;
+  constexpr uint64_t A_SBO = C_::A_SBO, A_LAYOUT = C_::A_LAYOUT;
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint64_t *bars = reinterpret_cast<uint64_t *>(smem + STAGES * STAGE_BYTES);
@@ -175,7 +197,7 @@ bgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
     if (lane == 0) {
       uint32_t g = 0;  // k blocks issued so far by this CTA
       for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
-        const TileCoord tc = tile_coord(t, tm, tn);
+        const TileCoord tc = tile_coord(t, tm, tn, BN);
         bool ok = true;
         for (int kb = 0; kb < nk; ++kb, ++g) {
           const int s = g % STAGES;
@@ -206,18 +228,26 @@ bgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
         const uint32_t d_tmem = tmem_base + buf * BN;
         for (int kb = 0; kb < nk; ++kb, ++g) {
           const int s = g % STAGES;
-          ok = mbar_wait(&conv[s], (g / STAGES) & 1);
+          // hi*hi needs only what TMA wrote: issue it as soon as the stage has landed, while the split
+          // warps are still producing the lo parts; the two correction products follow.
+          ok = mbar_wait(&full[s], (g / STAGES) & 1);
           if (!ok) break;
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           const uint32_t a = smem_u32(stage_a(s)), alo = smem_u32(stage_alo(s));
           const uint32_t b = smem_u32(stage_b(s)), blo = smem_u32(stage_blo(s));
 #pragma unroll
+          for (int ks = 0; ks < BK / 8; ++ks)
+            mma_tf32(d_tmem, desc_kmajor(a + ks * 32, A_SBO, A_LAYOUT), desc_mnmajor(b + ks * 1024, BOX_BYTES), IDESC,
+                     (kb > 0 || ks > 0) ? 1u : 0u);
+          ok = mbar_wait(&conv[s], (g / STAGES) & 1);
+          if (!ok) break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
           for (int ks = 0; ks < BK / 8; ++ks) {
-            const uint64_t da = desc_kmajor(a + ks * 32), dalo = desc_kmajor(alo + ks * 32);
-            const uint64_t db = desc_mnmajor(b + ks * 1024), dblo = desc_mnmajor(blo + ks * 1024);
-            mma_tf32(d_tmem, dalo, db, (kb > 0 || ks > 0) ? 1u : 0u);
-            mma_tf32(d_tmem, da, dblo, 1u);
-            mma_tf32(d_tmem, da, db, 1u);
+            const uint64_t da = desc_kmajor(a + ks * 32, A_SBO, A_LAYOUT), dalo = desc_kmajor(alo + ks * 32, A_SBO, A_LAYOUT);
+            const uint64_t db = desc_mnmajor(b + ks * 1024, BOX_BYTES), dblo = desc_mnmajor(blo + ks * 1024, BOX_BYTES);
+            mma_tf32(d_tmem, dalo, db, IDESC, 1u);
+            mma_tf32(d_tmem, da, dblo, IDESC, 1u);
           }
           // releases the stage once the MMAs above have read it
           asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
@@ -270,7 +300,7 @@ bgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
     uint32_t it = 0;
     bool ok = true;
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++it) {
-      const TileCoord tc = tile_coord(t, tm, tn);
+      const TileCoord tc = tile_coord(t, tm, tn, BN);
       const uint32_t buf = it & 1;
       float *cwarp = C + ((size_t)tc.batch * M + tc.m0 + 32 * q) * (size_t)N + tc.n0;  // this warp's 32 rows
       ok = mbar_wait(&acc_full[buf], (it >> 1) & 1);
@@ -350,14 +380,14 @@ static EncodeTiledFn encode_fn() {
   return fn;
 }
 
-// Row-major [batch][rows][cols] fp32 tensor, box = box_rows x 32 columns (128 bytes), swizzled.
+// Row-major [batch][rows][cols] fp32 tensor, box = box_rows x box_cols, swizzled.
 static int make_map(CUtensorMap *map, const float *base, int64_t batch, int64_t rows, int64_t cols, int box_rows,
-                    CUtensorMapSwizzle swizzle) {
+                    int box_cols, CUtensorMapSwizzle swizzle) {
   EncodeTiledFn fn = encode_fn();
   if (fn == nullptr) return fail(LAPIS_ECUDA, "bgemm: cuTensorMapEncodeTiled is not available from the driver");
   cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)rows, (cuuint64_t)batch};
   cuuint64_t strides[2] = {(cuuint64_t)cols * 4, (cuuint64_t)cols * rows * 4};
-  cuuint32_t box[3] = {32, (cuuint32_t)box_rows, 1};
+  cuuint32_t box[3] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows, 1};
   cuuint32_t estr[3] = {1, 1, 1};
   CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float *>(base), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
@@ -369,21 +399,41 @@ static int make_map(CUtensorMap *map, const float *base, int64_t batch, int64_t 
 }  // namespace tc
 
 static int *error_flag[64] = {nullptr};
-static bool attr_set[64] = {false};
+
+template <typename C_>
+static int launch_cfg(int64_t batch, int64_t M, int64_t N, int64_t K, const float *A, const float *B, float *C,
+                      int dev, cudaStream_t st) {
+  static bool attr_set[64] = {false};
+  CUtensorMap map_a, map_b;
+  LAPIS_TRY(tc::make_map(&map_a, A, batch, M, K, tc::BM, C_::BK,
+                         C_::BK == 32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B));
+  LAPIS_TRY(tc::make_map(&map_b, B, batch, K, N, C_::BK, 32, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B));
+  if (!attr_set[dev]) {
+    LAPIS_CUDA_TRY(cudaFuncSetAttribute(tc::bgemm_tcgen05_kernel<C_>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        C_::SMEM_BYTES));
+    attr_set[dev] = true;
+  }
+  const int64_t total = batch * (M / tc::BM) * (N / C_::BN);
+  const int64_t grid = total < sm_count() ? total : sm_count();  // persistent: one block per SM
+  tc::bgemm_tcgen05_kernel<C_><<<(unsigned)grid, tc::THREADS, C_::SMEM_BYTES, st>>>(map_a, map_b, C, (int)M, (int)N,
+                                                                                  (int)K, (int)total, error_flag[dev]);
+  LAPIS_CUDA_TRY(cudaGetLastError());
+  return LAPIS_OK;
+}
+
+using CfgSmall = tc::Cfg<128, 32, 3>;
+using CfgWide = tc::Cfg<256, 16, 4>;
 
 int bgemm_tcgen05_supported(int64_t batch, int64_t M, int64_t N, int64_t K) {
-  return batch >= 1 && M >= tc::BM && N >= tc::BN && K >= tc::BK && M % tc::BM == 0 && N % tc::BN == 0 &&
-         K % tc::BK == 0 && M <= (1 << 30) && N <= (1 << 30) && K <= (1 << 30) &&
-         batch * (M / tc::BM) * (N / tc::BN) < (1ll << 31) && batch < (1ll << 31);
+  return batch >= 1 && M >= tc::BM && N >= CfgSmall::BN && K >= CfgSmall::BK && M % tc::BM == 0 &&
+         N % CfgSmall::BN == 0 && K % CfgSmall::BK == 0 && M <= (1 << 30) && N <= (1 << 30) && K <= (1 << 30) &&
+         batch * (M / tc::BM) * (N / CfgSmall::BN) < (1ll << 31) && batch < (1ll << 31);
 }
 
 int bgemm_tcgen05_launch(int64_t batch, int64_t M, int64_t N, int64_t K, const float *A, const float *B, float *C,
                          cudaStream_t st) {
   if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) % 16)
     return fail(LAPIS_EBADARG, "bgemm: operands must be 16-byte aligned");
-  CUtensorMap map_a, map_b;
-  LAPIS_TRY(tc::make_map(&map_a, A, batch, M, K, tc::BM, CU_TENSOR_MAP_SWIZZLE_128B));
-  LAPIS_TRY(tc::make_map(&map_b, B, batch, K, N, tc::BK, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B));
   int dev = 0;
   LAPIS_CUDA_TRY(cudaGetDevice(&dev));
   if (dev < 0 || dev >= 64) return fail(LAPIS_EBADARG, "bgemm: device index %d not supported", dev);
@@ -391,17 +441,16 @@ int bgemm_tcgen05_launch(int64_t batch, int64_t M, int64_t N, int64_t K, const f
     LAPIS_CUDA_TRY(cudaMalloc(&error_flag[dev], sizeof(int)));
     LAPIS_CUDA_TRY(cudaMemset(error_flag[dev], 0, sizeof(int)));
   }
-  if (!attr_set[dev]) {
-    LAPIS_CUDA_TRY(cudaFuncSetAttribute(tc::bgemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        tc::SMEM_BYTES));
-    attr_set[dev] = true;
-  }
-  const int64_t total = batch * (M / tc::BM) * (N / tc::BN);
-  const int64_t grid = total < sm_count() ? total : sm_count();  // persistent: one block per SM
-  tc::bgemm_tcgen05_kernel<<<(unsigned)grid, tc::THREADS, tc::SMEM_BYTES, st>>>(map_a, map_b, C, (int)M, (int)N, (int)K,
-                                                                              (int)total, error_flag[dev]);
-  LAPIS_CUDA_TRY(cudaGetLastError());
-  return LAPIS_OK;
+  // 128 x 256 tiles when N allows and there are enough of them to fill the SMs; LAPIS_B200_GEMM_TILE=128 forces
+  // the 128 x 128 configuration.
+  static const int forced = [] {
+    const char *e = std::getenv("LAPIS_B200_GEMM_TILE");
+    return e ? atoi(e) : 0;
+  }();
+  const bool wide = forced != 128 && N % CfgWide::BN == 0 && K >= 8 * CfgWide::BK &&
+                    batch * (M / tc::BM) * (N / CfgWide::BN) >= sm_count();
+  if (wide) return launch_cfg<CfgWide>(batch, M, N, K, A, B, C, dev, st);
+  return launch_cfg<CfgSmall>(batch, M, N, K, A, B, C, dev, st);
 }
 
 }  // namespace lapis_b200

@@ -317,7 +317,8 @@ def test_bgemm_general_shapes_bit_exact(shape):
 
 
 @pytest.mark.parametrize("shape", [(1, 128, 128, 32), (1, 128, 128, 256), (3, 128, 128, 128), (2, 256, 384, 96),
-                                   (1, 512, 512, 1024)])
+                                   (1, 512, 512, 1024),
+                                   (1, 1024, 5120, 160), (2, 1280, 2048, 144)])  # enough 128 x 256 tiles: wide configuration
 def test_bgemm_tensor_core_path(shape):
     """Tile-aligned shapes run on tcgen05 with fp32 emulated by three TF32 products.  The bar is
     norm-wise against a product accumulated in double: no worse than max(1e-5 * |C|_max, the error
@@ -333,8 +334,8 @@ def test_bgemm_tensor_core_path(shape):
     bgemm(torch.as_tensor(A).to(dev), torch.as_tensor(B).to(dev), Cd)
     bgemm_status()
     got = Cd.cpu().numpy().astype(np.float64)
-    exact = oracle.bgemm_acc64(A, B, C0)
-    ref_err = np.max(np.abs(oracle.bgemm(A, B, C0).astype(np.float64) - exact))
+    exact = oracle.bgemm_acc64(A, B, C0, nthreads=8)
+    ref_err = np.max(np.abs(oracle.bgemm(A, B, C0, nthreads=8).astype(np.float64) - exact))
     err = np.max(np.abs(got - exact))
     scale = np.max(np.abs(exact))
     assert err <= max(1e-5 * scale, ref_err), f"err {err:.3e}, fp32 loop err {ref_err:.3e}, |C| {scale:.3e}"
