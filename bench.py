@@ -461,8 +461,8 @@ def run_ours(args, d, rank, world, local_rank):
 NCU_TRAFFIC = {
     "spmv": 3.325e9,    # profiles/spmv_chunk_kernel_config2.md
     "spmm": 3.380e10,   # profiles/spmm_row_kernel_config3.md
-    "bgemm": 1.034e9,   # profiles/bgemm_tcgen05_kernel.md (4096 x 128^3)
-    "gemm": 3.851e9,    # profiles/bgemm_tcgen05_kernel.md (8192^3)
+    "bgemm": 1.036e9,   # profiles/bgemm_tcgen05_kernel.md (4096 x 128^3)
+    "gemm": 3.455e9,    # profiles/bgemm_tcgen05_kernel.md (8192^3)
     "pcg": 2.71e9,      # profiles/pcg_iteration_config5.md (all kernels of one iteration)
 }
 
