@@ -614,22 +614,25 @@ static int launch_pipe(const lapis_b200_csr *h, int ctas_per_sm, const double *x
   const I *crd = static_cast<const I *>(h->crd);
   const int64_t abase = h->base & ~(int64_t)3, nnz_end = h->base + h->nnz;
   constexpr int smem = spmv_pipe_smem_bytes<I>(THREADS);
-  static bool attr_done[2] = {false, false};
+  static bool attr_done[64][2] = {};  // per device: the attribute belongs to the device's copy of the kernel
+  int dev = 0;
+  LAPIS_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return fail(LAPIS_EBADARG, "spmv: device index %d not supported", dev);
   int64_t grid = (int64_t)sm_count() * ctas_per_sm;
   if (grid > h->nblk) grid = h->nblk;
   if (dotvec != nullptr) {
     auto k = spmv_pipe_kernel<I, THREADS, true, HINT>;
-    if (!attr_done[1]) {
+    if (!attr_done[dev][1]) {
       LAPIS_CUDA_TRY(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-      attr_done[1] = true;
+      attr_done[dev][1] = true;
     }
     k<<<(unsigned)grid, THREADS, smem, st>>>(pos, crd, h->val, h->blk_row, abase, nnz_end, h->nrows, h->nblk, x, y,
                                              accumulate, h->carry, dotvec, blk_partial, skip_flag);
   } else {
     auto k = spmv_pipe_kernel<I, THREADS, false, HINT>;
-    if (!attr_done[0]) {
+    if (!attr_done[dev][0]) {
       LAPIS_CUDA_TRY(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-      attr_done[0] = true;
+      attr_done[dev][0] = true;
     }
     k<<<(unsigned)grid, THREADS, smem, st>>>(pos, crd, h->val, h->blk_row, abase, nnz_end, h->nrows, h->nblk, x, y,
                                              accumulate, h->carry, nullptr, nullptr, skip_flag);
