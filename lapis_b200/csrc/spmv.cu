@@ -189,6 +189,7 @@ spmv_chunk_kernel(const I *__restrict__ pos, const I *__restrict__ crd, const do
   __shared__ double s_red[THREADS / 32];
   using Pair = typename IndexPair<I>::type;
 
+  asm volatile("griddepcontrol.launch_dependents;");  // the fix-up kernel may start launching; it waits for our completion
   if (skip_flag != nullptr && *skip_flag != 0) return;
 
   const int tid = threadIdx.x;
@@ -330,6 +331,7 @@ spmv_pipe_kernel(const I *__restrict__ pos, const I *__restrict__ crd, const dou
   double *s_red = reinterpret_cast<double *>(s_nlong + 2);
   uint64_t *full = reinterpret_cast<uint64_t *>(s_red + THREADS / 32);
 
+  asm volatile("griddepcontrol.launch_dependents;");
   if (skip_flag != nullptr && *skip_flag != 0) return;
   const int tid = threadIdx.x;
   if (tid == 0) {
@@ -467,6 +469,9 @@ template <typename I>
 __global__ void spmv_fixup_kernel(const I *__restrict__ pos, const int64_t *__restrict__ plan, int64_t abase,
                                   int64_t nblk, int64_t nrows, const double *__restrict__ carry,
                                   double *__restrict__ y, const int *__restrict__ skip_flag) {
+  // Launched with programmatic stream serialization: the blocks may already be resident while the SpMV
+  // kernel drains; nothing is read before that kernel has completed and its writes are visible.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   if (skip_flag != nullptr && *skip_flag != 0) return;
   const int64_t b = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (b >= nblk - 1) return;
@@ -673,9 +678,22 @@ static int launch_spmv(const lapis_b200_csr *h, const double *x, double *y, int 
   LAPIS_CUDA_TRY(cudaGetLastError());
   if (h->nblk > 1) {
     const I *pos = static_cast<const I *>(h->pos);
-    spmv_fixup_kernel<I><<<(unsigned)((h->nblk - 1 + 255) / 256), 256, 0, st>>>(
-        pos, h->blk_row, h->base & ~(int64_t)3, h->nblk, h->nrows, h->carry, y, skip_flag);
-    LAPIS_CUDA_TRY(cudaGetLastError());
+    static const int pdl = [] {
+      const char *e = std::getenv("LAPIS_B200_PDL");
+      return e ? atoi(e) : 1;
+    }();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)((h->nblk - 1 + 255) / 256));
+    cfg.blockDim = dim3(256);
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;  // lets the fix-up blocks become resident while the SpMV kernel drains
+    LAPIS_CUDA_TRY(cudaLaunchKernelEx(&cfg, spmv_fixup_kernel<I>, pos, (const int64_t *)h->blk_row,
+                                      (int64_t)(h->base & ~(int64_t)3), (int64_t)h->nblk, (int64_t)h->nrows,
+                                      (const double *)h->carry, y, skip_flag));
   }
   return LAPIS_OK;
 }
