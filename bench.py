@@ -390,7 +390,10 @@ def run_ours(args, d, rank, world, local_rank):
     elif name == "pcg":
         from lapis_b200.dist import DistPcg
         n = d["shape"][0]
-        solver = DistPcg(d["pos"], d["crd"], d["val"], (n, n), d["b"], d["dinv"], dev, use_graph=True)
+        solver = DistPcg(d["pos"], d["crd"], d["val"], (n, n), d["b"], d["dinv"], dev, use_graph=True, comm=args.comm)
+        if world > 1:
+            extra_cfg = dict(extra_cfg or {}, exchange={"p2p": "stores into peer memory + flags (own kernels)",
+                                                        "nccl": "NCCL send/recv + allreduce"}[solver.comm])
         state = {}
 
         def solve(k):
@@ -400,7 +403,9 @@ def run_ours(args, d, rank, world, local_rank):
         # solver (it also captures the CUDA graph of one iteration that the timed solve replays).
         solver.solve(0.0, args.steps)
         kernel_name = "spmv_pipe_kernel|spmv_chunk_kernel (pass A) + pcg_update_kernel + pcg_direction_kernel"
-        launches_per_step = 6 if world == 1 else 8
+        # ours per iteration: SpMV + its fix-up, three vector passes... 6 on one rank; the NCCL transport adds
+        # two scalar-step kernels, the peer-to-peer one six exchange kernels
+        launches_per_step = 6 if world == 1 else (8 if solver.comm == "nccl" else 12)
         steps_holder = {"k": args.steps}
         ms, clocks = timed(lambda: solve(steps_holder["k"]), 1, 0)
         it = state["out"][1]
@@ -574,6 +579,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=None)
     ap.add_argument("--workload", default="spmv", choices=["spmv", "spmv1", "spmm", "pcg", "bgemm", "gemm"])
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--comm", default="p2p", choices=["p2p", "nccl"],
+                    help="exchange of the row-partitioned PCG on several GPUs: own peer-memory kernels or NCCL")
     ap.add_argument("--small", action="store_true", help="reduced sizes (for profiler captures and quick checks)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiler captures)")

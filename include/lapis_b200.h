@@ -216,6 +216,34 @@ int lapis_b200_pcg_step_spmv(void *d_work, lapis_b200_csr_t h, int64_t n_p, int6
 int lapis_b200_pcg_step_update(void *d_work, int64_t n, int64_t n_p, int64_t p_offset, const double *d_dinv,
                                double *d_x, int derive, double tol, uint64_t maxiter, void *stream);
 int lapis_b200_pcg_step_direction(void *d_work, int64_t n, int64_t n_p, int64_t p_offset, void *stream);
+/* The same exchanges without library collectives (one process per GPU on one node): a rank maps every
+ * peer's mailbox and workspace with CUDA IPC and the exchanges are stores into peer memory over NVLink
+ * plus sequence-numbered flags; the waits are bounded and stop the solve with an error mark in the
+ * mailbox if a peer never delivers.  No counterpart in the reference (it has no multi-device path).
+ *   peer_alloc / peer_open / peer_close / peer_free: device memory exported as a 64-byte IPC handle and
+ *     mapped by the peers (open with the consuming device current).
+ *   mailbox: lapis_b200_pcg_p2p_mailbox_bytes() bytes per rank, zero-initialised, from peer_alloc.
+ *   The caller stores epoch * 2^32 (a different epoch per solve) in workspace slot [10] after
+ *   lapis_b200_pcg_init.  phase: 0 = p.Ap, 1 = r.r / r.z, 2 = their initial values.
+ *   push_scalars: this rank's local sums (workspace slots [0] or [1..2]) to every rank's mailbox
+ *     (d_peer_mbox: device array of `world` mailbox addresses, own included).
+ *   wait_reduce: waits for all ranks' values of the phase, adds them in rank order (identical on every
+ *     rank) and runs the scalar recurrence `derive` (1, 2 or 3 as for lapis_b200_pcg_derive).
+ *   halo_push: copies pieces of this rank's p window into the peers' windows (d_pieces: device array of
+ *     {uint64 destination address, int64 source offset in the window, int64 length, uint64 flag address}).
+ *   halo_wait: waits until the ranks in d_srcs (device int array) have delivered this iteration's pieces. */
+int64_t lapis_b200_pcg_p2p_mailbox_bytes(void);
+/* Index, in doubles, of the first halo flag (one per source rank) and of the error mark in a mailbox. */
+void lapis_b200_pcg_p2p_mailbox_layout(int64_t *halo_index, int64_t *error_index);
+int lapis_b200_peer_alloc(int64_t bytes, void **ptr, unsigned char *handle64);
+int lapis_b200_peer_open(const unsigned char *handle64, void **ptr);
+int lapis_b200_peer_close(void *ptr);
+int lapis_b200_peer_free(void *ptr);
+int lapis_b200_pcg_p2p_push_scalars(void *d_work, int phase, int me, int world, const void *d_peer_mbox, void *stream);
+int lapis_b200_pcg_p2p_wait_reduce(void *d_work, void *d_mbox, int phase, int world, int derive, double tol,
+                                   uint64_t maxiter, void *stream);
+int lapis_b200_pcg_p2p_halo_push(void *d_work, int64_t n, int64_t n_p, const void *d_pieces, int npieces, void *stream);
+int lapis_b200_pcg_p2p_halo_wait(void *d_work, void *d_mbox, const void *d_srcs, int nsrc, void *stream);
 /* Copies {done, iters, relres} to the host; synchronises `stream`. */
 int lapis_b200_pcg_status(void *d_work, int *done, uint64_t *iters, double *relres, void *stream);
 

@@ -410,3 +410,230 @@ extern "C" int lapis_b200_pcg_f64(lapis_b200_csr_t h, const double *d_b, const d
   if (relres) *relres = rel;
   return LAPIS_OK;
 }
+
+// ---------------------------------------------------------------------------------------------
+// Row-partitioned PCG without library collectives: the three exchanges of an iteration (p.Ap; r.r and
+// r.z; the halo of p) are stores into the peers' memory over NVLink plus sequence-numbered flags, and
+// the consumers are small kernels that wait for the flags with a bound.  One process per GPU; a rank
+// maps every peer's mailbox and workspace with CUDA IPC (lapis_b200_peer_*).  The reference has no
+// multi-device path; this is this library's own.
+//
+// Mailbox of a rank (doubles): slot (phase, src) at (phase*16 + src)*4 = {v0, v1, seq, -}; halo flag of
+// src at 256 + src; error flag at 272.  Phases: 0 = p.Ap, 1 = r.r / r.z, 2 and 3 = the initial r.r / r.z
+// of even and odd epochs.  seq = epoch * 2^32 + iteration; the caller stores epoch * 2^32 in workspace
+// slot 10 after lapis_b200_pcg_init and raises the epoch by one per initialisation, so values left by an
+// earlier solve never match (a device-resident value keeps a captured CUDA graph of one iteration valid
+// across solves).  A slot is rewritten only after its reader has consumed it: a rank pushes phase 0 of
+// iteration k+1 after its phase-1 wait of iteration k, which needs every peer's phase-1 push, which each
+// peer does after its own phase-0 read of iteration k (and symmetrically for phase 1 and for the halo).
+// Two initialisations may follow one another with no iteration between them, hence the two initial
+// slots: the push of epoch e+2 comes after the wait of epoch e+1, which needs every peer's push of e+1,
+// which each peer issues after its own read of epoch e.
+// Every rank adds the same values in rank order, so all ranks derive bit-identical scalars.
+// ---------------------------------------------------------------------------------------------
+namespace lapis_b200 {
+
+constexpr int P2P_MAXW = 16;
+constexpr int P2P_HALO = 4 * P2P_MAXW * 4;
+constexpr int P2P_ERR = P2P_HALO + P2P_MAXW;
+constexpr int P2P_MBOX_DOUBLES = 512;
+constexpr int SC_EPOCH = 10;                   // workspace header slot holding epoch * 2^32
+constexpr unsigned P2P_SPIN_LIMIT = 1u << 22;  // polls with a short sleep: a few seconds at most
+enum { PH_A = 0, PH_B = 1, PH_INIT = 2 };
+
+struct HaloPiece {  // one contiguous piece of p this rank provides to a peer
+  unsigned long long dst_addr;   // address of the first destination element in the peer's p window
+  long long src_off;             // offset of the first source element in this rank's p window
+  long long len;
+  unsigned long long flag_addr;  // address of this rank's halo flag in the peer's mailbox
+};
+
+// Slot row of a phase: the initial exchange alternates between two rows by the parity of the epoch.
+__device__ __forceinline__ int p2p_slot_row(int phase, double base_seq) {
+  return phase == PH_INIT ? PH_INIT + (int)((long long)(base_seq * (1.0 / 4294967296.0)) & 1) : phase;
+}
+
+__device__ __forceinline__ bool p2p_wait_equal(const volatile double *flag, double expected) {
+  for (unsigned i = 0; i < P2P_SPIN_LIMIT; ++i) {
+    if (*flag == expected) return true;
+    __nanosleep(200);
+  }
+  return false;
+}
+
+__global__ void p2p_push_scalars_kernel(const double *__restrict__ sc, const long long *__restrict__ fl, int phase, int me,
+                                        int world, const unsigned long long *__restrict__ peer_mbox) {
+  const int j = threadIdx.x;
+  if (j >= world) return;
+  const double base_seq = sc[SC_EPOCH];
+  if (phase != PH_INIT && fl[FL_DONE] != 0) return;
+  const double seq = base_seq + (phase == PH_INIT ? 0.0 : (double)(fl[FL_ITERS] + 1));
+  const double v0 = phase == PH_A ? sc[SC_PAP] : sc[SC_RR];
+  const double v1 = phase == PH_A ? 0.0 : sc[SC_RZNEW];
+  volatile double *slot = reinterpret_cast<volatile double *>(peer_mbox[j]) + (p2p_slot_row(phase, base_seq) * P2P_MAXW + me) * 4;
+  slot[0] = v0;
+  slot[1] = v1;
+  __threadfence_system();  // values before the sequence number, system-wide
+  slot[2] = seq;
+}
+
+__global__ void p2p_wait_reduce_kernel(double *sc, long long *fl, double *mbox, int phase, int world, int derive,
+                                       double tol, unsigned long long maxiter) {
+  const int j = threadIdx.x;  // one warp
+  const double base_seq = sc[SC_EPOCH];
+  if (phase != PH_INIT && fl[FL_DONE] != 0) return;
+  const double expected = base_seq + (phase == PH_INIT ? 0.0 : (double)(fl[FL_ITERS] + 1));
+  const int row = p2p_slot_row(phase, base_seq);
+  bool ok = true;
+  if (j < world) ok = p2p_wait_equal(mbox + (row * P2P_MAXW + j) * 4 + 2, expected);
+  const bool all_ok = __all_sync(0xffffffffu, ok);
+  if (j != 0) return;
+  if (!all_ok) {  // a peer never delivered: stop the solve and let the host see why
+    mbox[P2P_ERR] = 1.0 + phase;
+    fl[FL_DONE] = 1;
+    return;
+  }
+  __threadfence_system();
+  double v0 = 0.0, v1 = 0.0;
+  for (int r = 0; r < world; ++r) {  // rank order on every rank
+    const volatile double *slot = mbox + (row * P2P_MAXW + r) * 4;
+    v0 = __dadd_rn(v0, slot[0]);
+    v1 = __dadd_rn(v1, slot[1]);
+  }
+  if (phase == PH_A) {
+    sc[SC_PAP] = v0;
+  } else {
+    sc[SC_RR] = v0;
+    sc[SC_RZNEW] = v1;
+  }
+  pcg_derive(derive, sc, fl, tol, maxiter);
+}
+
+__global__ void __launch_bounds__(256)
+p2p_halo_push_kernel(const double *__restrict__ p_window, const double *__restrict__ sc, const long long *__restrict__ fl,
+                     const HaloPiece *__restrict__ pieces) {
+  if (fl[FL_DONE] != 0) return;
+  const double base_seq = sc[SC_EPOCH];
+  const HaloPiece pc = pieces[blockIdx.x];
+  double *dst = reinterpret_cast<double *>(pc.dst_addr);
+  for (long long i = threadIdx.x; i < pc.len; i += blockDim.x) dst[i] = p_window[pc.src_off + i];
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) *reinterpret_cast<volatile double *>(pc.flag_addr) = base_seq + (double)(fl[FL_ITERS] + 1);
+}
+
+__global__ void p2p_halo_wait_kernel(const double *sc, long long *fl, double *mbox, const int *__restrict__ srcs, int nsrc) {
+  const int j = threadIdx.x;  // one warp
+  if (fl[FL_DONE] != 0) return;
+  const double base_seq = sc[SC_EPOCH];
+  const double expected = base_seq + (double)(fl[FL_ITERS] + 1);
+  bool ok = true;
+  if (j < nsrc) ok = p2p_wait_equal(mbox + P2P_HALO + srcs[j], expected);
+  const bool all_ok = __all_sync(0xffffffffu, ok);
+  if (j == 0 && !all_ok) {
+    mbox[P2P_ERR] = 9.0;
+    fl[FL_DONE] = 1;
+  }
+}
+
+}  // namespace lapis_b200
+
+extern "C" int64_t lapis_b200_pcg_p2p_mailbox_bytes(void) { return (int64_t)P2P_MBOX_DOUBLES * 8; }
+
+// Index (in doubles) of the first halo flag and of the error mark inside a mailbox.
+extern "C" void lapis_b200_pcg_p2p_mailbox_layout(int64_t *halo_index, int64_t *error_index) {
+  if (halo_index) *halo_index = P2P_HALO;
+  if (error_index) *error_index = P2P_ERR;
+}
+
+// Device memory that peers can map: allocated here (zeroed), exported as a CUDA IPC handle (64 bytes).
+extern "C" int lapis_b200_peer_alloc(int64_t bytes, void **ptr, unsigned char *handle64) {
+  clear_error();
+  if (bytes <= 0 || ptr == nullptr || handle64 == nullptr) return fail(LAPIS_EBADARG, "peer_alloc: bad arguments");
+  void *p = nullptr;
+  LAPIS_CUDA_TRY(cudaMalloc(&p, (size_t)bytes));
+  cudaError_t e = cudaMemset(p, 0, (size_t)bytes);
+  cudaIpcMemHandle_t h;
+  if (e == cudaSuccess) e = cudaIpcGetMemHandle(&h, p);
+  if (e != cudaSuccess) {
+    cudaFree(p);
+    return fail(LAPIS_ECUDA, "peer_alloc: %s", cudaGetErrorString(e));
+  }
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+  memcpy(handle64, &h, 64);
+  *ptr = p;
+  return LAPIS_OK;
+}
+
+// Maps a peer's allocation into this process for the current device (peer access is enabled by the
+// open itself); the pointer may be dereferenced by kernels running on the current device.
+extern "C" int lapis_b200_peer_open(const unsigned char *handle64, void **ptr) {
+  clear_error();
+  if (handle64 == nullptr || ptr == nullptr) return fail(LAPIS_EBADARG, "peer_open: bad arguments");
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, 64);
+  void *p = nullptr;
+  LAPIS_CUDA_TRY(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
+  *ptr = p;
+  return LAPIS_OK;
+}
+extern "C" int lapis_b200_peer_close(void *ptr) {
+  clear_error();
+  if (ptr != nullptr) LAPIS_CUDA_TRY(cudaIpcCloseMemHandle(ptr));
+  return LAPIS_OK;
+}
+extern "C" int lapis_b200_peer_free(void *ptr) {
+  clear_error();
+  if (ptr != nullptr) LAPIS_CUDA_TRY(cudaFree(ptr));
+  return LAPIS_OK;
+}
+
+extern "C" int lapis_b200_pcg_p2p_push_scalars(void *d_work, int phase, int me, int world, const void *d_peer_mbox,
+                                               void *stream) {
+  clear_error();
+  if (d_work == nullptr || d_peer_mbox == nullptr || world < 1 || world > P2P_MAXW || me < 0 || me >= world || phase < 0 ||
+      phase > 2)
+    return fail(LAPIS_EBADARG, "pcg_p2p_push_scalars: bad arguments");
+  double *base = static_cast<double *>(d_work);
+  p2p_push_scalars_kernel<<<1, 32, 0, as_stream(stream)>>>(base, reinterpret_cast<long long *>(base + SC_COUNT), phase, me,
+                                                           world, static_cast<const unsigned long long *>(d_peer_mbox));
+  LAPIS_CUDA_TRY(cudaGetLastError());
+  return LAPIS_OK;
+}
+
+extern "C" int lapis_b200_pcg_p2p_wait_reduce(void *d_work, void *d_mbox, int phase, int world, int derive, double tol,
+                                              uint64_t maxiter, void *stream) {
+  clear_error();
+  if (d_work == nullptr || d_mbox == nullptr || world < 1 || world > P2P_MAXW || phase < 0 || phase > 2 || derive < 1 ||
+      derive > 3)
+    return fail(LAPIS_EBADARG, "pcg_p2p_wait_reduce: bad arguments");
+  double *base = static_cast<double *>(d_work);
+  p2p_wait_reduce_kernel<<<1, 32, 0, as_stream(stream)>>>(base, reinterpret_cast<long long *>(base + SC_COUNT),
+                                                          static_cast<double *>(d_mbox), phase, world, derive, tol, maxiter);
+  LAPIS_CUDA_TRY(cudaGetLastError());
+  return LAPIS_OK;
+}
+
+// pieces: device array of npieces records {dst address, source offset in the p window, length, flag address}.
+extern "C" int lapis_b200_pcg_p2p_halo_push(void *d_work, int64_t n, int64_t n_p, const void *d_pieces, int npieces,
+                                            void *stream) {
+  clear_error();
+  if (npieces == 0) return LAPIS_OK;
+  if (d_work == nullptr || d_pieces == nullptr || npieces < 0) return fail(LAPIS_EBADARG, "pcg_p2p_halo_push: bad arguments");
+  PcgWork w = carve(d_work, n, n_p);
+  p2p_halo_push_kernel<<<npieces, 256, 0, as_stream(stream)>>>(w.p, w.sc, w.fl, static_cast<const HaloPiece *>(d_pieces));
+  LAPIS_CUDA_TRY(cudaGetLastError());
+  return LAPIS_OK;
+}
+
+extern "C" int lapis_b200_pcg_p2p_halo_wait(void *d_work, void *d_mbox, const void *d_srcs, int nsrc, void *stream) {
+  clear_error();
+  if (nsrc == 0) return LAPIS_OK;
+  if (d_work == nullptr || d_mbox == nullptr || d_srcs == nullptr || nsrc < 0 || nsrc > 32)
+    return fail(LAPIS_EBADARG, "pcg_p2p_halo_wait: bad arguments");
+  double *base = static_cast<double *>(d_work);
+  p2p_halo_wait_kernel<<<1, 32, 0, as_stream(stream)>>>(base, reinterpret_cast<long long *>(base + SC_COUNT),
+                                                        static_cast<double *>(d_mbox), static_cast<const int *>(d_srcs), nsrc);
+  LAPIS_CUDA_TRY(cudaGetLastError());
+  return LAPIS_OK;
+}

@@ -6,12 +6,16 @@ operator needs one:
 
 * SpMV / SpMM: rank g owns an nnz-balanced block of rows; x (or B) is replicated, as
   a caller that holds the same right-hand side on every GPU has it; no collective.
-* PCG: every vector is split like the rows.  Before the SpMV pass each rank receives
-  the pieces of p that its columns reach outside its own block (for a banded matrix
-  one grid row from each neighbour) with point-to-point sends, and the two scalar
-  groups of an iteration (p.Ap; r.r and r.z) are summed with an allreduce of the
-  solver's scalar block.  One iteration is captured in a CUDA graph and replayed, so
-  the host is not in the loop between checks of the stop flag.
+* PCG: every vector is split like the rows.  Before the SpMV pass each rank needs the
+  pieces of p that its columns reach outside its own block (for a banded matrix one
+  grid row from each neighbour), and the two scalar groups of an iteration (p.Ap; r.r
+  and r.z) must be summed over the ranks.  Two transports: ``comm="p2p"`` (default on
+  several GPUs) -- every rank maps its peers' workspaces and mailboxes with CUDA IPC,
+  the producers store straight into peer memory over NVLink and raise sequence-numbered
+  flags, small kernels wait for them with a bound; ``comm="nccl"`` -- NCCL send/recv
+  for the halo and two allreduces of the solver's scalar block.  One iteration is
+  captured in a CUDA graph and replayed, so the host is not in the loop between checks
+  of the stop flag.
 """
 from __future__ import annotations
 
@@ -102,11 +106,35 @@ class ShardedSpmv:
         return self.matrix.spmm(B, C_local, accumulate)
 
 
+class _PeerBuffer:
+    """Device memory from ``lapis_b200_peer_alloc``: zero-initialised, exportable as a CUDA IPC handle,
+    visible to torch as a float64 tensor (zero-copy) through ``__cuda_array_interface__``."""
+
+    def __init__(self, lib, check, nbytes: int, device):
+        self._lib, self._check = lib, check
+        self.nbytes = int(nbytes)
+        ptr = ctypes.c_void_p()
+        handle = ctypes.create_string_buffer(64)
+        with torch.cuda.device(device):
+            check(lib.lapis_b200_peer_alloc(self.nbytes, ctypes.byref(ptr), handle))
+        self.ptr, self.handle = int(ptr.value), handle.raw
+        self.__cuda_array_interface__ = {"shape": (self.nbytes // 8,), "typestr": "<f8", "data": (self.ptr, False),
+                                         "version": 2, "strides": None}
+        self.tensor = torch.as_tensor(self, device=device)
+
+    def free(self):
+        if self.ptr:
+            self.tensor = None
+            self._lib.lapis_b200_peer_free(ctypes.c_void_p(self.ptr))
+            self.ptr = 0
+
+
 class DistPcg:
     """Jacobi-preconditioned CG (examples/pcg_solve.py:52-101 in the LAPIS project) on a
     row-partitioned matrix.  Construct on every rank with the same host CSR, b and dinv."""
 
-    def __init__(self, pos, crd, val, shape, b, dinv, device, group=None, use_graph: bool = True):
+    def __init__(self, pos, crd, val, shape, b, dinv, device, group=None, use_graph: bool = True, comm: str = "p2p",
+                 transport_on_one_rank: bool = False, tune: bool = True):
         from ._lib import check, load
         from .device import CsrMatrix
         self._check, self._lib = check, load()
@@ -126,20 +154,98 @@ class DistPcg:
         self.p_off = self.halo.own_offset
         lcrd = (lcrd.astype(np.int64) - self.halo.c0).astype(lcrd.dtype)  # columns index the window
         with torch.cuda.device(self.device):
-            self.matrix = CsrMatrix.from_host(lpos, lcrd, lval, (self.n, self.n_p), self.device, tune=True)
+            self.matrix = CsrMatrix.from_host(lpos, lcrd, lval, (self.n, self.n_p), self.device, tune=tune)
             sl = slice(self.halo.r0, self.halo.r1)
             self.b = torch.as_tensor(np.ascontiguousarray(b[sl])).to(self.device)
             self.dinv = torch.as_tensor(np.ascontiguousarray(dinv[sl])).to(self.device)
             self.x = torch.zeros(self.n, dtype=torch.float64, device=self.device)
             nbytes = int(self._lib.lapis_b200_pcg_workspace_bytes(self.n, self.n_p))
-            self.work = torch.zeros(nbytes // 8, dtype=torch.float64, device=self.device)
+            if comm not in ("p2p", "nccl"):
+                raise ValueError("comm must be 'p2p' or 'nccl'")
+            # one rank needs no exchange; transport_on_one_rank keeps the peer-to-peer kernels in the loop
+            # anyway (the rank is its own only peer), which exercises them on a single GPU
+            self.comm = comm if self.world > 1 or (transport_on_one_rank and comm == "p2p") else "none"
+            if self.comm == "p2p":
+                self._work_buf = _PeerBuffer(self._lib, check, nbytes, self.device)
+                self.work = self._work_buf.tensor
+            else:
+                self.work = torch.zeros(nbytes // 8, dtype=torch.float64, device=self.device)
             offs = (ctypes.c_int64 * 4)()
             check(self._lib.lapis_b200_pcg_workspace_layout(self.n, self.n_p, offs))
+            self._p_doubles = int(offs[2])
             self.p_ext = self.work[offs[2]:offs[2] + self.n_p]
             self.sc = self.work[0:8]
             self.flags = self.work[8:10].view(torch.int64)
+            if self.comm == "p2p":
+                self._setup_p2p(windows)
         self.n_global = n_global
         self._graph = None
+        self._epoch = 0
+
+    # -- peer-to-peer transport -----------------------------------------------------------
+    def _setup_p2p(self, windows):
+        """Exchanges IPC handles, maps every peer's workspace and mailbox, and builds the device tables
+        the exchange kernels read: mailbox addresses, halo pieces to push, ranks to wait for."""
+        lib, check = self._lib, self._check
+        if self.world > 16:
+            raise ValueError("the peer-to-peer transport supports up to 16 ranks")
+        self._mbox_buf = _PeerBuffer(lib, check, int(lib.lapis_b200_pcg_p2p_mailbox_bytes()), self.device)
+        mine = (self._work_buf.handle, self._mbox_buf.handle, self.n_p, self._p_doubles)
+        infos = [mine] * self.world
+        if self.world > 1:
+            dist.all_gather_object(infos, mine, group=self.group)
+        self._peer_ptrs = []
+        work_addr, mbox_addr = [0] * self.world, [0] * self.world
+        for r, (wh, mh, _, _) in enumerate(infos):
+            if r == self.rank:
+                work_addr[r], mbox_addr[r] = self._work_buf.ptr, self._mbox_buf.ptr
+                continue
+            for h, table in ((wh, work_addr), (mh, mbox_addr)):
+                ptr = ctypes.c_void_p()
+                check(lib.lapis_b200_peer_open(h, ctypes.byref(ptr)))
+                table[r] = int(ptr.value)
+                self._peer_ptrs.append(int(ptr.value))
+        self._peer_mbox = torch.tensor(mbox_addr, dtype=torch.int64, device=self.device)
+        halo_index, err_index = ctypes.c_int64(), ctypes.c_int64()
+        lib.lapis_b200_pcg_p2p_mailbox_layout(ctypes.byref(halo_index), ctypes.byref(err_index))
+        HALO, self._err_index = int(halo_index.value), int(err_index.value)
+        pieces = []
+        for (consumer, s, e) in self.halo.send:
+            c0_peer = windows[consumer][0]
+            n_p_peer, p_doubles_peer = infos[consumer][2], infos[consumer][3]
+            dst_off, src_off, length = s - c0_peer, s - self.halo.c0, e - s
+            if not (0 <= dst_off and dst_off + length <= n_p_peer and 0 <= src_off and src_off + length <= self.n_p):
+                raise RuntimeError("halo piece outside a window")  # never dereference an address we cannot bound
+            pieces += [work_addr[consumer] + 8 * (p_doubles_peer + dst_off), src_off, length,
+                       mbox_addr[consumer] + 8 * (HALO + self.rank)]
+        self._npieces = len(pieces) // 4
+        self._pieces = torch.tensor(pieces if pieces else [0], dtype=torch.int64, device=self.device)
+        srcs = sorted({owner for owner, _, _ in self.halo.recv})
+        self._nsrc = len(srcs)
+        self._srcs = torch.tensor(srcs if srcs else [0], dtype=torch.int32, device=self.device)
+        if self.world > 1:
+            dist.barrier(group=self.group)  # every rank has mapped every buffer before anyone pushes
+
+    def _p2p_scalars(self, phase: int, derive: int, tol: float, maxiter: int):
+        lib, check, w = self._lib, self._check, ctypes.c_void_p(self.work.data_ptr())
+        check(lib.lapis_b200_pcg_p2p_push_scalars(w, phase, self.rank, self.world,
+                                                  ctypes.c_void_p(self._peer_mbox.data_ptr()), self._stream()))
+        check(lib.lapis_b200_pcg_p2p_wait_reduce(w, ctypes.c_void_p(self._mbox_buf.ptr), phase, self.world, derive, tol,
+                                                 maxiter, self._stream()))
+
+    def _p2p_halo_push(self):
+        self._check(self._lib.lapis_b200_pcg_p2p_halo_push(ctypes.c_void_p(self.work.data_ptr()), self.n, self.n_p,
+                                                           ctypes.c_void_p(self._pieces.data_ptr()), self._npieces,
+                                                           self._stream()))
+
+    def _p2p_halo_wait(self):
+        self._check(self._lib.lapis_b200_pcg_p2p_halo_wait(ctypes.c_void_p(self.work.data_ptr()),
+                                                           ctypes.c_void_p(self._mbox_buf.ptr),
+                                                           ctypes.c_void_p(self._srcs.data_ptr()), self._nsrc, self._stream()))
+
+    def comm_error(self) -> float:
+        """Non-zero when a bounded wait of the peer-to-peer transport gave up (1-3: scalars, 9: halo)."""
+        return float(self._mbox_buf.tensor[self._err_index].item()) if self.comm == "p2p" else 0.0
 
     # -- one iteration, enqueued on the current stream ---------------------------------
     def _stream(self):
@@ -151,27 +257,42 @@ class DistPcg:
 
     def _iteration(self, tol: float, maxiter: int):
         lib, check, w = self._lib, self._check, ctypes.c_void_p(self.work.data_ptr())
-        single = 1 if self.world == 1 else 0
-        if self.world > 1:
+        single = 1 if self.comm == "none" else 0
+        p2p = self.comm == "p2p"
+        if p2p:
+            self._p2p_halo_wait()
+        elif self.world > 1:
             self.halo.exchange(self.p_ext)
         check(lib.lapis_b200_pcg_step_spmv(w, self.matrix.handle, self.n_p, self.p_off, single, self._stream()))
-        if not single:
+        if p2p:
+            self._p2p_scalars(0, 2, tol, maxiter)
+        elif not single:
             self._allreduce(self.sc[0:1])
             check(lib.lapis_b200_pcg_derive(w, 2, tol, maxiter, self._stream()))
         check(lib.lapis_b200_pcg_step_update(w, self.n, self.n_p, self.p_off, ctypes.c_void_p(self.dinv.data_ptr()),
                                              ctypes.c_void_p(self.x.data_ptr()), single, tol, maxiter, self._stream()))
-        if not single:
+        if p2p:
+            self._p2p_scalars(1, 3, tol, maxiter)
+        elif not single:
             self._allreduce(self.sc[1:3])
             check(lib.lapis_b200_pcg_derive(w, 3, tol, maxiter, self._stream()))
         check(lib.lapis_b200_pcg_step_direction(w, self.n, self.n_p, self.p_off, self._stream()))
+        if p2p:
+            self._p2p_halo_push()
 
     def _init(self, tol, maxiter):
         lib, check, w = self._lib, self._check, ctypes.c_void_p(self.work.data_ptr())
-        single = 1 if self.world == 1 else 0
+        single = 1 if self.comm == "none" else 0
         check(lib.lapis_b200_pcg_init(w, self.n, self.n_p, self.p_off, ctypes.c_void_p(self.b.data_ptr()),
                                       ctypes.c_void_p(self.dinv.data_ptr()), ctypes.c_void_p(self.x.data_ptr()),
                                       single, self._stream()))
-        if not single:
+        if self.comm == "p2p":
+            # a new epoch per solve: sequence numbers left in the mailboxes by an earlier solve never match
+            self._epoch += 1
+            self.work[10:11].fill_(float(self._epoch) * 4294967296.0)
+            self._p2p_scalars(2, 1, tol, maxiter)
+            self._p2p_halo_push()
+        elif not single:
             self._allreduce(self.sc[1:3])
             check(lib.lapis_b200_pcg_derive(w, 1, tol, maxiter, self._stream()))
 
@@ -179,6 +300,9 @@ class DistPcg:
         """Returns (x_local, iters, relres); x_local holds rows [bounds[rank], bounds[rank+1])."""
         limit = maxiter if maxiter > 0 else 1 << 31
         with torch.cuda.device(self.device):
+            if self.comm == "p2p" and self.world > 1:
+                # the waits of the exchange kernels are bounded (seconds): start the ranks together
+                dist.barrier(group=self.group)
             self._init(tol, maxiter)
             if self.use_graph and self._graph is None:
                 # Warm up once on a side stream (NCCL and the kernels must have run before capture);
@@ -211,4 +335,7 @@ class DistPcg:
                 done = bool(fl[0].item())
             iters = int(self.flags[1].item())
             relres = float(self.sc[5].item())
+            err = self.comm_error()
+            if err != 0.0:
+                raise RuntimeError(f"pcg: a peer did not deliver in time (exchange {int(err)}: 1-3 scalar sums, 9 halo)")
         return self.x, iters, relres

@@ -431,3 +431,24 @@ def test_pcg_laplacian_converges_and_graph_matches_eager():
     # the solution satisfies the system
     res = oracle.spmv(d["pos"], d["crd"], d["val"], xe.cpu().numpy(), -d["b"])
     assert np.linalg.norm(res) <= 2e-8 * np.linalg.norm(d["b"])
+
+
+def test_pcg_peer_transport_on_one_rank():
+    """The peer-to-peer exchange kernels with the rank as its own only peer (push, then wait, in stream
+    order: nothing waits on another launch): same bits as the fused single-rank scalar steps, over
+    two solves (two epochs of the sequence numbers) with and without a captured graph."""
+    from lapis_b200.dist import DistPcg
+    dev = _dev()
+    d = w.pcg_laplacian(64)
+    n = d["shape"][0]
+    args = (d["pos"], d["crd"], d["val"], (n, n), d["b"], d["dinv"], dev)
+    # tune=False: every solver uses the default SpMV kernel (the timed choice may differ between objects,
+    # and the kernels group the fused dot partials differently)
+    xr, ir, rr = DistPcg(*args, use_graph=False, tune=False).solve(1e-9, 500, check_every=8)
+    for use_graph in (False, True):
+        solver = DistPcg(*args, use_graph=use_graph, comm="p2p", transport_on_one_rank=True, tune=False)
+        assert solver.comm == "p2p"
+        for _ in range(2):
+            x, it, rel = solver.solve(1e-9, 500, check_every=8)
+            assert it == ir and rel == rr and torch.equal(x, xr)
+            assert solver.comm_error() == 0.0
