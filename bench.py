@@ -385,6 +385,30 @@ def run_ours(args, d, rank, world, local_rank):
             e2e = {"value": d["work"] * e2e_steps / t_e2e * d["unit_scale"], "unit": d["unit"],
                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps,
                    "api": f"KokkosBackend.compile(...).{fn.__name__} -> py_{fn.__name__}_f64_i64, pinned host buffers"}
+            # The same call with resident operands (DualView arguments): the matrix is uploaded once before
+            # the timed region; every step the dense operand is declared modified on the host (re-uploaded)
+            # and the result is brought back.
+            from lapis_b200.dualview import DualView
+            dvs = [DualView(a, device=dev) for a in pnp]
+            out_dv = DualView(out.numpy(), device=dev)
+            fn(dvs[0], dvs[1], dvs[2], spec, dvs[3], out_dv).syncHost()
+            torch.cuda.synchronize()
+            if world > 1:
+                dist.barrier()
+            t0 = time.perf_counter()
+            for _ in range(e2e_steps):
+                dvs[3].modifyHost()
+                fn(dvs[0], dvs[1], dvs[2], spec, dvs[3], out_dv).syncHost()
+            t_res = time.perf_counter() - t0
+            if world > 1:
+                t = torch.tensor([t_res], dtype=torch.float64, device=dev)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                t_res = float(t.item())
+            e2e["resident"] = {"value": d["work"] * e2e_steps / t_res * d["unit_scale"], "unit": d["unit"],
+                               "h2d_bytes_per_step": int(pnp[3].nbytes), "d2h_bytes_per_step": d2h,
+                               "api": "same call with lapis_b200.dualview.DualView arguments: matrix resident, dense "
+                                      "operand re-uploaded and result downloaded every step"}
+            del dvs, out_dv
         del pinned, out
         algo_bytes_rank = (len(lcrd) * 16 + len(lpos) * 8 + (8 * n + 8 * (r1 - r0)) * (64 if name == "spmm" else 1))
     elif name == "pcg":

@@ -29,7 +29,7 @@ import re
 import numpy as np
 
 from . import _memref as rt
-from ._lib import check_last, load
+from ._lib import LapisError, check_last, load
 
 _PAR_STRATEGIES = ("none", "dense-outer-loop", "any-storage-outer-loop", "dense-any-loop", "any-storage-any-loop")
 
@@ -183,14 +183,27 @@ def _flatten_spec(spec):
     return flat
 
 
+def _resident(*args) -> bool:
+    from .dualview import DualView
+    return any(isinstance(a, DualView) for a in args)
+
+
 class LAPISModule:
-    """Same lifecycle as the generated class: initialize on construction, finalize on deletion."""
+    """Same lifecycle as the generated class: initialize on construction, finalize on deletion.
+
+    Every function takes numpy arrays as the generated module does (operands are uploaded, results
+    downloaded, on every call).  If any array argument is a ``lapis_b200.dualview.DualView`` the call takes
+    the resident path instead: operands are uploaded only when their host side was modified, the CSR
+    streaming plan is kept per (pos, crd, val) triple, results stay on the device until ``syncHost()`` /
+    ``numpy()``, and the in/out argument is returned as a DualView.
+    """
 
     def __init__(self, bindings: dict):
         self.libHandle = load()
         self.libHandle.lapis_initialize()
         check_last()
         self._live = True
+        self._plans = {}  # (id(pos), id(crd), id(val)) -> (weakrefs, versions, shape, CsrMatrix)
         for name, (kind, sfx, idx_dtype) in bindings.items():
             setattr(self, name, self._bind(kind, sfx, idx_dtype))
 
@@ -198,6 +211,36 @@ class LAPISModule:
         if getattr(self, "_live", False):
             self._live = False
             self.libHandle.lapis_finalize()
+
+    # -- resident path ---------------------------------------------------------------------
+    @staticmethod
+    def _dv(a, dtype):
+        from .dualview import DualView
+        if isinstance(a, DualView):
+            if a.dtype != np.dtype(dtype):
+                raise TypeError(f"DualView of {a.dtype} where {np.dtype(dtype)} is expected")
+            return a
+        return DualView(np.require(a, dtype=dtype, requirements=["C"]))
+
+    def _plan(self, pos, crd, val, spec, idx_dtype):
+        """The device CSR with its streaming plan, rebuilt only if one of the three arrays changed."""
+        import weakref
+        from .device import CsrMatrix
+        pos, crd, val = self._dv(pos, idx_dtype), self._dv(crd, idx_dtype), self._dv(val, np.float64)
+        flat = _flatten_spec(spec)
+        shape = (int(flat[0]), int(flat[1]))
+        if pos.extent(0) != flat[2] or crd.extent(0) != flat[3] or val.extent(0) != flat[4] or flat[2] != flat[0] + 1:
+            raise LapisError(1, "storage specifier does not match the pos/crd/val arrays")
+        key = (id(pos), id(crd), id(val))
+        versions = (pos.version, crd.version, val.version)
+        hit = self._plans.get(key)
+        if hit is not None and all(r() is o for r, o in zip(hit[0], (pos, crd, val))) and hit[1] == versions and hit[2] == shape:
+            return hit[3]
+        A = CsrMatrix(pos.device_view(), crd.device_view(), val.device_view(), shape, tune=True)
+        if len(self._plans) >= 16:
+            self._plans.pop(next(iter(self._plans)))
+        self._plans[key] = (tuple(weakref.ref(o) for o in (pos, crd, val)), versions, shape, A)
+        return A
 
     def _bind(self, kind, sfx, idx_dtype):
         lib = self.libHandle
@@ -213,6 +256,12 @@ class LAPISModule:
             fn = getattr(lib, f"py_spmv_f64_{sfx}")
 
             def spmv(pos, crd, val, spec, x, y):
+                if _resident(pos, crd, val, x, y):
+                    A = self._plan(pos, crd, val, spec, idx_dtype)
+                    x, y = self._dv(x, np.float64), self._dv(y, np.float64)
+                    A.spmv(x.device_view(), y.device_view(), accumulate=True)
+                    y.modifyDevice()
+                    return y
                 keep, cargs = csr_args(pos, crd, val, spec)
                 x = np.require(x, dtype=np.float64, requirements=["C"])
                 y = np.require(y, dtype=np.float64, requirements=["C"])
@@ -227,6 +276,12 @@ class LAPISModule:
             fn = getattr(lib, f"py_spmm_f64_{sfx}")
 
             def spmm(pos, crd, val, spec, B, C):
+                if _resident(pos, crd, val, B, C):
+                    A = self._plan(pos, crd, val, spec, idx_dtype)
+                    B, C = self._dv(B, np.float64), self._dv(C, np.float64)
+                    A.spmm(B.device_view(), C.device_view(), accumulate=True)
+                    C.modifyDevice()
+                    return C
                 keep, cargs = csr_args(pos, crd, val, spec)
                 B = np.require(B, dtype=np.float64, requirements=["C"])
                 C = np.require(C, dtype=np.float64, requirements=["C"])
@@ -242,6 +297,12 @@ class LAPISModule:
             rank = 2 if kind == "matmul" else 3
 
             def forward(A, B, C):
+                if _resident(A, B, C):
+                    from . import device as D
+                    A, B, C = (self._dv(t, np.float32) for t in (A, B, C))
+                    D.bgemm(A.device_view(), B.device_view(), C.device_view())
+                    C.modifyDevice()
+                    return C
                 A = np.require(A, dtype=np.float32, requirements=["C"])
                 B = np.require(B, dtype=np.float32, requirements=["C"])
                 C = np.require(C, dtype=np.float32, requirements=["C"])
@@ -255,6 +316,12 @@ class LAPISModule:
             fn = getattr(lib, f"py_pcg_f64_{sfx}")
 
             def pcg(pos, crd, val, spec, b, dinv, tol, maxiter):
+                if _resident(pos, crd, val, b, dinv):
+                    from .dualview import DualView
+                    A = self._plan(pos, crd, val, spec, idx_dtype)
+                    b, dinv = self._dv(b, np.float64), self._dv(dinv, np.float64)
+                    x, iters, relres = A.pcg(b.device_view(), dinv.device_view(), float(tol), int(maxiter))
+                    return DualView.from_device(x), iters, relres
                 keep, cargs = csr_args(pos, crd, val, spec)
                 b = np.require(b, dtype=np.float64, requirements=["C"])
                 dinv = np.require(dinv, dtype=np.float64, requirements=["C"])
