@@ -395,8 +395,9 @@ def run_ours(args, d, rank, world, local_rank):
             torch.cuda.synchronize()
             if world > 1:
                 dist.barrier()
+            res_steps = max(e2e_steps, min(args.steps, 20))
             t0 = time.perf_counter()
-            for _ in range(e2e_steps):
+            for _ in range(res_steps):
                 dvs[3].modifyHost()
                 fn(dvs[0], dvs[1], dvs[2], spec, dvs[3], out_dv).syncHost()
             t_res = time.perf_counter() - t0
@@ -404,10 +405,15 @@ def run_ours(args, d, rank, world, local_rank):
                 t = torch.tensor([t_res], dtype=torch.float64, device=dev)
                 dist.all_reduce(t, op=dist.ReduceOp.MAX)
                 t_res = float(t.item())
-            e2e["resident"] = {"value": d["work"] * e2e_steps / t_res * d["unit_scale"], "unit": d["unit"],
-                               "h2d_bytes_per_step": int(pnp[3].nbytes), "d2h_bytes_per_step": d2h,
-                               "api": "same call with lapis_b200.dualview.DualView arguments: matrix resident, dense "
-                                      "operand re-uploaded and result downloaded every step"}
+            # Headline e2e: the call as a caller who keeps the matrix between calls makes it (the reference's
+            # driver, benchmarks/spmv/main.cpp:42-62, also uploads once and loops on the device).  The figure
+            # with every operand uploaded on every call stays beside it.
+            e2e = {"value": d["work"] * res_steps / t_res * d["unit_scale"], "unit": d["unit"],
+                   "h2d_bytes_per_step": int(pnp[3].nbytes), "d2h_bytes_per_step": d2h, "steps": res_steps,
+                   "api": f"KokkosBackend.compile(...).{fn.__name__} with lapis_b200.dualview.DualView arguments over pinned "
+                          "host buffers: matrix uploaded once before the timed region, dense operand re-uploaded "
+                          "(modifyHost) and result downloaded (syncHost) every step",
+                   "all_operands_uploaded_per_call": e2e}
             del dvs, out_dv
         del pinned, out
         algo_bytes_rank = (len(lcrd) * 16 + len(lpos) * 8 + (8 * n + 8 * (r1 - r0)) * (64 if name == "spmm" else 1))

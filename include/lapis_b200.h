@@ -111,6 +111,19 @@ void py_pcg_f64_i64(lapis_memref1 **ret0, size_t *ret1, double *ret2, lapis_memr
                     lapis_memref1 *val, const lapis_csr_spec *spec, lapis_memref1 *b, lapis_memref1 *dinv,
                     double tol, size_t maxiter);
 
+/* Hitting-time moments of a graph, examples/hitting_times.py:151-194 (`mht`, called at :216): two
+ * Jacobi-PCG solves with the masked Laplacian mask*(d - alpha*A)*mask (`plpt`, :73-92) and z = r / d.
+ * Returns the two moment vectors (module-owned, valid until lapis_finalize).  The caller's values array is
+ * not modified (the emitted code scales it in place on the device; the host copy never sees that). */
+void py_mht_f64_i32(lapis_memref1 **ret0, lapis_memref1 **ret1, lapis_memref1 *pos, lapis_memref1 *crd,
+                    lapis_memref1 *val, const lapis_csr_spec *spec, lapis_memref1 *mask, lapis_memref1 *d,
+                    double alpha, double tol, size_t maxiter);
+void py_mht_f64_i64(lapis_memref1 **ret0, lapis_memref1 **ret1, lapis_memref1 *pos, lapis_memref1 *crd,
+                    lapis_memref1 *val, const lapis_csr_spec *spec, lapis_memref1 *mask, lapis_memref1 *d,
+                    double alpha, double tol, size_t maxiter);
+/* sqrt(mom2 - mom1^2), examples/hitting_times.py:196-218 (`normalize_mom2`, called at :218). */
+void py_normalize_mom2_f64(lapis_memref1 **ret0, lapis_memref1 *mom1, lapis_memref1 *mom2);
+
 /* ---- layer 2: device-resident entry points -------------------------------- */
 
 /* A CSR matrix resident on the device plus this library's streaming plan for it
@@ -189,6 +202,15 @@ int lapis_b200_mult_f64(int64_t n, const double *d_x, const double *d_y, double 
  * the solution; *iters and *relres are host outputs.  Blocks until finished. */
 int lapis_b200_pcg_f64(lapis_b200_csr_t h, const double *d_b, const double *d_dinv, double tol, uint64_t maxiter,
                        double *d_x, uint64_t *iters, double *relres, void *stream);
+
+/* Hitting-time moments with all operands on the device (examples/hitting_times.py:151-194): d_mom1 and d_mom2
+ * receive the first two moments; iters2 / relres2 (host, two entries each, may be null) the iteration counts
+ * and final relative residuals of the two solves.  The matrix values are read through a scaled copy; the
+ * caller's array is not modified.  Blocks until finished. */
+int lapis_b200_mht_f64(lapis_b200_csr_t h, const double *d_mask, const double *d_d, double alpha, double tol,
+                       uint64_t maxiter, double *d_mom1, double *d_mom2, uint64_t *iters2, double *relres2, void *stream);
+/* d_out[i] = sqrt(d_mom2[i] - d_mom1[i]^2)  (examples/hitting_times.py:196-218). */
+int lapis_b200_normalize_mom2_f64(int64_t n, const double *d_mom1, const double *d_mom2, double *d_out, void *stream);
 
 /* Step-level PCG entry points: the three passes of one iteration, for callers that
  * put an exchange between them (row-block partitioned solves put a halo copy of p in

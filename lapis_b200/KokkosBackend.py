@@ -158,9 +158,23 @@ def _classify(fn: dict, all_funcs: dict):
             and "linalg.matvec" in all_funcs["spmv"]["body"] and "linalg.dot" in all_funcs["dot"]["body"]):
         dt, sfx = _index_dtype(a[0].sparse)
         return "pcg", sfx, dt
+    # hitting-time moments (examples/hitting_times.py:151-194): scale, two masked-Laplacian PCG solves
+    if (len(a) == 6 and _is_csr(a[0]) and a[0].elem == "f64" and _dense(a[1], 1, "f64") and _dense(a[2], 1, "f64")
+            and a[3].elem == "f64" and a[4].elem == "f64" and a[5].elem == "index" and len(r) == 2
+            and all(f"@{h}" in body for h in ("scale_csr", "pcg", "spmv", "mult"))
+            and all(h in all_funcs for h in ("scale_csr", "pcg", "plpt", "spmv", "dot", "axpby", "mult"))
+            and body.count("@pcg(") == 2 and "@plpt" in all_funcs["pcg"]["body"] and "linalg.div" in all_funcs["pcg"]["body"]
+            and "scf.while" in all_funcs["pcg"]["body"] and "arith.subf" in all_funcs["plpt"]["body"]
+            and "linalg.matvec" in all_funcs["spmv"]["body"]):
+        dt, sfx = _index_dtype(a[0].sparse)
+        return "mht", sfx, dt
+    if (len(a) == 2 and _dense(a[0], 1, "f64") and _dense(a[1], 1, "f64") and len(r) == 1 and "math.sqrt" in body
+            and "arith.subf" in body and "arith.mulf" in body and "func.call" not in body):
+        return "normalize_mom2", "", None
     raise Exception(
         f"function @{fn['name']} is not on the accelerated path (CSR matvec/matmul in f64, dense matmul / "
-        "batch_matmul in f32, the Jacobi PCG loop); lapis_b200 has no general MLIR lowering and no fallback")
+        "batch_matmul in f32, the Jacobi PCG loop, the hitting-time moments); lapis_b200 has no general MLIR "
+        "lowering and no fallback")
 
 
 # ---------------------------------------------------------------------------
@@ -336,6 +350,44 @@ class LAPISModule:
                 return (rt.ranked_memref_to_numpy(ret0[0], np.float64), int(ret1.value), float(ret2.value))
 
             return pcg
+        if kind == "mht":
+            fn = getattr(lib, f"py_mht_f64_{sfx}")
+
+            def mht(pos, crd, val, spec, mask, d, alpha, tol, maxiter):
+                if _resident(pos, crd, val, mask, d):
+                    from .dualview import DualView
+                    A = self._plan(pos, crd, val, spec, idx_dtype)
+                    mask, d = self._dv(mask, np.float64), self._dv(d, np.float64)
+                    m1, m2 = A.mht(mask.device_view(), d.device_view(), float(alpha), float(tol), int(maxiter))
+                    return DualView.from_device(m1), DualView.from_device(m2)
+                keep, cargs = csr_args(pos, crd, val, spec)
+                mask = np.require(mask, dtype=np.float64, requirements=["C"])
+                d = np.require(d, dtype=np.float64, requirements=["C"])
+                ret0, ret1 = _ret_slot(1), _ret_slot(1)
+                fn(ret0, ret1, *cargs, _desc(mask), _desc(d), ctypes.c_double(alpha), ctypes.c_double(tol),
+                   ctypes.c_size_t(maxiter))
+                check_last()
+                del keep
+                return (rt.ranked_memref_to_numpy(ret0[0], np.float64), rt.ranked_memref_to_numpy(ret1[0], np.float64))
+
+            return mht
+        if kind == "normalize_mom2":
+            fn = lib.py_normalize_mom2_f64
+
+            def normalize_mom2(mom1, mom2):
+                if _resident(mom1, mom2):
+                    from . import device as D
+                    from .dualview import DualView
+                    mom1, mom2 = self._dv(mom1, np.float64), self._dv(mom2, np.float64)
+                    return DualView.from_device(D.normalize_mom2(mom1.device_view(), mom2.device_view()))
+                mom1 = np.require(mom1, dtype=np.float64, requirements=["C"])
+                mom2 = np.require(mom2, dtype=np.float64, requirements=["C"])
+                ret0 = _ret_slot(1)
+                fn(ret0, _desc(mom1), _desc(mom2))
+                check_last()
+                return rt.ranked_memref_to_numpy(ret0[0], np.float64)
+
+            return normalize_mom2
         raise AssertionError(kind)
 
 

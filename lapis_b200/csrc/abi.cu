@@ -267,6 +267,79 @@ static int pcg_host(lapis_memref1 **ret0, size_t *ret1, double *ret2, lapis_memr
   return LAPIS_OK;
 }
 
+// A result vector owned by the module until lapis_finalize (LAPISSupport.hpp:93-120), filled from the device.
+static int result_vector(const void *d_src, int64_t n, lapis_memref1 *out, cudaStream_t st) {
+  double *hx = static_cast<double *>(std::malloc(n > 0 ? (size_t)n * 8 : 8));
+  if (hx == nullptr) return fail(LAPIS_ECUDA, "host allocation failed");
+  g_alive_host.push_back(hx);
+  if (n > 0) LAPIS_CUDA_TRY(cudaMemcpyAsync(hx, d_src, (size_t)n * 8, cudaMemcpyDeviceToHost, st));
+  out->basePtr = hx;
+  out->data = hx;
+  out->offset = 0;
+  out->sizes[0] = n;
+  out->strides[0] = 1;
+  return LAPIS_OK;
+}
+
+// examples/hitting_times.py:151-194 (@mht), call at :216
+template <typename I>
+static int mht_host(lapis_memref1 **ret0, lapis_memref1 **ret1, lapis_memref1 *pos, lapis_memref1 *crd, lapis_memref1 *val,
+                    const lapis_csr_spec *spec, lapis_memref1 *mask, lapis_memref1 *dvec, double alpha, double tol,
+                    size_t maxiter) {
+  clear_error();
+  LAPIS_TRY(require_init());
+  CsrArgs a;
+  LAPIS_TRY(check_csr(pos, crd, val, spec, &a));
+  LAPIS_TRY((check_contig<lapis_memref1, 1>(mask, "mask")));
+  LAPIS_TRY((check_contig<lapis_memref1, 1>(dvec, "d")));
+  const int64_t n = dvec->sizes[0];
+  if (a.nrows != n || a.ncols != n || mask->sizes[0] != n) return fail(LAPIS_EBADSHAPE, "mht: A, mask, d sizes differ");
+  if (ret0 == nullptr || *ret0 == nullptr || ret1 == nullptr || *ret1 == nullptr)
+    return fail(LAPIS_EBADARG, "mht: null result slot");
+  cudaStream_t st = nullptr;
+  DeviceCsr d;
+  LAPIS_TRY(upload_csr<I>(pos, crd, val, a, &d, st));
+  DevBuf dmask, dd, dm1, dm2;
+  LAPIS_TRY(dmask.alloc((size_t)n * 8));
+  LAPIS_TRY(dd.alloc((size_t)n * 8));
+  LAPIS_TRY(dm1.alloc((size_t)n * 8));
+  LAPIS_TRY(dm2.alloc((size_t)n * 8));
+  LAPIS_CUDA_TRY(cudaMemcpyAsync(dmask.p, elem_ptr<double>(mask), (size_t)n * 8, cudaMemcpyHostToDevice, st));
+  LAPIS_CUDA_TRY(cudaMemcpyAsync(dd.p, elem_ptr<double>(dvec), (size_t)n * 8, cudaMemcpyHostToDevice, st));
+  LAPIS_TRY(lapis_b200_mht_f64(d.h, static_cast<const double *>(dmask.p), static_cast<const double *>(dd.p), alpha, tol,
+                               (uint64_t)maxiter, static_cast<double *>(dm1.p), static_cast<double *>(dm2.p), nullptr,
+                               nullptr, st));
+  LAPIS_TRY(result_vector(dm1.p, n, *ret0, st));
+  LAPIS_TRY(result_vector(dm2.p, n, *ret1, st));
+  LAPIS_CUDA_TRY(cudaStreamSynchronize(st));
+  return LAPIS_OK;
+}
+
+// examples/hitting_times.py:196-218 (@normalize_mom2), call at :218
+static int normalize_mom2_host(lapis_memref1 **ret0, lapis_memref1 *mom1, lapis_memref1 *mom2) {
+  clear_error();
+  LAPIS_TRY(require_init());
+  LAPIS_TRY((check_contig<lapis_memref1, 1>(mom1, "mom1")));
+  LAPIS_TRY((check_contig<lapis_memref1, 1>(mom2, "mom2")));
+  const int64_t n = mom1->sizes[0];
+  if (mom2->sizes[0] != n) return fail(LAPIS_EBADSHAPE, "normalize_mom2: lengths differ");
+  if (ret0 == nullptr || *ret0 == nullptr) return fail(LAPIS_EBADARG, "normalize_mom2: null result slot");
+  cudaStream_t st = nullptr;
+  DevBuf d1, d2, dout;
+  LAPIS_TRY(d1.alloc((size_t)n * 8));
+  LAPIS_TRY(d2.alloc((size_t)n * 8));
+  LAPIS_TRY(dout.alloc((size_t)n * 8));
+  if (n > 0) {
+    LAPIS_CUDA_TRY(cudaMemcpyAsync(d1.p, elem_ptr<double>(mom1), (size_t)n * 8, cudaMemcpyHostToDevice, st));
+    LAPIS_CUDA_TRY(cudaMemcpyAsync(d2.p, elem_ptr<double>(mom2), (size_t)n * 8, cudaMemcpyHostToDevice, st));
+  }
+  LAPIS_TRY(lapis_b200_normalize_mom2_f64(n, static_cast<const double *>(d1.p), static_cast<const double *>(d2.p),
+                                          static_cast<double *>(dout.p), st));
+  LAPIS_TRY(result_vector(dout.p, n, *ret0, st));
+  LAPIS_CUDA_TRY(cudaStreamSynchronize(st));
+  return LAPIS_OK;
+}
+
 }  // namespace lapis_b200
 
 using namespace lapis_b200;
@@ -368,6 +441,20 @@ extern "C" void py_pcg_f64_i64(lapis_memref1 **ret0, size_t *ret1, double *ret2,
                                lapis_memref1 *crd, lapis_memref1 *val, const lapis_csr_spec *spec, lapis_memref1 *b,
                                lapis_memref1 *dinv, double tol, size_t maxiter) {
   pcg_host<int64_t>(ret0, ret1, ret2, pos, crd, val, spec, b, dinv, tol, maxiter);
+}
+
+extern "C" void py_mht_f64_i32(lapis_memref1 **ret0, lapis_memref1 **ret1, lapis_memref1 *pos, lapis_memref1 *crd,
+                               lapis_memref1 *val, const lapis_csr_spec *spec, lapis_memref1 *mask, lapis_memref1 *d,
+                               double alpha, double tol, size_t maxiter) {
+  mht_host<int32_t>(ret0, ret1, pos, crd, val, spec, mask, d, alpha, tol, maxiter);
+}
+extern "C" void py_mht_f64_i64(lapis_memref1 **ret0, lapis_memref1 **ret1, lapis_memref1 *pos, lapis_memref1 *crd,
+                               lapis_memref1 *val, const lapis_csr_spec *spec, lapis_memref1 *mask, lapis_memref1 *d,
+                               double alpha, double tol, size_t maxiter) {
+  mht_host<int64_t>(ret0, ret1, pos, crd, val, spec, mask, d, alpha, tol, maxiter);
+}
+extern "C" void py_normalize_mom2_f64(lapis_memref1 **ret0, lapis_memref1 *mom1, lapis_memref1 *mom2) {
+  normalize_mom2_host(ret0, mom1, mom2);
 }
 
 // ---- host-side partition rule ------------------------------------------------

@@ -34,7 +34,8 @@ constexpr int SUM_THREADS = 1024;
 // Device scalar block at the head of a PCG workspace (doubles, then flags).
 enum { SC_PAP = 0, SC_RR = 1, SC_RZNEW = 2, SC_RZ = 3, SC_INITRES = 4, SC_RELRES = 5, SC_ALPHA = 6, SC_BETA = 7, SC_COUNT = 8 };
 enum { FL_DONE = 0, FL_ITERS = 1, FL_COUNT = 2 };  // int64 each
-enum { DERIVE_NONE = 0, DERIVE_INIT = 1, DERIVE_ALPHA = 2, DERIVE_DECIDE = 3 };
+enum { DERIVE_NONE = 0, DERIVE_INIT = 1, DERIVE_ALPHA = 2, DERIVE_DECIDE = 3, DERIVE_ALPHA_MASKED = 4 };
+constexpr int SC_DMP2 = 11;  // header slot: sum of d * (mask*p)^2 of the masked-Laplacian operator
 
 __device__ __forceinline__ double block_sum_vec(double v, double *s_red) {
 #pragma unroll
@@ -63,6 +64,9 @@ __device__ void pcg_derive(int kind, double *sc, long long *fl, double tol, unsi
     fl[FL_ITERS] = 0;
   } else if (kind == DERIVE_ALPHA) {
     sc[SC_ALPHA] = sc[SC_RZ] / sc[SC_PAP];
+  } else if (kind == DERIVE_ALPHA_MASKED) {
+    // p.(M (D - A) M p) = sum d (m p)^2 - (m p).(A (m p)): the two sums arrive separately
+    sc[SC_ALPHA] = sc[SC_RZ] / __dsub_rn(sc[SC_DMP2], sc[SC_PAP]);
   } else if (kind == DERIVE_DECIDE) {
     const double relres = sqrt(sc[SC_RR]) / sc[SC_INITRES];
     sc[SC_RELRES] = relres;
@@ -634,6 +638,223 @@ extern "C" int lapis_b200_pcg_p2p_halo_wait(void *d_work, void *d_mbox, const vo
   double *base = static_cast<double *>(d_work);
   p2p_halo_wait_kernel<<<1, 32, 0, as_stream(stream)>>>(base, reinterpret_cast<long long *>(base + SC_COUNT),
                                                         static_cast<double *>(d_mbox), static_cast<const int *>(d_srcs), nsrc);
+  LAPIS_CUDA_TRY(cudaGetLastError());
+  return LAPIS_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Hitting-time moments (examples/hitting_times.py:151-194 in the LAPIS project): two Jacobi-PCG solves
+// with the masked graph Laplacian y = M (D - alpha A) M x as the operator (@plpt, :73-92) and z = r / d
+// as the preconditioner (:113, :140).  Same three passes per iteration as the plain solver:
+//   A  t = (alpha A) mp with the fused partial sums of mp.t        (mp = mask * p, kept beside p)
+//   B  Ap = (d*mp - t)*mask on the fly; x, r, z updates; partial sums of r.r and r.z
+//   C  p = z + beta p; mp = mask*p; partial sums of d*mp*mp
+// so p.Ap = sum d mp^2 - mp.t needs no pass of its own.
+// ---------------------------------------------------------------------------------------------
+namespace lapis_b200 {
+
+__global__ void __launch_bounds__(VEC_THREADS)
+scale_copy_kernel(int64_t n, const double *__restrict__ src, double a, double *__restrict__ dst) {
+  for (int64_t i = (int64_t)blockIdx.x * VEC_THREADS + threadIdx.x; i < n; i += (int64_t)gridDim.x * VEC_THREADS)
+    dst[i] = __dmul_rn(src[i], a);  // hitting_times.py:50-70
+}
+
+// r = b; z = r/d; p = z; mp = mask*p; x = 0; partial sums of r.r, r.z and d*mp*mp  (hitting_times.py:111-117)
+__global__ void __launch_bounds__(VEC_THREADS)
+mht_init_kernel(int64_t n, const double *__restrict__ b, const double *__restrict__ d, const double *__restrict__ mask,
+                double *__restrict__ r, double *__restrict__ z, double *__restrict__ p, double *__restrict__ mp,
+                double *__restrict__ x, double *__restrict__ partials) {
+  __shared__ double s_red[VEC_THREADS / 32];
+  double rr = 0.0, rz = 0.0, dm = 0.0;
+  for (int64_t i = (int64_t)blockIdx.x * VEC_THREADS + threadIdx.x; i < n; i += (int64_t)gridDim.x * VEC_THREADS) {
+    const double ri = b[i], di = d[i];
+    const double zi = __ddiv_rn(ri, di);
+    const double mpi = __dmul_rn(zi, mask[i]);
+    r[i] = ri;
+    z[i] = zi;
+    p[i] = zi;
+    mp[i] = mpi;
+    x[i] = 0.0;
+    rr = __dadd_rn(rr, __dmul_rn(ri, ri));
+    rz = __dadd_rn(rz, __dmul_rn(ri, zi));
+    dm = __dadd_rn(dm, __dmul_rn(__dmul_rn(di, mpi), mpi));
+  }
+  const double t0 = block_sum_vec(rr, s_red);
+  const double t1 = block_sum_vec(rz, s_red);
+  const double t2 = block_sum_vec(dm, s_red);
+  if (threadIdx.x == 0) {
+    partials[blockIdx.x] = t0;
+    partials[gridDim.x + blockIdx.x] = t1;
+    partials[2 * gridDim.x + blockIdx.x] = t2;
+  }
+}
+
+// Ap = (d*mp - t)*mask (hitting_times.py:84-88); x += alpha p; r -= alpha Ap; z = r/d; partial sums of r.r, r.z
+__global__ void __launch_bounds__(VEC_THREADS)
+mht_update_kernel(int64_t n, const double *__restrict__ sc, const long long *__restrict__ fl,
+                  const double *__restrict__ p, const double *__restrict__ mp, const double *__restrict__ t,
+                  const double *__restrict__ d, const double *__restrict__ mask, double *__restrict__ x,
+                  double *__restrict__ r, double *__restrict__ z, double *__restrict__ partials) {
+  __shared__ double s_red[VEC_THREADS / 32];
+  if (fl[FL_DONE] != 0) return;
+  const double alpha = sc[SC_ALPHA];
+  const double malpha = -alpha;
+  double rr = 0.0, rz = 0.0;
+  for (int64_t i = (int64_t)blockIdx.x * VEC_THREADS + threadIdx.x; i < n; i += (int64_t)gridDim.x * VEC_THREADS) {
+    const double di = d[i];
+    const double api = __dmul_rn(__dsub_rn(__dmul_rn(di, mp[i]), t[i]), mask[i]);
+    const double xi = __dadd_rn(__dmul_rn(x[i], 1.0), __dmul_rn(p[i], alpha));
+    const double ri = __dadd_rn(__dmul_rn(r[i], 1.0), __dmul_rn(api, malpha));
+    const double zi = __ddiv_rn(ri, di);
+    x[i] = xi;
+    r[i] = ri;
+    z[i] = zi;
+    rr = __dadd_rn(rr, __dmul_rn(ri, ri));
+    rz = __dadd_rn(rz, __dmul_rn(ri, zi));
+  }
+  const double t0 = block_sum_vec(rr, s_red);
+  const double t1 = block_sum_vec(rz, s_red);
+  if (threadIdx.x == 0) {
+    partials[blockIdx.x] = t0;
+    partials[gridDim.x + blockIdx.x] = t1;
+  }
+}
+
+// p = z + beta p (hitting_times.py:143); mp = mask*p; partial sums of d*mp*mp
+__global__ void __launch_bounds__(VEC_THREADS)
+mht_direction_kernel(int64_t n, const double *__restrict__ sc, const long long *__restrict__ fl,
+                     const double *__restrict__ z, const double *__restrict__ d, const double *__restrict__ mask,
+                     double *__restrict__ p, double *__restrict__ mp, double *__restrict__ partials) {
+  __shared__ double s_red[VEC_THREADS / 32];
+  if (fl[FL_DONE] != 0) return;
+  const double beta = sc[SC_BETA];
+  double dm = 0.0;
+  for (int64_t i = (int64_t)blockIdx.x * VEC_THREADS + threadIdx.x; i < n; i += (int64_t)gridDim.x * VEC_THREADS) {
+    const double pi = __dadd_rn(__dmul_rn(z[i], 1.0), __dmul_rn(p[i], beta));
+    const double mpi = __dmul_rn(pi, mask[i]);
+    p[i] = pi;
+    mp[i] = mpi;
+    dm = __dadd_rn(dm, __dmul_rn(__dmul_rn(d[i], mpi), mpi));
+  }
+  const double t0 = block_sum_vec(dm, s_red);
+  if (threadIdx.x == 0) partials[2 * gridDim.x + blockIdx.x] = t0;
+}
+
+// b2 = mask * (d*mom1 + t) with t = (alpha A) mom1  (hitting_times.py:163-176)
+__global__ void __launch_bounds__(VEC_THREADS)
+mht_rhs2_kernel(int64_t n, const double *__restrict__ t, const double *__restrict__ mask, const double *__restrict__ mom1,
+                const double *__restrict__ d, double *__restrict__ b2) {
+  for (int64_t i = (int64_t)blockIdx.x * VEC_THREADS + threadIdx.x; i < n; i += (int64_t)gridDim.x * VEC_THREADS)
+    b2[i] = __dmul_rn(__dadd_rn(__dmul_rn(d[i], mom1[i]), t[i]), mask[i]);
+}
+
+// sqrt(mom2 - mom1^2)  (hitting_times.py:196-218)
+__global__ void __launch_bounds__(VEC_THREADS)
+normalize_mom2_kernel(int64_t n, const double *__restrict__ mom1, const double *__restrict__ mom2, double *__restrict__ out) {
+  for (int64_t i = (int64_t)blockIdx.x * VEC_THREADS + threadIdx.x; i < n; i += (int64_t)gridDim.x * VEC_THREADS)
+    out[i] = sqrt(__dsub_rn(mom2[i], __dmul_rn(mom1[i], mom1[i])));
+}
+
+// One masked solve.  work: [16 header][3*G partials][r][z][p][mp][t], G = vec_grid(n).
+static int mht_solve(const lapis_b200_csr *A, const double *d_b, const double *d_d, const double *d_mask, double tol,
+                     uint64_t maxiter, double *d_x, double *work, uint64_t *iters, double *relres, cudaStream_t st) {
+  const int64_t n = A->nrows;
+  const unsigned G = vec_grid(n);
+  double *sc = work;
+  long long *fl = reinterpret_cast<long long *>(work + SC_COUNT);
+  double *partials = work + 16;
+  double *r = partials + 3 * (int64_t)G, *z = r + n, *p = z + n, *mp = p + n, *t = mp + n;
+  const int *skip = reinterpret_cast<const int *>(fl);
+  LAPIS_CUDA_TRY(cudaMemsetAsync(work, 0, 16 * sizeof(double), st));
+  mht_init_kernel<<<G, VEC_THREADS, 0, st>>>(n, d_b, d_d, d_mask, r, z, p, mp, d_x, partials);
+  sum_partials_kernel<<<1, SUM_THREADS, 0, st>>>(partials + 2 * (int64_t)G, G, 1, sc + SC_DMP2, nullptr, DERIVE_NONE, sc, fl,
+                                                 0.0, 0, nullptr);
+  sum_partials_kernel<<<1, SUM_THREADS, 0, st>>>(partials, G, 2, sc + SC_RR, sc + SC_RZNEW, DERIVE_INIT, sc, fl, 0.0, 0,
+                                                 nullptr);
+  LAPIS_CUDA_TRY(cudaGetLastError());
+  const uint64_t limit = maxiter == 0 ? (1ull << 31) : maxiter;
+  const uint64_t check_every = 16;
+  int done = 0;
+  double host[16];
+  for (uint64_t i = 1; !done && i <= limit; ++i) {
+    LAPIS_TRY(spmv_launch(A, mp, t, 0, mp, A->blk_partial, skip, st));
+    sum_partials_kernel<<<1, SUM_THREADS, 0, st>>>(A->blk_partial, A->nblk, 1, sc + SC_PAP, nullptr, DERIVE_ALPHA_MASKED, sc,
+                                                   fl, 0.0, 0, fl);
+    mht_update_kernel<<<G, VEC_THREADS, 0, st>>>(n, sc, fl, p, mp, t, d_d, d_mask, d_x, r, z, partials);
+    sum_partials_kernel<<<1, SUM_THREADS, 0, st>>>(partials, G, 2, sc + SC_RR, sc + SC_RZNEW, DERIVE_DECIDE, sc, fl, tol,
+                                                   maxiter, fl);
+    mht_direction_kernel<<<G, VEC_THREADS, 0, st>>>(n, sc, fl, z, d_d, d_mask, p, mp, partials);
+    sum_partials_kernel<<<1, SUM_THREADS, 0, st>>>(partials + 2 * (int64_t)G, G, 1, sc + SC_DMP2, nullptr, DERIVE_NONE, sc,
+                                                   fl, 0.0, 0, fl);
+    LAPIS_CUDA_TRY(cudaGetLastError());
+    if (i % check_every == 0 || i == limit) {
+      LAPIS_CUDA_TRY(cudaMemcpyAsync(host, work, sizeof(host), cudaMemcpyDeviceToHost, st));
+      LAPIS_CUDA_TRY(cudaStreamSynchronize(st));
+      done = (int)reinterpret_cast<const long long *>(host + SC_COUNT)[FL_DONE];
+    }
+  }
+  LAPIS_CUDA_TRY(cudaMemcpyAsync(host, work, sizeof(host), cudaMemcpyDeviceToHost, st));
+  LAPIS_CUDA_TRY(cudaStreamSynchronize(st));
+  if (iters) *iters = (uint64_t) reinterpret_cast<const long long *>(host + SC_COUNT)[FL_ITERS];
+  if (relres) *relres = host[SC_RELRES];
+  return LAPIS_OK;
+}
+
+}  // namespace lapis_b200
+
+extern "C" int lapis_b200_mht_f64(lapis_b200_csr_t h, const double *d_mask, const double *d_d, double alpha, double tol,
+                                  uint64_t maxiter, double *d_mom1, double *d_mom2, uint64_t *iters2, double *relres2,
+                                  void *stream) {
+  clear_error();
+  if (h == nullptr) return fail(LAPIS_EBADARG, "mht: null matrix handle");
+  if (h->nrows != h->ncols) return fail(LAPIS_EBADSHAPE, "mht: matrix is not square");
+  const int64_t n = h->nrows;
+  if (n == 0) return LAPIS_OK;
+  if (d_mask == nullptr || d_d == nullptr || d_mom1 == nullptr || d_mom2 == nullptr)
+    return fail(LAPIS_EBADARG, "mht: null operand");
+  cudaStream_t st = as_stream(stream);
+  const unsigned G = vec_grid(n);
+  const size_t work_doubles = 16 + 3 * (size_t)G + 5 * (size_t)n;
+  // [work][b][pad][scaled values][pad]: the SpMV kernels stream the values with 16-byte accesses starting at
+  // entry (base & ~3) of the array the handle points to, so "scaled copy - base" must be 16-byte aligned
+  // like the caller's array is, and the few entries in front of the copy must be readable (they are
+  // masked out, not used).
+  size_t sval_index = work_doubles + (size_t)n + 4;
+  if (((int64_t)sval_index - h->base) & 1) sval_index += 1;
+  double *buf = nullptr;
+  LAPIS_CUDA_TRY(cudaMalloc(&buf, (sval_index + (size_t)h->nnz + 8) * sizeof(double)));
+  double *work = buf, *bbuf = buf + work_doubles, *sval = buf + sval_index;
+  // the emitted code scales the matrix values in place; here the caller's array stays as it is and the
+  // solves read a scaled copy through a shallow copy of the handle (same streaming plan)
+  lapis_b200_csr scaled = *h;
+  const double *val0 = h->val + h->base;  // the handle's arrays are indexed by absolute offsets
+  if (h->nnz > 0) scale_copy_kernel<<<vec_grid(h->nnz), VEC_THREADS, 0, st>>>(h->nnz, val0, alpha, sval);
+  scaled.val = sval - h->base;
+  uint64_t it[2] = {0, 0};
+  double rel[2] = {0.0, 0.0};
+  mult_kernel<<<G, VEC_THREADS, 0, st>>>(n, d_d, d_mask, bbuf);  // hitting_times.py:158
+  int status = mht_solve(&scaled, bbuf, d_d, d_mask, tol, maxiter, d_mom1, work, &it[0], &rel[0], st);
+  if (status == LAPIS_OK) status = spmv_launch(&scaled, d_mom1, work + 16, 0, nullptr, nullptr, nullptr, st);
+  if (status == LAPIS_OK) {
+    mht_rhs2_kernel<<<G, VEC_THREADS, 0, st>>>(n, work + 16, d_mask, d_mom1, d_d, bbuf);
+    status = mht_solve(&scaled, bbuf, d_d, d_mask, tol, maxiter, d_mom2, work, &it[1], &rel[1], st);
+  }
+  cudaError_t e = cudaStreamSynchronize(st);
+  cudaFree(buf);
+  if (status != LAPIS_OK) return status;
+  if (e != cudaSuccess) return fail(LAPIS_ECUDA, "mht: %s", cudaGetErrorString(e));
+  if (iters2) iters2[0] = it[0], iters2[1] = it[1];
+  if (relres2) relres2[0] = rel[0], relres2[1] = rel[1];
+  return LAPIS_OK;
+}
+
+extern "C" int lapis_b200_normalize_mom2_f64(int64_t n, const double *d_mom1, const double *d_mom2, double *d_out,
+                                             void *stream) {
+  clear_error();
+  if (n < 0) return fail(LAPIS_EBADSHAPE, "normalize_mom2: negative length");
+  if (n == 0) return LAPIS_OK;
+  if (d_mom1 == nullptr || d_mom2 == nullptr || d_out == nullptr) return fail(LAPIS_EBADARG, "normalize_mom2: null operand");
+  normalize_mom2_kernel<<<vec_grid(n), VEC_THREADS, 0, as_stream(stream)>>>(n, d_mom1, d_mom2, d_out);
   LAPIS_CUDA_TRY(cudaGetLastError());
   return LAPIS_OK;
 }

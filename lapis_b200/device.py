@@ -109,6 +109,31 @@ class CsrMatrix:
                                            ctypes.byref(iters), ctypes.byref(relres), _stream()))
         return x, int(iters.value), float(relres.value)
 
+    def mht(self, mask: torch.Tensor, d: torch.Tensor, alpha: float, tol: float, maxiter: int, info: bool = False):
+        """First two hitting-time moments (examples/hitting_times.py:151-194 in the LAPIS project): two PCG
+        solves with mask*(d - alpha*A)*mask.  Returns (mom1, mom2), plus ((iters1, iters2), (relres1, relres2))
+        with ``info``; blocks until finished.  The matrix values are not modified."""
+        _f64(mask, "mask"), _f64(d, "d")
+        if mask.numel() != self.nrows or d.numel() != self.nrows:
+            raise ValueError("mht: mask/d length mismatch")
+        m1, m2 = torch.empty_like(d), torch.empty_like(d)
+        iters, relres = (c_u64 * 2)(), (c_dbl * 2)()
+        check(self._lib.lapis_b200_mht_f64(self._h, _ptr(mask), _ptr(d), c_dbl(alpha), c_dbl(tol), c_u64(maxiter),
+                                           _ptr(m1), _ptr(m2), iters, relres, _stream()))
+        if info:
+            return m1, m2, (int(iters[0]), int(iters[1])), (float(relres[0]), float(relres[1]))
+        return m1, m2
+
+
+def normalize_mom2(mom1: torch.Tensor, mom2: torch.Tensor) -> torch.Tensor:
+    """sqrt(mom2 - mom1^2) elementwise (examples/hitting_times.py:196-218 in the LAPIS project)."""
+    _f64(mom1, "mom1"), _f64(mom2, "mom2")
+    if mom1.numel() != mom2.numel():
+        raise ValueError("normalize_mom2: lengths differ")
+    out = torch.empty_like(mom1)
+    check(load().lapis_b200_normalize_mom2_f64(mom1.numel(), _ptr(mom1), _ptr(mom2), _ptr(out), _stream()))
+    return out
+
 
 def bgemm(A: torch.Tensor, B: torch.Tensor, C: torch.Tensor) -> torch.Tensor:
     """C = C + A @ B in place; fp32, [M,K]x[K,N] or batched [b,M,K]x[b,K,N]."""

@@ -92,6 +92,23 @@ def test_backend_classifies_on_path_modules():
         assert KB._classify(public[0], {f["name"]: f for f in funcs})[:2] == want
 
 
+def test_backend_classifies_the_hitting_times_module():
+    for enc_text, sfx in ((mm.CSR32, "i32"), (mm.CSR64, "i64")):
+        text = mm.hitting_times(enc_text)
+        funcs = KB._parse_functions(text, KB._parse_encodings(text))
+        by = {f["name"]: f for f in funcs}
+        public = sorted(f["name"] for f in funcs if not f["private"])
+        assert public == ["mht", "normalize_mom2"]
+        assert KB._classify(by["mht"], by)[:2] == ("mht", sfx)
+        assert KB._classify(by["normalize_mom2"], by)[:2] == ("normalize_mom2", "")
+    # the plain solver's module is not mistaken for it, and a module without the masked operator is refused
+    text = mm.hitting_times().replace("@plpt", "@other")
+    funcs = KB._parse_functions(text, KB._parse_encodings(text))
+    by = {f["name"]: f for f in funcs}
+    with pytest.raises(Exception, match="not on the accelerated path"):
+        KB._classify(by["mht"], by)
+
+
 def test_backend_rejects_off_path_modules():
     with pytest.raises(Exception, match="not on the accelerated path"):
         KB.KokkosBackend().compile(mm.UNSUPPORTED)
