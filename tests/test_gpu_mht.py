@@ -1,5 +1,7 @@
 """Hitting-time moments on the GPU (masked-Laplacian PCG): against the reference's 17-digit golden vectors
 (examples/hitting_times.py:219-222 in the LAPIS project), and against the oracle on a generated graph."""
+import os
+
 import numpy as np
 import pytest
 import torch
@@ -29,7 +31,7 @@ def _random_graph(n, deg, seed):
 
 
 def test_mht_golden_vectors_through_backend(golden_dir):
-    g = np.load(golden_dir / "mht.npz")
+    g = dict(np.load(os.path.join(golden_dir, "mht.npz")))
     n = len(g["D"])
     nnz = len(g["data"])
     module = KB.KokkosBackend(decompose_tensors=True).compile(mm.hitting_times(mm.CSR32))
