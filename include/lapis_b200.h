@@ -69,6 +69,12 @@ typedef struct { void *basePtr; void *data; int64_t offset; int64_t sizes[3]; in
  * (TranslateToKokkosCpp.cpp:4495-4546; benchmarks/spmv/main.cpp:48-51):
  * {rows, cols, len(pos), len(crd), len(val)} as five contiguous int64. */
 typedef struct { int64_t dims[2]; int64_t mem_sizes[3]; } lapis_csr_spec;
+/* The same for a 3-D CSRV tensor (dense, compressed, dense), examples/bspmm.py:103:
+ * {n1, n2, nh, len(pos), len(crd), len(val) = stored entries * nh}. */
+typedef struct { int64_t dims[3]; int64_t mem_sizes[3]; } lapis_csrv_spec;
+/* And for a 2-D DCSR matrix (compressed, compressed), buffers in the order of
+ * examples/spmm_dcsr_opdsl.py:137-143, 156: {rows, cols, len(p1), len(i1), len(p2), len(i2), len(val)}. */
+typedef struct { int64_t dims[2]; int64_t mem_sizes[5]; } lapis_dcsr_spec;
 
 /* ---- layer 1: emitted-module ABI ------------------------------------------ */
 
@@ -123,6 +129,24 @@ void py_mht_f64_i64(lapis_memref1 **ret0, lapis_memref1 **ret1, lapis_memref1 *p
                     double alpha, double tol, size_t maxiter);
 /* sqrt(mom2 - mom1^2), examples/hitting_times.py:196-218 (`normalize_mom2`, called at :218). */
 void py_normalize_mom2_f64(lapis_memref1 **ret0, lapis_memref1 *mom1, lapis_memref1 *mom2);
+
+/* Batched SpMM over a CSRV tensor, fp32: out[n1, dh, nh] = sum_n2 A[n1, n2, nh] * B[n2, dh, nh].  Replaces
+ * `pte_local_bspmm` of examples/bspmm.py:26-52 (called at :103): the result is a new zero-initialised tensor
+ * (module-owned, valid until lapis_finalize). */
+void py_bspmm_f32_i32(lapis_memref3 **ret0, lapis_memref1 *pos, lapis_memref1 *crd, lapis_memref1 *val,
+                      const lapis_csrv_spec *spec, lapis_memref3 *B);
+void py_bspmm_f32_i64(lapis_memref3 **ret0, lapis_memref1 *pos, lapis_memref1 *crd, lapis_memref1 *val,
+                      const lapis_csrv_spec *spec, lapis_memref3 *B);
+
+/* C += A B with A in DCSR, fp64.  The operation of `spMxM` in examples/spmm_dcsr_opdsl.py:59-101 (called at
+ * :160) in the decomposed-argument form (the example itself passes an opaque sparse-runtime handle, which
+ * this library does not take).  Returns its in/out argument C. */
+void py_spmm_dcsr_f64_i32(lapis_memref2 **ret0, lapis_memref1 *p1, lapis_memref1 *i1, lapis_memref1 *p2,
+                          lapis_memref1 *i2, lapis_memref1 *val, const lapis_dcsr_spec *spec, lapis_memref2 *B,
+                          lapis_memref2 *C);
+void py_spmm_dcsr_f64_i64(lapis_memref2 **ret0, lapis_memref1 *p1, lapis_memref1 *i1, lapis_memref1 *p2,
+                          lapis_memref1 *i2, lapis_memref1 *val, const lapis_dcsr_spec *spec, lapis_memref2 *B,
+                          lapis_memref2 *C);
 
 /* ---- layer 2: device-resident entry points -------------------------------- */
 
@@ -202,6 +226,20 @@ int lapis_b200_mult_f64(int64_t n, const double *d_x, const double *d_y, double 
  * the solution; *iters and *relres are host outputs.  Blocks until finished. */
 int lapis_b200_pcg_f64(lapis_b200_csr_t h, const double *d_b, const double *d_dinv, double tol, uint64_t maxiter,
                        double *d_x, uint64_t *iters, double *relres, void *stream);
+
+/* Batched SpMM over a CSRV tensor on the device (examples/bspmm.py:14-52): d_val holds nh values per stored
+ * entry, d_B is [n2, dh, nh], d_C is [n1, dh, nh], all row-major fp32.  Every output element is updated in
+ * ascending entry order starting from its old value (accumulate != 0) or from zero: bit-identical to the
+ * sequential loop nest. */
+int lapis_b200_bspmm_csrv_f32(int idx_bytes, int64_t n1, int64_t n2, int64_t nh, int64_t dh, const void *d_pos,
+                              const void *d_crd, const float *d_val, const float *d_B, float *d_C, int accumulate,
+                              void *stream);
+/* C[i1[r], :] += sum_j val[j] * B[i2[j], :] over the nstored stored rows of a DCSR matrix
+ * (examples/spmm_dcsr_opdsl.py:59-101); rows that are not stored keep their values; d_i1 ascends (a row
+ * number may repeat).  Bit-identical to the sequential loop nest. */
+int lapis_b200_spmm_dcsr_f64(int idx_bytes, int64_t nrows, int64_t ncols, int64_t nstored, int64_t k, const void *d_i1,
+                             const void *d_p2, const void *d_i2, const double *d_val, const double *d_B, double *d_C,
+                             void *stream);
 
 /* Hitting-time moments with all operands on the device (examples/hitting_times.py:151-194): d_mom1 and d_mom2
  * receive the first two moments; iters2 / relres2 (host, two entries each, may be null) the iteration counts

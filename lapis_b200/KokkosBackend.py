@@ -136,9 +136,45 @@ def _dense(t: _Type, rank: int, elem: str) -> bool:
     return t.sparse is None and t.rank == rank and t.elem == elem
 
 
-def _classify(fn: dict, all_funcs: dict):
+def _is_csrv(t: _Type) -> bool:
+    return t.sparse is not None and t.rank == 3 and t.sparse["levels"] == ["dense", "compressed", "dense"]
+
+
+def _is_dcsr(t: _Type) -> bool:
+    return t.sparse is not None and t.rank == 2 and t.sparse["levels"] == ["compressed", "compressed"]
+
+
+def _indexing_maps(text: str):
+    """Every `indexing_maps = [...]` list of the text as tuples of dimension positions."""
+    out = []
+    for m in re.finditer(r"indexing_maps\s*=\s*\[(.*?)\]", text, re.S):
+        maps = []
+        for mm_ in re.finditer(r"affine_map<\(([^)]*)\)\s*->\s*\(([^)]*)\)>", m.group(1)):
+            dims = [d.strip() for d in mm_.group(1).split(",")]
+            try:
+                maps.append(tuple(dims.index(d.strip()) for d in mm_.group(2).split(",")))
+            except ValueError:
+                maps.append(None)
+        out.append(maps)
+    return out
+
+
+def _classify(fn: dict, all_funcs: dict, module_text: str = ""):
     """Returns (kind, index suffix, index dtype) or raises for an off-path function."""
     a, r, body = fn["args"], fn["results"], fn["body"]
+    # a function that only prints its sparse argument (examples/bspmm.py:54-58, spmm_dcsr_opdsl.py:66-68): host work
+    if len(a) == 1 and a[0].sparse is not None and len(r) == 0 and "sparse_tensor.print" in body and "linalg." not in body:
+        return "print", "x".join(a[0].sparse["levels"]), None
+    # batched SpMM over a CSRV tensor (examples/bspmm.py:14-52): out(n1,dh,nh) = sum_n2 A(n1,n2,nh) * B(n2,dh,nh)
+    if (len(a) == 2 and _is_csrv(a[0]) and a[0].elem == "f32" and _dense(a[1], 3, "f32") and len(r) == 1
+            and "linalg.generic" in body and "arith.mulf" in body and "arith.addf" in body and "linalg.fill" in body
+            and [(0, 1, 3), (1, 2, 3), (0, 2, 3)] in _indexing_maps(module_text)):
+        dt, sfx = _index_dtype(a[0].sparse)
+        return "bspmm", sfx, dt
+    if (len(a) == 3 and _is_dcsr(a[0]) and a[0].elem == "f64" and _dense(a[1], 2, "f64") and _dense(a[2], 2, "f64")
+            and len(r) == 1 and ("linalg.matmul" in body or [(1, 0), (0, 2), (1, 2)] in _indexing_maps(body))):
+        dt, sfx = _index_dtype(a[0].sparse)
+        return "spmm_dcsr", sfx, dt
     if (len(a) == 3 and _is_csr(a[0]) and a[0].elem == "f64" and _dense(a[1], 1, "f64") and _dense(a[2], 1, "f64")
             and "linalg.matvec" in body and len(r) == 1):
         dt, sfx = _index_dtype(a[0].sparse)
@@ -350,6 +386,84 @@ class LAPISModule:
                 return (rt.ranked_memref_to_numpy(ret0[0], np.float64), int(ret1.value), float(ret2.value))
 
             return pcg
+        if kind == "print":
+            nbuf = 2 * sfx.split("x").count("compressed") + 1  # pos and crd per compressed level, then the values
+
+            def print_tensor(*args):
+                """Prints the decomposed sparse tensor (buffers..., specifier) on the host in the layout of
+                ``sparse_tensor.print``: stored-entry count, dimensions, then each level's buffers."""
+                if len(args) != nbuf + 1:
+                    raise TypeError(f"expected {nbuf} buffers and the storage specifier")
+                bufs = [np.asarray(getattr(b, "numpy", lambda: b)()) for b in args[:nbuf]]
+                dims = tuple(int(x) for x in args[-1][0])
+                print("---- Sparse Tensor ----")
+                print(f"nse = {len(bufs[-1])}")
+                print("dim = ( " + ", ".join(str(x) for x in dims) + " )")
+                lvl = 0
+                it = iter(bufs[:-1])
+                for kind_ in sfx.split("x"):
+                    if kind_ == "compressed":
+                        for name in ("pos", "crd"):
+                            print(f"{name}[{lvl}] : ( " + ", ".join(str(int(x)) for x in next(it)) + " )")
+                    lvl += 1
+                print("values : ( " + ", ".join(repr(float(x)) for x in bufs[-1]) + " )")
+                print("----")
+
+            return print_tensor
+        if kind == "bspmm":
+            fn = getattr(lib, f"py_bspmm_f32_{sfx}")
+
+            def bspmm(pos, crd, val, spec, B):
+                flat = np.array(list(spec[0]) + list(spec[1]), dtype=np.int64)
+                if flat.shape != (6,):
+                    raise LapisError(1, "the CSRV specifier is ((n1, n2, nh), (len pos, len crd, len val))")
+                if _resident(pos, crd, val, B):
+                    from . import device as D
+                    from .dualview import DualView
+                    pos, crd = self._dv(pos, idx_dtype), self._dv(crd, idx_dtype)
+                    val, B = self._dv(val, np.float32), self._dv(B, np.float32)
+                    if (pos.extent(0), crd.extent(0), val.extent(0)) != tuple(flat[3:]) or flat[3] != flat[0] + 1:
+                        raise LapisError(1, "storage specifier does not match the pos/crd/val arrays")
+                    C = D.bspmm_csrv(pos.device_view(), crd.device_view(), val.device_view(), B.device_view(),
+                                     int(flat[1]), None)
+                    return DualView.from_device(C)
+                pos = np.require(pos, dtype=idx_dtype, requirements=["C"])
+                crd = np.require(crd, dtype=idx_dtype, requirements=["C"])
+                val = np.require(val, dtype=np.float32, requirements=["C"])
+                B = np.require(B, dtype=np.float32, requirements=["C"])
+                ret0 = _ret_slot(3)
+                fn(ret0, _desc(pos), _desc(crd), _desc(val), flat.ctypes.data_as(ctypes.c_void_p), _desc(B))
+                check_last()
+                return rt.ranked_memref_to_numpy(ret0[0], np.float32)
+
+            return bspmm
+        if kind == "spmm_dcsr":
+            fn = getattr(lib, f"py_spmm_dcsr_f64_{sfx}")
+
+            def spmm_dcsr(p1, i1, p2, i2, val, spec, B, C):
+                flat = np.array(list(spec[0]) + list(spec[1]), dtype=np.int64)
+                if flat.shape != (7,):
+                    raise LapisError(1, "the DCSR specifier is ((rows, cols), (len p1, len i1, len p2, len i2, len val))")
+                if _resident(p1, i1, p2, i2, val, B, C):
+                    from . import device as D
+                    i1, p2, i2 = (self._dv(t, idx_dtype) for t in (i1, p2, i2))
+                    val, B, C = (self._dv(t, np.float64) for t in (val, B, C))
+                    if (i1.extent(0), p2.extent(0), i2.extent(0), val.extent(0)) != tuple(flat[3:]) or flat[4] != flat[3] + 1:
+                        raise LapisError(1, "storage specifier does not match the DCSR arrays")
+                    D.spmm_dcsr(i1.device_view(), p2.device_view(), i2.device_view(), val.device_view(),
+                                B.device_view(), C.device_view(), int(flat[1]))
+                    C.modifyDevice()
+                    return C
+                arrs = [np.require(t, dtype=idx_dtype, requirements=["C"]) for t in (p1, i1, p2, i2)]
+                val = np.require(val, dtype=np.float64, requirements=["C"])
+                B = np.require(B, dtype=np.float64, requirements=["C"])
+                C = np.require(C, dtype=np.float64, requirements=["C"])
+                ret0 = _ret_slot(2)
+                fn(ret0, *[_desc(t) for t in arrs], _desc(val), flat.ctypes.data_as(ctypes.c_void_p), _desc(B), _desc(C))
+                check_last()
+                return C
+
+            return spmm_dcsr
         if kind == "mht":
             fn = getattr(lib, f"py_mht_f64_{sfx}")
 
@@ -420,8 +534,8 @@ class KokkosBackend:
             raise Exception("module has no public function")
         bindings = {}
         for fn in public:
-            kind, sfx, dt = _classify(fn, by_name)
-            if sfx and not self.decompose_tensors:
+            kind, sfx, dt = _classify(fn, by_name, moduleText)
+            if sfx and kind != "print" and not self.decompose_tensors:
                 raise Exception("sparse tensor arguments need decompose_tensors=True (pos, crd, val, specifier "
                                 "arguments); the opaque sparse-runtime handle form is not supported")
             bindings[fn["name"]] = (kind, sfx, dt)

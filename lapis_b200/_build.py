@@ -14,7 +14,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "liblapis_b200.so")
-SOURCES = ["abi.cu", "spmv.cu", "pcg.cu", "gemm.cu", "gemm_tcgen05.cu", "mmio.cu"]
+SOURCES = ["abi.cu", "spmv.cu", "pcg.cu", "gemm.cu", "gemm_tcgen05.cu", "mmio.cu", "formats.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "--fmad=false",

@@ -340,6 +340,118 @@ static int normalize_mom2_host(lapis_memref1 **ret0, lapis_memref1 *mom1, lapis_
   return LAPIS_OK;
 }
 
+// examples/bspmm.py:26-52, call at :103
+template <typename I>
+static int bspmm_host(lapis_memref3 **ret0, lapis_memref1 *pos, lapis_memref1 *crd, lapis_memref1 *val,
+                      const lapis_csrv_spec *spec, lapis_memref3 *B) {
+  clear_error();
+  LAPIS_TRY(require_init());
+  LAPIS_TRY((check_contig<lapis_memref1, 1>(pos, "pos")));
+  LAPIS_TRY((check_contig<lapis_memref1, 1>(crd, "crd")));
+  LAPIS_TRY((check_contig<lapis_memref1, 1>(val, "val")));
+  LAPIS_TRY((check_contig<lapis_memref3, 3>(B, "B")));
+  if (spec == nullptr) return fail(LAPIS_EBADARG, "null storage specifier");
+  if (ret0 == nullptr || *ret0 == nullptr) return fail(LAPIS_EBADARG, "bspmm: null result slot");
+  const int64_t n1 = spec->dims[0], n2 = spec->dims[1], nh = spec->dims[2];
+  const int64_t npos = spec->mem_sizes[0], nnz = spec->mem_sizes[1], nval = spec->mem_sizes[2];
+  if (n1 < 0 || n2 < 0 || nh < 0) return fail(LAPIS_EBADSHAPE, "negative tensor dimension");
+  if (npos != n1 + 1 || pos->sizes[0] < npos) return fail(LAPIS_EBADSHAPE, "pos must have rows+1 entries");
+  if (nval != nnz * nh || crd->sizes[0] < nnz || val->sizes[0] < nval)
+    return fail(LAPIS_EBADSHAPE, "crd/val shorter than the specifier says");
+  if (B->sizes[0] != n2 || B->sizes[2] != nh) return fail(LAPIS_EBADSHAPE, "bspmm: B must be [n2, dh, nh]");
+  const int64_t dh = B->sizes[1];
+  const I *hpos = elem_ptr<I>(pos);
+  LAPIS_TRY(check_pos_host<I>(hpos, n1, nnz));
+  const I *hcrd = elem_ptr<I>(crd);
+  for (int64_t j = 0; j < nnz; ++j)
+    if (hcrd[j] < 0 || (int64_t)hcrd[j] >= n2) return fail(LAPIS_EBADSHAPE, "bspmm: column index out of range at entry %lld", (long long)j);
+  cudaStream_t st = nullptr;
+  DevBuf dpos, dcrd, dval, dB, dC;
+  const size_t bB = (size_t)n2 * dh * nh * 4, bC = (size_t)n1 * dh * nh * 4;
+  LAPIS_TRY(dpos.alloc((size_t)npos * sizeof(I)));
+  LAPIS_TRY(dcrd.alloc((size_t)nnz * sizeof(I)));
+  LAPIS_TRY(dval.alloc((size_t)nval * 4));
+  LAPIS_TRY(dB.alloc(bB));
+  LAPIS_TRY(dC.alloc(bC));
+  LAPIS_CUDA_TRY(cudaMemcpyAsync(dpos.p, hpos, (size_t)npos * sizeof(I), cudaMemcpyHostToDevice, st));
+  LAPIS_CUDA_TRY(cudaMemcpyAsync(dcrd.p, hcrd, (size_t)nnz * sizeof(I), cudaMemcpyHostToDevice, st));
+  LAPIS_CUDA_TRY(cudaMemcpyAsync(dval.p, elem_ptr<float>(val), (size_t)nval * 4, cudaMemcpyHostToDevice, st));
+  LAPIS_CUDA_TRY(cudaMemcpyAsync(dB.p, elem_ptr<float>(B), bB, cudaMemcpyHostToDevice, st));
+  LAPIS_TRY(lapis_b200_bspmm_csrv_f32((int)sizeof(I), n1, n2, nh, dh, dpos.p, dcrd.p, static_cast<const float *>(dval.p),
+                                      static_cast<const float *>(dB.p), static_cast<float *>(dC.p), 0, st));
+  float *hc = static_cast<float *>(std::malloc(bC > 0 ? bC : 8));
+  if (hc == nullptr) return fail(LAPIS_ECUDA, "bspmm: host allocation failed");
+  g_alive_host.push_back(hc);
+  if (bC > 0) LAPIS_CUDA_TRY(cudaMemcpyAsync(hc, dC.p, bC, cudaMemcpyDeviceToHost, st));
+  LAPIS_CUDA_TRY(cudaStreamSynchronize(st));
+  lapis_memref3 out;
+  out.basePtr = hc;
+  out.data = hc;
+  out.offset = 0;
+  out.sizes[0] = n1;
+  out.sizes[1] = dh;
+  out.sizes[2] = nh;
+  out.strides[0] = dh * nh;
+  out.strides[1] = nh;
+  out.strides[2] = 1;
+  **ret0 = out;
+  return LAPIS_OK;
+}
+
+// examples/spmm_dcsr_opdsl.py:59-101, call at :160 (decomposed arguments)
+template <typename I>
+static int spmm_dcsr_host(lapis_memref2 **ret0, lapis_memref1 *p1, lapis_memref1 *i1, lapis_memref1 *p2, lapis_memref1 *i2,
+                          lapis_memref1 *val, const lapis_dcsr_spec *spec, lapis_memref2 *B, lapis_memref2 *C) {
+  clear_error();
+  LAPIS_TRY(require_init());
+  LAPIS_TRY((check_contig<lapis_memref1, 1>(p1, "p1")));
+  LAPIS_TRY((check_contig<lapis_memref1, 1>(i1, "i1")));
+  LAPIS_TRY((check_contig<lapis_memref1, 1>(p2, "p2")));
+  LAPIS_TRY((check_contig<lapis_memref1, 1>(i2, "i2")));
+  LAPIS_TRY((check_contig<lapis_memref1, 1>(val, "val")));
+  LAPIS_TRY((check_contig<lapis_memref2, 2>(B, "B")));
+  LAPIS_TRY((check_contig<lapis_memref2, 2>(C, "C")));
+  if (spec == nullptr) return fail(LAPIS_EBADARG, "null storage specifier");
+  const int64_t nrows = spec->dims[0], ncols = spec->dims[1];
+  const int64_t nstored = spec->mem_sizes[1], nnz = spec->mem_sizes[4];
+  if (nrows < 0 || ncols < 0) return fail(LAPIS_EBADSHAPE, "negative matrix dimension");
+  if (spec->mem_sizes[0] != 2 || p1->sizes[0] < 2 || spec->mem_sizes[2] != nstored + 1 || p2->sizes[0] < nstored + 1 ||
+      i1->sizes[0] < nstored || spec->mem_sizes[3] != nnz || i2->sizes[0] < nnz || val->sizes[0] < nnz)
+    return fail(LAPIS_EBADSHAPE, "spmm_dcsr: buffers do not match the specifier");
+  const int64_t k = B->sizes[1];
+  if (B->sizes[0] != ncols || C->sizes[0] != nrows || C->sizes[1] != k) return fail(LAPIS_EBADSHAPE, "spmm_dcsr: B/C shape mismatch");
+  const I *hp1 = elem_ptr<I>(p1), *hi1 = elem_ptr<I>(i1), *hp2 = elem_ptr<I>(p2), *hi2 = elem_ptr<I>(i2);
+  if (hp1[0] != 0 || (int64_t)hp1[1] != nstored) return fail(LAPIS_EBADSHAPE, "spmm_dcsr: p1 must be {0, stored rows}");
+  LAPIS_TRY(check_pos_host<I>(hp2, nstored, nnz));
+  for (int64_t r = 0; r < nstored; ++r)  // ascending row numbers: equal ones are adjacent and one warp takes the run
+    if (hi1[r] < 0 || (int64_t)hi1[r] >= nrows || (r > 0 && hi1[r] < hi1[r - 1]))
+      return fail(LAPIS_EBADSHAPE, "spmm_dcsr: stored row numbers must ascend within [0, rows)");
+  for (int64_t j = 0; j < nnz; ++j)
+    if (hi2[j] < 0 || (int64_t)hi2[j] >= ncols) return fail(LAPIS_EBADSHAPE, "spmm_dcsr: column index out of range at entry %lld", (long long)j);
+  cudaStream_t st = nullptr;
+  DevBuf di1, dp2, di2, dval, dB, dC;
+  const size_t bB = (size_t)ncols * k * 8, bC = (size_t)nrows * k * 8;
+  LAPIS_TRY(di1.alloc((size_t)nstored * sizeof(I)));
+  LAPIS_TRY(dp2.alloc((size_t)(nstored + 1) * sizeof(I)));
+  LAPIS_TRY(di2.alloc((size_t)nnz * sizeof(I)));
+  LAPIS_TRY(dval.alloc((size_t)nnz * 8));
+  LAPIS_TRY(dB.alloc(bB));
+  LAPIS_TRY(dC.alloc(bC));
+  LAPIS_CUDA_TRY(cudaMemcpyAsync(di1.p, hi1, (size_t)nstored * sizeof(I), cudaMemcpyHostToDevice, st));
+  LAPIS_CUDA_TRY(cudaMemcpyAsync(dp2.p, hp2, (size_t)(nstored + 1) * sizeof(I), cudaMemcpyHostToDevice, st));
+  LAPIS_CUDA_TRY(cudaMemcpyAsync(di2.p, hi2, (size_t)nnz * sizeof(I), cudaMemcpyHostToDevice, st));
+  LAPIS_CUDA_TRY(cudaMemcpyAsync(dval.p, elem_ptr<double>(val), (size_t)nnz * 8, cudaMemcpyHostToDevice, st));
+  LAPIS_CUDA_TRY(cudaMemcpyAsync(dB.p, elem_ptr<double>(B), bB, cudaMemcpyHostToDevice, st));
+  LAPIS_CUDA_TRY(cudaMemcpyAsync(dC.p, elem_ptr<double>(C), bC, cudaMemcpyHostToDevice, st));
+  LAPIS_TRY(lapis_b200_spmm_dcsr_f64((int)sizeof(I), nrows, ncols, nstored, k, di1.p, dp2.p, di2.p,
+                                     static_cast<const double *>(dval.p), static_cast<const double *>(dB.p),
+                                     static_cast<double *>(dC.p), st));
+  LAPIS_CUDA_TRY(cudaMemcpyAsync(elem_ptr<double>(C), dC.p, bC, cudaMemcpyDeviceToHost, st));
+  LAPIS_CUDA_TRY(cudaStreamSynchronize(st));
+  if (ret0 != nullptr && *ret0 != nullptr) **ret0 = *C;
+  return LAPIS_OK;
+}
+
 }  // namespace lapis_b200
 
 using namespace lapis_b200;
@@ -455,6 +567,25 @@ extern "C" void py_mht_f64_i64(lapis_memref1 **ret0, lapis_memref1 **ret1, lapis
 }
 extern "C" void py_normalize_mom2_f64(lapis_memref1 **ret0, lapis_memref1 *mom1, lapis_memref1 *mom2) {
   normalize_mom2_host(ret0, mom1, mom2);
+}
+
+extern "C" void py_bspmm_f32_i32(lapis_memref3 **ret0, lapis_memref1 *pos, lapis_memref1 *crd, lapis_memref1 *val,
+                                 const lapis_csrv_spec *spec, lapis_memref3 *B) {
+  bspmm_host<int32_t>(ret0, pos, crd, val, spec, B);
+}
+extern "C" void py_bspmm_f32_i64(lapis_memref3 **ret0, lapis_memref1 *pos, lapis_memref1 *crd, lapis_memref1 *val,
+                                 const lapis_csrv_spec *spec, lapis_memref3 *B) {
+  bspmm_host<int64_t>(ret0, pos, crd, val, spec, B);
+}
+extern "C" void py_spmm_dcsr_f64_i32(lapis_memref2 **ret0, lapis_memref1 *p1, lapis_memref1 *i1, lapis_memref1 *p2,
+                                     lapis_memref1 *i2, lapis_memref1 *val, const lapis_dcsr_spec *spec,
+                                     lapis_memref2 *B, lapis_memref2 *C) {
+  spmm_dcsr_host<int32_t>(ret0, p1, i1, p2, i2, val, spec, B, C);
+}
+extern "C" void py_spmm_dcsr_f64_i64(lapis_memref2 **ret0, lapis_memref1 *p1, lapis_memref1 *i1, lapis_memref1 *p2,
+                                     lapis_memref1 *i2, lapis_memref1 *val, const lapis_dcsr_spec *spec,
+                                     lapis_memref2 *B, lapis_memref2 *C) {
+  spmm_dcsr_host<int64_t>(ret0, p1, i1, p2, i2, val, spec, B, C);
 }
 
 // ---- host-side partition rule ------------------------------------------------

@@ -125,6 +125,45 @@ class CsrMatrix:
         return m1, m2
 
 
+def bspmm_csrv(pos: torch.Tensor, crd: torch.Tensor, val: torch.Tensor, B: torch.Tensor, n2: int, C=None) -> torch.Tensor:
+    """Batched SpMM over a CSRV tensor (examples/bspmm.py:14-52 in the LAPIS project), fp32:
+    C[n1, dh, nh] (+)= sum_j val[j, nh] * B[crd[j], dh, nh] over the stored entries j of row n1.  ``val`` holds
+    nh values per stored entry.  With ``C`` given the product is added to it in place; otherwise a new
+    zero-initialised result is returned."""
+    if pos.dtype != crd.dtype or pos.dtype not in (torch.int32, torch.int64):
+        raise TypeError("pos/crd must both be int32 or both int64")
+    for t in (val, B):
+        if not (t.is_cuda and t.dtype == torch.float32 and t.is_contiguous()):
+            raise TypeError("val/B must be contiguous float32 CUDA tensors")
+    if B.dim() != 3 or B.shape[0] != n2:
+        raise ValueError("bspmm: B must be [n2, dh, nh]")
+    n1, dh, nh = pos.numel() - 1, int(B.shape[1]), int(B.shape[2])
+    if val.numel() != crd.numel() * nh:
+        raise ValueError("bspmm: val must hold nh values per stored entry")
+    accumulate = C is not None
+    if C is None:
+        C = torch.empty((n1, dh, nh), dtype=torch.float32, device=B.device)
+    elif tuple(C.shape) != (n1, dh, nh) or C.dtype != torch.float32 or not C.is_contiguous():
+        raise ValueError("bspmm: C must be a contiguous float32 [n1, dh, nh] tensor")
+    check(load().lapis_b200_bspmm_csrv_f32(c_int(pos.element_size()), n1, n2, nh, dh, _ptr(pos), _ptr(crd), _ptr(val),
+                                           _ptr(B), _ptr(C), c_int(1 if accumulate else 0), _stream()))
+    return C
+
+
+def spmm_dcsr(i1: torch.Tensor, p2: torch.Tensor, i2: torch.Tensor, val: torch.Tensor, B: torch.Tensor, C: torch.Tensor,
+              ncols: int) -> torch.Tensor:
+    """C[i1[r], :] += sum_j val[j] * B[i2[j], :] for the stored rows r of a DCSR matrix
+    (examples/spmm_dcsr_opdsl.py:59-101 in the LAPIS project), in place; ``i1`` must ascend (a row number may repeat)."""
+    if not (i1.dtype == p2.dtype == i2.dtype) or p2.dtype not in (torch.int32, torch.int64):
+        raise TypeError("i1/p2/i2 must all be int32 or all int64")
+    _f64(val, "val"), _f64(B, "B"), _f64(C, "C")
+    if B.dim() != 2 or C.dim() != 2 or B.shape[0] != ncols or B.shape[1] != C.shape[1] or p2.numel() != i1.numel() + 1:
+        raise ValueError("spmm_dcsr: shape mismatch")
+    check(load().lapis_b200_spmm_dcsr_f64(c_int(p2.element_size()), int(C.shape[0]), ncols, i1.numel(), int(B.shape[1]),
+                                          _ptr(i1), _ptr(p2), _ptr(i2), _ptr(val), _ptr(B), _ptr(C), _stream()))
+    return C
+
+
 def normalize_mom2(mom1: torch.Tensor, mom2: torch.Tensor) -> torch.Tensor:
     """sqrt(mom2 - mom1^2) elementwise (examples/hitting_times.py:196-218 in the LAPIS project)."""
     _f64(mom1, "mom1"), _f64(mom2, "mom2")

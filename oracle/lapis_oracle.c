@@ -395,6 +395,51 @@ ORACLE_API void oracle_mht_f64_i32(int64_t n, const int32_t *pos, const int32_t 
 }
 
 /* ------------------------------------------------------------------------
+ * Batched SpMM over a CSRV tensor, examples/bspmm.py:14-52: loop nest rows -> stored
+ * entries -> dh -> nh, out[n1,dh,nh] = a*b + out[n1,dh,nh] in place (:47-49), fp32.
+ * val holds nh values per stored entry; B is [n2, dh, nh]; C is [n1, dh, nh].
+ * ---------------------------------------------------------------------- */
+#define DEFINE_BSPMM(SUFFIX, IDX)                                                          \
+  ORACLE_API void oracle_bspmm_f32_##SUFFIX(int64_t n1, int64_t nh, int64_t dh,             \
+                                            const IDX *pos, const IDX *crd, const float *val, \
+                                            const float *B, float *C) {                     \
+    for (int64_t i = 0; i < n1; i++)                                                        \
+      for (int64_t j = (int64_t)pos[i]; j < (int64_t)pos[i + 1]; j++) {                     \
+        const float *brow = B + (int64_t)crd[j] * dh * nh;                                  \
+        for (int64_t d = 0; d < dh; d++)                                                    \
+          for (int64_t h = 0; h < nh; h++) {                                                \
+            float prod = val[j * nh + h] * brow[d * nh + h];                                \
+            C[(i * dh + d) * nh + h] = prod + C[(i * dh + d) * nh + h];                     \
+          }                                                                                 \
+      }                                                                                     \
+  }
+DEFINE_BSPMM(i32, int32_t)
+DEFINE_BSPMM(i64, int64_t)
+
+/* ------------------------------------------------------------------------
+ * SpMM with A in DCSR, examples/spmm_dcsr_opdsl.py:59-101: stored rows -> stored
+ * entries -> k, C[row,k] = C[row,k] + a*b in place, fp64.
+ * ---------------------------------------------------------------------- */
+#define DEFINE_SPMM_DCSR(SUFFIX, IDX)                                                      \
+  ORACLE_API void oracle_spmm_dcsr_f64_##SUFFIX(int64_t nstored, int64_t k, const IDX *i1,  \
+                                                const IDX *p2, const IDX *i2,               \
+                                                const double *val, const double *B,         \
+                                                double *C) {                                \
+    for (int64_t r = 0; r < nstored; r++) {                                                 \
+      double *crow = C + (int64_t)i1[r] * k;                                                \
+      for (int64_t j = (int64_t)p2[r]; j < (int64_t)p2[r + 1]; j++) {                       \
+        const double *brow = B + (int64_t)i2[j] * k;                                        \
+        for (int64_t c = 0; c < k; c++) {                                                   \
+          double prod = val[j] * brow[c];                                                   \
+          crow[c] = crow[c] + prod;                                                         \
+        }                                                                                   \
+      }                                                                                     \
+    }                                                                                       \
+  }
+DEFINE_SPMM_DCSR(i32, int32_t)
+DEFINE_SPMM_DCSR(i64, int64_t)
+
+/* ------------------------------------------------------------------------
  * Integer host logic that must be bit-exact.
  * nnz-balanced row partition: boundary g is the first row whose start offset
  * is >= g*nnz/G (lower bound on pos), g = 0..G, with boundary G = nrows.

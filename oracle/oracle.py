@@ -190,6 +190,31 @@ def mht(pos, crd, val, mask, d, alpha, tol, maxiter):
     return mom1, mom2
 
 
+def bspmm(pos, crd, val, B, C_in=None):
+    """Batched SpMM over a CSRV tensor (examples/bspmm.py:14-52), fp32: val [nnz*nh], B [n2, dh, nh]."""
+    pos = np.ascontiguousarray(pos)
+    crd = np.ascontiguousarray(crd, dtype=pos.dtype)
+    s = "i32" if pos.dtype == np.int32 else "i64"
+    val = np.ascontiguousarray(val, dtype=np.float32)
+    B = np.ascontiguousarray(B, dtype=np.float32)
+    n1, (n2, dh, nh) = len(pos) - 1, B.shape
+    C = np.zeros((n1, dh, nh), dtype=np.float32) if C_in is None else np.array(C_in, dtype=np.float32, copy=True, order="C")
+    getattr(lib(), f"oracle_bspmm_f32_{s}")(c_i64(n1), c_i64(nh), c_i64(dh), _p(pos), _p(crd), _p(val), _p(B), _p(C))
+    return C
+
+
+def spmm_dcsr(i1, p2, i2, val, B, C_in):
+    """C_in + A B with A in DCSR (examples/spmm_dcsr_opdsl.py:59-101), fp64."""
+    p2 = np.ascontiguousarray(p2)
+    i1 = np.ascontiguousarray(i1, dtype=p2.dtype)
+    i2 = np.ascontiguousarray(i2, dtype=p2.dtype)
+    s = "i32" if p2.dtype == np.int32 else "i64"
+    val, B = _f64(val), _f64(B)
+    C = np.array(C_in, dtype=np.float64, copy=True, order="C")
+    getattr(lib(), f"oracle_spmm_dcsr_f64_{s}")(c_i64(len(i1)), c_i64(B.shape[1]), _p(i1), _p(p2), _p(i2), _p(val), _p(B), _p(C))
+    return C
+
+
 def partition_rows(pos, G: int):
     pos = np.ascontiguousarray(pos)
     s = "i32" if pos.dtype == np.int32 else "i64"

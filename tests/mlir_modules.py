@@ -279,6 +279,58 @@ module {{
 }}"""
 
 
+CSRV32 = ("#CSRV = #sparse_tensor.encoding<{ map = (i, j, h) -> (i : dense, j : compressed, h : dense), "
+          "posWidth = 32, crdWidth = 32 }>")
+CSRV64 = "#CSRV = #sparse_tensor.encoding<{ map = (i, j, h) -> (i : dense, j : compressed, h : dense) }>"
+
+
+def bspmm(enc=CSRV32):
+    """Batched SpMM over a CSRV tensor: out(n1, dh, nh) = sum over n2 of A(n1, n2, nh) * B(n2, dh, nh), the
+    operation of examples/bspmm.py in the LAPIS project, written out for these tests."""
+    return enc + """
+#trait = {
+  indexing_maps = [affine_map<(n1, n2, dh, nh) -> (n1, n2, nh)>,
+                   affine_map<(n1, n2, dh, nh) -> (n2, dh, nh)>,
+                   affine_map<(n1, n2, dh, nh) -> (n1, dh, nh)>],
+  iterator_types = ["parallel", "reduction", "parallel", "parallel"]
+}
+module {
+  func.func @bspmm(%A: tensor<?x?x?xf32, #CSRV>, %B: tensor<?x?x?xf32>) -> tensor<?x?x?xf32> {
+    %c0 = arith.constant 0 : index
+    %c1 = arith.constant 1 : index
+    %c2 = arith.constant 2 : index
+    %z = arith.constant 0.0 : f32
+    %n1 = tensor.dim %A, %c0 : tensor<?x?x?xf32, #CSRV>
+    %nh = tensor.dim %A, %c2 : tensor<?x?x?xf32, #CSRV>
+    %dh = tensor.dim %B, %c1 : tensor<?x?x?xf32>
+    %e = tensor.empty(%n1, %dh, %nh) : tensor<?x?x?xf32>
+    %init = linalg.fill ins(%z : f32) outs(%e : tensor<?x?x?xf32>) -> tensor<?x?x?xf32>
+    %r = linalg.generic #trait ins(%A, %B : tensor<?x?x?xf32, #CSRV>, tensor<?x?x?xf32>) outs(%init : tensor<?x?x?xf32>) {
+    ^bb0(%a: f32, %b: f32, %o: f32):
+      %p = arith.mulf %a, %b : f32
+      %s = arith.addf %p, %o : f32
+      linalg.yield %s : f32
+    } -> tensor<?x?x?xf32>
+    return %r : tensor<?x?x?xf32>
+  }
+}"""
+
+
+DCSR64 = "#DCSR = #sparse_tensor.encoding<{ map = (i, j) -> (i : compressed, j : compressed) }>"
+DCSR32 = "#DCSR = #sparse_tensor.encoding<{ map = (i, j) -> (i : compressed, j : compressed), posWidth = 32, crdWidth = 32 }>"
+
+
+def spmm_dcsr(enc=DCSR64):
+    """C += A B with A compressed in both levels (the operation of examples/spmm_dcsr_opdsl.py)."""
+    return enc + """
+module {
+  func.func @spMxM(%A: tensor<?x?xf64, #DCSR>, %B: tensor<?x?xf64>, %C: tensor<?x?xf64>) -> tensor<?x?xf64> {
+    %r = linalg.matmul ins(%A, %B : tensor<?x?xf64, #DCSR>, tensor<?x?xf64>) outs(%C : tensor<?x?xf64>) -> tensor<?x?xf64>
+    return %r : tensor<?x?xf64>
+  }
+}"""
+
+
 UNSUPPORTED = """
 module {
   func.func @relu(%x: tensor<?xf32>) -> tensor<?xf32> {

@@ -109,6 +109,69 @@ def test_backend_classifies_the_hitting_times_module():
         KB._classify(by["mht"], by)
 
 
+def test_backend_classifies_neighbouring_formats():
+    for text, want in ((mm.bspmm(mm.CSRV32), ("bspmm", "i32")), (mm.bspmm(mm.CSRV64), ("bspmm", "i64")),
+                       (mm.spmm_dcsr(mm.DCSR64), ("spmm_dcsr", "i64")), (mm.spmm_dcsr(mm.DCSR32), ("spmm_dcsr", "i32"))):
+        funcs = KB._parse_functions(text, KB._parse_encodings(text))
+        by = {f["name"]: f for f in funcs}
+        public = [f for f in funcs if not f["private"]]
+        assert len(public) == 1 and KB._classify(public[0], by, text)[:2] == want
+    # a CSRV contraction over another index pair is not the batched SpMM
+    text = mm.bspmm().replace("-> (n2, dh, nh)", "-> (n2, nh, dh)")
+    funcs = KB._parse_functions(text, KB._parse_encodings(text))
+    with pytest.raises(Exception, match="not on the accelerated path"):
+        KB._classify(funcs[0], {f["name"]: f for f in funcs}, text)
+    # a print-only function is bound to host code
+    text = mm.CSRV32 + """
+module {
+  func.func @show(%A: tensor<?x?x?xf32, #CSRV>) {
+    sparse_tensor.print %A : tensor<?x?x?xf32, #CSRV>
+    return
+  }
+}"""
+    funcs = KB._parse_functions(text, KB._parse_encodings(text))
+    assert KB._classify(funcs[0], {}, text)[:2] == ("print", "densexcompressedxdense")
+
+
+def test_oracle_bspmm_and_dcsr_against_scipy():
+    """The two restatements against scipy's own products (the check examples/bspmm.py:80-90 and
+    examples/spmm_dcsr_opdsl.py:163-172 make), and each other's index widths."""
+    import scipy.sparse as sp
+    rng = np.random.default_rng(3)
+    m, n, b, k = 50, 60, 8, 3
+    A = sp.random(m, n, density=0.1, random_state=7, format="csr")
+    A.sort_indices()
+    nnz = A.nnz
+    vals = rng.uniform(1.0, 2.0, nnz * b).astype(np.float32)
+    B = rng.uniform(1.0, 2.0, (n, k, b)).astype(np.float32)
+    C = oracle.bspmm(A.indptr.astype(np.int32), A.indices.astype(np.int32), vals, B)
+    gold = np.zeros((m, k, b), dtype=np.float32)
+    for i in range(b):
+        gold[:, :, i] = sp.csr_matrix((vals[i::b], A.indices, A.indptr), (m, n)) @ B[:, :, i]
+    assert np.allclose(C, gold)
+    assert np.array_equal(C, oracle.bspmm(A.indptr.astype(np.int64), A.indices.astype(np.int64), vals, B))
+    assert np.array_equal(oracle.bspmm(A.indptr.astype(np.int32), A.indices.astype(np.int32), vals, B, C_in=C),
+                          oracle.bspmm(A.indptr.astype(np.int64), A.indices.astype(np.int64), vals, B, C_in=C))
+    # DCSR: the example's 3x4 matrix, then a generated one with empty rows
+    p2, i1, i2 = np.array([0, 1, 3, 3]), np.array([0, 1, 1]), np.array([0, 1, 2])
+    vals = np.array([1.1, 2.2, 3.3])
+    Bd = np.array([[1.0, 2.0], [4.0, 3.0], [5.0, 6.0], [8.0, 7.0]])
+    dense = np.array([[1.1, 0, 0, 0], [0, 2.2, 3.3, 0], [0, 0, 0, 0]])
+    # the example's buffers list row 1 twice in i1, the second time with an empty segment
+    C = oracle.spmm_dcsr(i1, p2, i2, vals, Bd, np.zeros((3, 2)))
+    assert np.allclose(C, dense @ Bd)
+    A = sp.random(40, 30, density=0.05, random_state=11, format="csr")
+    A.sort_indices()
+    stored = np.flatnonzero(np.diff(A.indptr))
+    p2 = np.concatenate([[0], np.cumsum(np.diff(A.indptr)[stored])])
+    Bd = rng.standard_normal((30, 17))
+    C0 = rng.standard_normal((40, 17))
+    C = oracle.spmm_dcsr(stored, p2, A.indices, A.data, Bd, C0)
+    assert np.allclose(C, C0 + A @ Bd)
+    untouched = np.setdiff1d(np.arange(40), stored)
+    assert np.array_equal(C[untouched], C0[untouched])
+
+
 def test_backend_rejects_off_path_modules():
     with pytest.raises(Exception, match="not on the accelerated path"):
         KB.KokkosBackend().compile(mm.UNSUPPORTED)
