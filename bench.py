@@ -487,6 +487,19 @@ def run_ours(args, d, rank, world, local_rank):
     ms_step = ms / args.steps
     value = d["work"] / (ms_step * 1e-3) * d["unit_scale"]
     bound = "tensor" if name == "gemm" else "hbm"
+    if world > 1 and name == "spmv" and len(d["x"]) % world == 0:
+        # Reported beside the headline, not in it: the same step when x arrives split over the ranks and has to
+        # be gathered first (for these random-column matrices every rank needs all of x).
+        n_x = len(d["x"])
+        x_part = xd[rank * (n_x // world):(rank + 1) * (n_x // world)].clone()
+
+        def step_gather():
+            dist.all_gather_into_tensor(xd, x_part)
+            A.spmv(xd, yd, accumulate=False)
+
+        ms_g, _ = timed(step_gather, args.steps, 3)
+        extra_cfg["with_x_allgather"] = {"ms_per_step": ms_g / args.steps, "unit": d["unit"],
+                                         "value": d["work"] / (ms_g / args.steps * 1e-3) * d["unit_scale"]}
     emit(args, d, value, ms_step, clocks, e2e, launches_per_step * args.steps * world, kernel_name, algo_bytes_rank,
          ms_step, peaks, peak_kind, world, rank, extra_cfg, bound=bound)
 
