@@ -11,7 +11,7 @@
 //   Struct0                                     the flattened CSR storage specifier
 //                                               (mlir/lib/Target/KokkosCpp/TranslateToKokkosCpp.cpp:4495-4546)
 //   lapis_initialize / lapis_finalize           from lapis_b200.h
-//   spmv, spmm, forward, pcg                    the emitted functions of the accelerated path
+//   spmv, spmm, forward, pcg, mht, normalize_mom2   the emitted functions of the accelerated path
 //
 // What is not here: Kokkos itself (views are plain pointer + extents, no subviews, LayoutRight only),
 // Kokkos::Timer / fill_random used by the drivers' set-up code, and any function outside the
@@ -277,6 +277,37 @@ inline std::tuple<LAPIS::DualView<double *, Kokkos::LayoutRight>, size_t, double
                "pcg");
   x.modifyDevice();
   return std::make_tuple(x, (size_t)iters, relres);
+}
+
+// Hitting-time moments (examples/hitting_times.py:151-194): returns (first moment, second moment).
+template <typename I>
+inline std::tuple<LAPIS::DualView<double *, Kokkos::LayoutRight>, LAPIS::DualView<double *, Kokkos::LayoutRight>> mht(
+    LAPIS::DualView<I *, Kokkos::LayoutRight> pos, LAPIS::DualView<I *, Kokkos::LayoutRight> crd,
+    LAPIS::DualView<double *, Kokkos::LayoutRight> val, Struct0 shape, LAPIS::DualView<double *, Kokkos::LayoutRight> mask,
+    LAPIS::DualView<double *, Kokkos::LayoutRight> d, double alpha, double tol, size_t maxiter) {
+  lapis_b200_csr_t h = lapis_b200_detail::plan_for<I>(pos, crd, val, shape);
+  mask.syncDevice();
+  d.syncDevice();
+  LAPIS::DualView<double *, Kokkos::LayoutRight> mom1("mom1", d.extent(0)), mom2("mom2", d.extent(0));
+  LAPIS::check(lapis_b200_mht_f64(h, mask.device_view().data(), d.device_view().data(), alpha, tol, (uint64_t)maxiter,
+                                  mom1.device_view().data(), mom2.device_view().data(), nullptr, nullptr, nullptr),
+               "mht");
+  mom1.modifyDevice();
+  mom2.modifyDevice();
+  return std::make_tuple(mom1, mom2);
+}
+
+// sqrt(mom2 - mom1^2) (examples/hitting_times.py:196-218).
+inline LAPIS::DualView<double *, Kokkos::LayoutRight> normalize_mom2(LAPIS::DualView<double *, Kokkos::LayoutRight> mom1,
+                                                                     LAPIS::DualView<double *, Kokkos::LayoutRight> mom2) {
+  mom1.syncDevice();
+  mom2.syncDevice();
+  LAPIS::DualView<double *, Kokkos::LayoutRight> out("nm2", mom1.extent(0));
+  LAPIS::check(lapis_b200_normalize_mom2_f64((int64_t)mom1.extent(0), mom1.device_view().data(), mom2.device_view().data(),
+                                             out.device_view().data(), nullptr),
+               "normalize_mom2");
+  out.modifyDevice();
+  return out;
 }
 
 #endif  // LAPIS_B200_HPP

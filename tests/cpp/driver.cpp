@@ -91,6 +91,39 @@ int main() {
     for (int i = 0; i < n; i++) if (std::fabs(x.host_view()(i) - 1.0) > 1e-9) rc |= fail("pcg solution");
     std::printf("pcg: %zu iterations, relres %.3e\n", iters, relres);
   }
+  {
+    // Hitting-time moments on a 6-cycle with unit weights, node 0 absorbing: d = degree, mask[0] = 0.
+    // The first moment solves mask (D - alpha A) mask m = mask d; checked by its residual on the host.
+    const int n = 6;
+    const double alpha = 0.9;
+    IntDV pos("pos", n + 1), crd("crd", 2 * n);
+    VecDV val("val", 2 * n), mask("mask", n), d("d", n);
+    for (int i = 0; i < n; i++) {
+      pos.host_view()(i) = 2 * i;
+      const int lo = (i + n - 1) % n, hi = (i + 1) % n;
+      crd.host_view()(2 * i) = lo < hi ? lo : hi;
+      crd.host_view()(2 * i + 1) = lo < hi ? hi : lo;
+      val.host_view()(2 * i) = val.host_view()(2 * i + 1) = 1.0;
+      mask.host_view()(i) = i == 0 ? 0.0 : 1.0;
+      d.host_view()(i) = 2.0;
+    }
+    pos.host_view()(n) = 2 * n;
+    pos.modifyHost(); crd.modifyHost(); val.modifyHost(); mask.modifyHost(); d.modifyHost();
+    Struct0 shape = {{n, n}, {n + 1, 2 * n, 2 * n}};
+    auto [m1, m2] = mht(pos, crd, val, shape, mask, d, alpha, 1e-13, (size_t)50);
+    auto sd = normalize_mom2(m1, m2);
+    m1.syncHost(); m2.syncHost(); sd.syncHost(); val.syncHost();
+    if (m1.host_view()(0) != 0.0) rc |= fail("mht: masked node must stay 0");
+    for (int i = 1; i < n; i++) {
+      const int lo = (i + n - 1) % n, hi = (i + 1) % n;
+      const double nb = (lo ? m1.host_view()(lo) : 0.0) + (hi ? m1.host_view()(hi) : 0.0);
+      if (std::fabs(2.0 * m1.host_view()(i) - alpha * nb - 2.0) > 1e-9) rc |= fail("mht: first moment residual");
+      const double var = m2.host_view()(i) - m1.host_view()(i) * m1.host_view()(i);
+      if (std::fabs(sd.host_view()(i) - std::sqrt(var)) > 1e-12) rc |= fail("normalize_mom2");
+    }
+    for (int j = 0; j < 2 * n; j++) if (val.host_view()(j) != 1.0) rc |= fail("mht changed the caller's values");
+    std::printf("mht: m1[1] = %.6f, m1[3] = %.6f\n", m1.host_view()(1), m1.host_view()(3));
+  }
   lapis_finalize();
   std::printf(rc == 0 ? "driver ok\n" : "driver failed\n");
   return rc;
