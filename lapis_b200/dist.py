@@ -209,15 +209,8 @@ class DistPcg:
         halo_index, err_index = ctypes.c_int64(), ctypes.c_int64()
         lib.lapis_b200_pcg_p2p_mailbox_layout(ctypes.byref(halo_index), ctypes.byref(err_index))
         HALO, self._err_index = int(halo_index.value), int(err_index.value)
-        pieces = []
-        for (consumer, s, e) in self.halo.send:
-            c0_peer = windows[consumer][0]
-            n_p_peer, p_doubles_peer = infos[consumer][2], infos[consumer][3]
-            dst_off, src_off, length = s - c0_peer, s - self.halo.c0, e - s
-            if not (0 <= dst_off and dst_off + length <= n_p_peer and 0 <= src_off and src_off + length <= self.n_p):
-                raise RuntimeError("halo piece outside a window")  # never dereference an address we cannot bound
-            pieces += [work_addr[consumer] + 8 * (p_doubles_peer + dst_off), src_off, length,
-                       mbox_addr[consumer] + 8 * (HALO + self.rank)]
+        pieces = part.push_pieces(self.halo.send, windows, self.rank, [i[2] for i in infos], [i[3] for i in infos],
+                                  work_addr, mbox_addr, HALO)
         self._npieces = len(pieces) // 4
         self._pieces = torch.tensor(pieces if pieces else [0], dtype=torch.int64, device=self.device)
         srcs = sorted({owner for owner, _, _ in self.halo.recv})

@@ -69,3 +69,27 @@ def exchange_plan(bounds: np.ndarray, windows):
     for lst in send:
         lst.sort()
     return recv, send
+
+
+def push_pieces(send, windows, rank: int, peer_window_len, peer_p_index, work_addr, mbox_addr, halo_index: int):
+    """Records for the peer-memory halo push of a row-partitioned PCG (consumed by
+    ``lapis_b200_pcg_p2p_halo_push``): for every (consumer, start, stop) of ``send`` the four integers
+    {destination address of the piece inside the consumer's p window, offset of the piece in this rank's
+    window, length, address of this rank's halo flag in the consumer's mailbox}.
+
+    ``windows[g] = (c0, c1)`` are the ranks' column windows, ``peer_window_len[g]`` / ``peer_p_index[g]`` the
+    length of rank g's window and the index (in doubles) of its first element inside g's workspace,
+    ``work_addr[g]`` / ``mbox_addr[g]`` the addresses at which this rank sees g's workspace and mailbox.
+    Every piece is checked against both windows: no address is formed that was not bounded first.
+    """
+    c0_me, c1_me = windows[rank]
+    out = []
+    for (consumer, s, e) in send:
+        c0_peer = windows[consumer][0]
+        dst_off, src_off, length = s - c0_peer, s - c0_me, e - s
+        if not (length > 0 and 0 <= dst_off and dst_off + length <= peer_window_len[consumer]
+                and 0 <= src_off and src_off + length <= c1_me - c0_me):
+            raise RuntimeError(f"halo piece [{s}, {e}) for rank {consumer} lies outside a window")
+        out += [work_addr[consumer] + 8 * (peer_p_index[consumer] + dst_off), src_off, length,
+                mbox_addr[consumer] + 8 * (halo_index + rank)]
+    return out

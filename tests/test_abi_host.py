@@ -10,6 +10,7 @@ import torch
 
 from lapis_b200 import KokkosBackend as KB
 from lapis_b200 import _lib, _memref, partition
+from lapis_b200 import workloads as w
 from oracle import oracle
 from tests import mlir_modules as mm
 
@@ -217,3 +218,41 @@ def test_exchange_plan_and_windows():
             assert (g, s, e) in send[o]
     lpos, lcrd, lval = partition.row_block(pos, crd, val, int(bounds[1]), int(bounds[2]))
     assert lpos[0] == 0 and lpos[-1] == len(lcrd) == len(lval)
+
+
+@pytest.mark.parametrize("world", [2, 3, 5])
+def test_push_pieces_cover_every_halo_exactly(world):
+    """The records of the peer-memory halo push, decoded back: every rank's non-owned window entries are
+    written exactly once, by their owner, from the owner's own entries; flags land in the right slots."""
+    from lapis_b200 import partition as part
+    from lapis_b200.dist import all_windows
+    d = w.pcg_laplacian(24)
+    pos, crd = d["pos"], d["crd"]
+    bounds = part.partition_rows(pos, world)
+    windows = all_windows(pos, crd, bounds)
+    recv, send = part.exchange_plan(bounds, windows)
+    lens = [c1 - c0 for c0, c1 in windows]
+    p_index = [100 + 7 * g for g in range(world)]
+    work = [1 << 40 | g << 32 for g in range(world)]        # disjoint fake address ranges
+    mbox = [1 << 44 | g << 32 for g in range(world)]
+    HALO = 256
+    written = [np.zeros(n, dtype=np.int64) for n in lens]
+    for r in range(world):
+        rec = part.push_pieces(send[r], windows, r, lens, p_index, work, mbox, HALO)
+        assert len(rec) == 4 * len(send[r])
+        for (consumer, s, e), k in zip(send[r], range(0, len(rec), 4)):
+            dst, src_off, length, flag = rec[k:k + 4]
+            assert flag == mbox[consumer] + 8 * (HALO + r)
+            dst_index = (dst - work[consumer]) // 8 - p_index[consumer]
+            assert (dst - work[consumer]) % 8 == 0 and 0 <= dst_index and dst_index + length <= lens[consumer]
+            # source entries are owned by r; destination entries are the same global indices
+            g0 = windows[r][0] + src_off
+            assert bounds[r] <= g0 and g0 + length <= bounds[r + 1]
+            assert windows[consumer][0] + dst_index == g0 == s and length == e - s
+            written[consumer][dst_index:dst_index + length] += 1
+    for g in range(world):
+        own = np.zeros(lens[g], dtype=bool)
+        own[int(bounds[g]) - windows[g][0]:int(bounds[g + 1]) - windows[g][0]] = True
+        assert np.all(written[g][~own] == 1) and np.all(written[g][own] == 0)
+    with pytest.raises(RuntimeError):
+        part.push_pieces([(1, windows[1][0] - 5, windows[1][0] + 1)], windows, 0, lens, p_index, work, mbox, HALO)
