@@ -615,6 +615,110 @@ def probe_gather(args, d):
     return 0
 
 
+def probe_formats(args):
+    """Timings of the neighbouring kernels (hitting-time moments, CSRV batched SpMM, DCSR SpMM): device time
+    with operands resident, algorithmic GB/s against the measured copy bandwidth, and the CPU restatement on
+    the same inputs.  One JSON line per kernel; informational, not the headline metric."""
+    import torch
+    from lapis_b200 import device as D
+    from lapis_b200 import workloads as w
+    from oracle import oracle
+    dev = torch.device("cuda:0")
+    peaks, peak_kind = measured_peaks()
+    t = lambda a: torch.as_tensor(np.ascontiguousarray(a)).to(dev)
+
+    def gpu_ms(fn, steps, warmup=3):
+        for _ in range(warmup):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / steps
+
+    def line(kernel, workload, ms, nbytes, cpu_ms, extra=None):
+        gbs = nbytes / (ms * 1e-3) * 1e-9
+        out = {"probe": "formats", "kernel": kernel, "workload": workload, "ms": ms, "algorithmic_bytes": int(nbytes),
+               "gbs": gbs, "frac_of_copy_peak": gbs / peaks["hbm_gbs"], "peak_source": peak_kind,
+               "cpu_ms_1_thread": cpu_ms, "speedup_vs_1_cpu_thread": cpu_ms / ms}
+        out.update(extra or {})
+        print(json.dumps(out), flush=True)
+
+    small = args.small
+    # -- CSRV batched SpMM: 32 stored entries per row, fibers of 8, dh = 64 (2 KiB rows of B and C) --------
+    n = 1 << (14 if small else 17)
+    sp = w.spmm_uniform(n, per_row=32, k=1, idx_dtype=np.int32)
+    nh, dh = 8, 64
+    rng = np.random.default_rng(12)
+    val = rng.standard_normal(len(sp["crd"]) * nh).astype(np.float32)
+    B = rng.standard_normal((n, dh, nh)).astype(np.float32)
+    dpos, dcrd, dval, dB = t(sp["pos"]), t(sp["crd"]), t(val), t(B)
+    C = torch.zeros((n, dh, nh), dtype=torch.float32, device=dev)
+    ms = gpu_ms(lambda: D.bspmm_csrv(dpos, dcrd, dval, dB, n, C), max(3, min(args.steps, 20)))
+    rows_cpu = min(n, 1 << 12)
+    t0 = time.perf_counter()
+    oracle.bspmm(sp["pos"][:rows_cpu + 1], sp["crd"][:int(sp["pos"][rows_cpu])], val[:int(sp["pos"][rows_cpu]) * nh], B)
+    cpu_ms = (time.perf_counter() - t0) * 1e3 * n / rows_cpu
+    nnz = len(sp["crd"])
+    line("bspmm_csrv_kernel", f"CSRV {n} x {n}, 32 per row, nh 8, dh 64, fp32, int32 indices", ms,
+         nnz * (4 + 4 * nh) + 4 * (n + 1) + 2 * 4 * n * dh * nh + 4 * n * dh * nh, cpu_ms,
+         {"gathered_B_bytes": int(nnz) * dh * nh * 4, "cpu_sample": f"first {rows_cpu} rows, scaled by rows"})
+    del dB, C, dval
+    # -- DCSR SpMM: every other row stored, 32 per stored row, k = 64 ------------------------------------
+    n = 1 << (15 if small else 19)
+    sp = w.spmm_uniform(n, per_row=32, k=64, idx_dtype=np.int64)
+    i1 = np.arange(0, 2 * n, 2, dtype=np.int64)
+    dB = t(sp["B"])
+    Cd = torch.zeros((2 * n, 64), dtype=torch.float64, device=dev)
+    di1, dp2, di2, dv = t(i1), t(sp["pos"]), t(sp["crd"]), t(sp["val"])
+    ms = gpu_ms(lambda: D.spmm_dcsr(di1, dp2, di2, dv, dB, Cd, n), max(3, min(args.steps, 20)))
+    rows_cpu = min(n, 1 << 13)
+    t0 = time.perf_counter()
+    oracle.spmm_dcsr(i1[:rows_cpu], sp["pos"][:rows_cpu + 1], sp["crd"], sp["val"], sp["B"], np.zeros((2 * rows_cpu, 64)))
+    cpu_ms = (time.perf_counter() - t0) * 1e3 * n / rows_cpu
+    nnz = len(sp["crd"])
+    line("spmm_dcsr_kernel", f"DCSR {2 * n} x {n}, {n} stored rows, 32 per row, k 64, fp64, int64 indices", ms,
+         nnz * 16 + 8 * (2 * n + 1) + 8 * n * 64 + 2 * 8 * n * 64, cpu_ms,
+         {"gathered_B_bytes": int(nnz) * 64 * 8, "cpu_sample": f"first {rows_cpu} stored rows, scaled by rows"})
+    del dB, Cd
+    # -- hitting-time moments on a grid graph: adjacency of the 5-point stencil, d = degree --------------
+    g = 512 if small else 2048
+    def grid_graph(gg):
+        """Adjacency (unit weights) of the gg x gg grid as int32 CSR, its degree vector and a seed mask."""
+        pos, crd, _ = w.laplacian_2d(gg, idx_dtype=np.int32)
+        rows = np.repeat(np.arange(gg * gg), np.diff(pos))
+        off = crd != rows
+        apos_ = np.concatenate([[0], np.cumsum(np.bincount(rows[off], minlength=gg * gg))]).astype(np.int32)
+        mask_ = np.ones(gg * gg)
+        mask_[:: gg * 7 + 3] = 0.0
+        return apos_, crd[off].astype(np.int32), np.diff(apos_).astype(np.float64), mask_
+
+    apos, acrd, dvec, mask = grid_graph(g)
+    aval = np.ones(len(acrd))
+    its = max(8, min(args.steps, 100))
+    A = D.CsrMatrix.from_host(apos, acrd, aval, (g * g, g * g), dev, tune=True)
+    dm, dd = t(mask), t(dvec)
+    A.mht(dm, dd, 0.95, 0.0, its)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    _, _, iters, _ = A.mht(dm, dd, 0.95, 0.0, its, info=True)
+    torch.cuda.synchronize()
+    ms = (time.perf_counter() - t0) * 1e3 / sum(iters)
+    gc = min(g, 512)
+    cpos, ccrd, cd, cmask = (apos, acrd, dvec, mask) if gc == g else grid_graph(gc)
+    t0 = time.perf_counter()
+    oracle.mht(cpos, ccrd, np.ones(len(ccrd)), cmask, cd, 0.95, 0.0, 8)
+    cpu_ms = (time.perf_counter() - t0) * 1e3 / 16 * (g * g) / (gc * gc)
+    nn, nnz = g * g, len(acrd)
+    line("mht passes (spmv + mht_update + mht_direction)", f"hitting-time moments, {g} x {g} grid graph, int32 indices, "
+         f"{sum(iters)} iterations over the two solves (host-timed, whole solve)", ms,
+         nnz * 12 + 4 * (nn + 1) + 19 * 8 * nn, cpu_ms, {"cpu_sample": f"{gc} x {gc} grid, 16 iterations, scaled by rows"})
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -627,9 +731,10 @@ def main():
     ap.add_argument("--small", action="store_true", help="reduced sizes (for profiler captures and quick checks)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiler captures)")
-    ap.add_argument("--probe", choices=["gather"], default=None,
+    ap.add_argument("--probe", choices=["gather", "formats"], default=None,
                     help="diagnostic instead of the benchmark: 'gather' times out[j] = x[crd[j]] over the SpMV "
-                         "workload's own index stream (torch.index_select), the cost of the x gathers alone")
+                         "workload's own index stream (torch.index_select), the cost of the x gathers alone; "
+                         "'formats' times the hitting-time moments, CSRV batched SpMM and DCSR SpMM kernels")
     ap.add_argument("--shrink", type=int, default=0, help="divide the SpMV/SpMM row count by 2^SHRINK (profiler captures)")
     args = ap.parse_args()
     defaults = {"spmv": (500, 10), "spmv1": (1000, 10), "spmm": (50, 5), "pcg": (200, 5), "bgemm": (200, 10), "gemm": (20, 3)}
@@ -657,6 +762,8 @@ def main():
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         torch.cuda.set_device(local_rank)
         dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local_rank}"))
+    if args.probe == "formats":
+        return probe_formats(args)
     d = make_workload(args.workload, args.small, args.shrink)
     if args.probe == "gather":
         return probe_gather(args, d)
