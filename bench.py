@@ -698,7 +698,7 @@ def probe_formats(args):
 
     apos, acrd, dvec, mask = grid_graph(g)
     aval = np.ones(len(acrd))
-    its = max(8, min(args.steps, 100))
+    its = 100
     A = D.CsrMatrix.from_host(apos, acrd, aval, (g * g, g * g), dev, tune=True)
     dm, dd = t(mask), t(dvec)
     A.mht(dm, dd, 0.95, 0.0, its)

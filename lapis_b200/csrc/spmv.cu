@@ -567,6 +567,48 @@ spmm_row_kernel(const I *__restrict__ pos, const I *__restrict__ crd, const doub
   }
 }
 
+// The same row mapping without the shuffle broadcast: every lane reads the row's (crd, val) pairs itself (one
+// address per warp, served as a broadcast) and keeps UNROLL rows of B in flight as 16-byte loads.  k even, B and
+// C 16-byte aligned.  Same sums in the same order as spmm_row_kernel.
+template <typename I, int SPMM_WARPS, int SPMM_UNROLL>
+__global__ void __launch_bounds__(SPMM_WARPS * 32)
+spmm_row_direct_kernel(const I *__restrict__ pos, const I *__restrict__ crd, const double *__restrict__ val,
+                       int64_t nrows, int64_t k2, const double2 *__restrict__ B2, double2 *__restrict__ C2,
+                       int accumulate) {
+  const int lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * SPMM_WARPS + (threadIdx.x >> 5);
+  if (row >= nrows) return;
+  const int64_t lo = (int64_t)pos[row], hi = (int64_t)pos[row + 1];
+  double2 *crow = C2 + row * k2;
+  for (int64_t c = lane; c < k2; c += 32) {
+    double2 acc = make_double2(0.0, 0.0);
+    int64_t j = lo;
+    for (; j + SPMM_UNROLL <= hi; j += SPMM_UNROLL) {
+      double a[SPMM_UNROLL];
+      double2 b[SPMM_UNROLL];
+#pragma unroll
+      for (int u = 0; u < SPMM_UNROLL; ++u) {
+        a[u] = __ldg(val + j + u);
+        b[u] = __ldg(B2 + (int64_t)crd[j + u] * k2 + c);
+      }
+#pragma unroll
+      for (int u = 0; u < SPMM_UNROLL; ++u) {
+        acc.x = __dadd_rn(acc.x, __dmul_rn(a[u], b[u].x));
+        acc.y = __dadd_rn(acc.y, __dmul_rn(a[u], b[u].y));
+      }
+    }
+    for (; j < hi; ++j) {
+      const double a = __ldg(val + j);
+      const double2 b = __ldg(B2 + (int64_t)crd[j] * k2 + c);
+      acc.x = __dadd_rn(acc.x, __dmul_rn(a, b.x));
+      acc.y = __dadd_rn(acc.y, __dmul_rn(a, b.y));
+    }
+    double2 cin = make_double2(0.0, 0.0);
+    if (accumulate) cin = crow[c];
+    crow[c] = make_double2(__dadd_rn(acc.x, cin.x), __dadd_rn(acc.y, cin.y));
+  }
+}
+
 // ---------------------------------------------------------------------------
 // Host side
 // ---------------------------------------------------------------------------
@@ -724,12 +766,27 @@ template <typename I>
 static int launch_spmm(const lapis_b200_csr *h, int64_t k, const double *B, double *C, int accumulate,
                        cudaStream_t st) {
   static const int variant = [] {
-    int w = 8, u = 4;
+    int w = 0, u = 1;
     if (const char *e = std::getenv("LAPIS_B200_SPMM")) sscanf(e, "%d,%d", &w, &u);
     return w * 100 + u;
   }();
-  // Measured on the 2^21-row, 32-per-row, k = 64 case: (8,4) 6.6 ms, (16,4) 6.7 ms, (8,8) 10.0 ms:
-  // four 512-byte rows in flight per warp at 64 registers (4 blocks per SM) beat eight at 80.
+  // Measured on the 2^21-row, 32-per-row, k = 64 case: the direct-load kernel 5.10 ms with four rows of B in
+  // flight per lane ("0,1", the default) and 5.12 ms with eight ("0,2"); the shuffle-broadcast kernel 6.6 ms
+  // as (8,4), 6.7 ms as (16,4), 10.0 ms as (8,8).  The direct kernel needs k even and 16-byte aligned B, C.
+  const bool vec2 = (k % 2 == 0) && ((reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) % 16 == 0);
+  if (vec2 && (variant == 1 || variant == 2)) {
+    const I *pos = static_cast<const I *>(h->pos);
+    const I *crd = static_cast<const I *>(h->crd);
+    const unsigned grid = (unsigned)((h->nrows + 7) / 8);
+    const double2 *B2 = reinterpret_cast<const double2 *>(B);
+    double2 *C2 = reinterpret_cast<double2 *>(C);
+    if (variant == 1)
+      spmm_row_direct_kernel<I, 8, 4><<<grid, 256, 0, st>>>(pos, crd, h->val, h->nrows, k / 2, B2, C2, accumulate);
+    else
+      spmm_row_direct_kernel<I, 8, 8><<<grid, 256, 0, st>>>(pos, crd, h->val, h->nrows, k / 2, B2, C2, accumulate);
+    LAPIS_CUDA_TRY(cudaGetLastError());
+    return LAPIS_OK;
+  }
   switch (variant) {
     case 808: launch_spmm_variant<I, 8, 8>(h, k, B, C, accumulate, st); break;
     case 1604: launch_spmm_variant<I, 16, 4>(h, k, B, C, accumulate, st); break;
