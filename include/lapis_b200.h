@@ -178,7 +178,11 @@ int lapis_b200_spmv_f64(lapis_b200_csr_t h, const double *d_x, double *d_y, int 
  * synchronises `stream`) and stores the winner in the handle; untuned handles use (256,4).
  * lapis_b200_spmv_select_kernel forces one variant process-wide (threads = 0 returns to the
  * handles' own choice); the environment variable LAPIS_B200_SPMV="threads,blocks,l2_hint" does
- * the same from outside.  l2_hint marks x evict-last in L2. */
+ * the same from outside.  l2_hint marks x evict-last in L2.
+ * A third kind, threads = 1 and blocks_per_sm = 0, gives every row to one thread; the tuner considers it
+ * (and the launch honours it) only for matrices whose longest row has at most 32 entries -- up to there it
+ * returns the same bits as the others -- and such matrices (stencils, bounded-degree graphs) are where it
+ * wins.  On other matrices, and on handles that were never tuned, a request for it runs (256,4). */
 int lapis_b200_csr_tune(lapis_b200_csr_t h, void *stream);
 int lapis_b200_csr_tuned_kernel(lapis_b200_csr_t h, int *threads, int *blocks_per_sm);
 int lapis_b200_spmv_select_kernel(int threads, int blocks_per_sm, int l2_hint);

@@ -52,5 +52,8 @@ struct lapis_b200_csr {
   double *blk_partial;
   // Kernel variant chosen by lapis_b200_csr_tune (tuned_threads == 0: not tuned).
   int tuned_threads, tuned_minb, tuned_hint;
+  // Longest row, found by lapis_b200_csr_tune (-1: not known).  The one-thread-per-row kernel is only used
+  // when no row has more than 32 entries: up to there it returns the same bits as the chunk kernels.
+  int64_t max_row_len;
   int device;
 };

@@ -28,6 +28,7 @@
 // sequential CPU loop (identical bits).  Rows handled by a warp, and rows cut by a chunk
 // boundary, are summed in another fixed order (documented tolerance 1e-12 of the row's
 // magnitude).
+#include <algorithm>
 #include <cstdlib>
 #include <cstring>
 
@@ -487,6 +488,89 @@ __global__ void spmv_fixup_kernel(const I *__restrict__ pos, const int64_t *__re
 }
 
 // ---------------------------------------------------------------------------
+// One thread per row, for matrices whose rows are all short (at most 32 entries; stencils, graphs of bounded
+// degree).  A warp's 32 rows are adjacent in the arrays, so the lines it touches are used completely over the
+// few iterations of the row loop and there is nothing to stage or to synchronise.  A row is summed in entry
+// order; a row that crosses a chunk boundary of the plan is summed in the same two pieces, joined in the same
+// order, as the chunk kernels plus the fix-up kernel do: y has the same bits whichever kernel ran.
+// The grid has one block per chunk of the plan (blocks loop over 256-row tiles), so that blk_partial has the
+// length its consumers expect.
+// ---------------------------------------------------------------------------
+template <typename I>
+__device__ __forceinline__ double row_piece_sum(const I *__restrict__ crd, const double *__restrict__ val,
+                                                const double *__restrict__ x, int64_t lo, int64_t hi) {
+  double acc = 0.0;
+  int64_t j = lo;
+  for (; j + 3 < hi; j += 4) {
+    double a[4], xv[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      a[u] = __ldg(val + j + u);
+      xv[u] = __ldg(x + (int64_t)__ldg(crd + j + u));
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) acc = __dadd_rn(acc, __dmul_rn(a[u], xv[u]));
+  }
+  for (; j < hi; ++j) acc = __dadd_rn(acc, __dmul_rn(__ldg(val + j), __ldg(x + (int64_t)__ldg(crd + j))));
+  return acc;
+}
+
+template <typename I, bool FUSE_DOT>
+__global__ void __launch_bounds__(256)
+spmv_rowthread_kernel(const I *__restrict__ pos, const I *__restrict__ crd, const double *__restrict__ val,
+                      int64_t abase, int64_t nrows, int64_t ntiles, const double *__restrict__ x,
+                      double *__restrict__ y, int accumulate, const double *__restrict__ dotvec,
+                      double *__restrict__ blk_partial, const int *__restrict__ skip_flag) {
+  __shared__ double s_red[8];
+  if (skip_flag != nullptr && *skip_flag != 0) return;
+  double dot_local = 0.0;
+  for (int64_t tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+    const int64_t row = tile * 256 + threadIdx.x;
+    if (row >= nrows) continue;
+    const int64_t lo = (int64_t)pos[row], hi = (int64_t)pos[row + 1];
+    const double yin = accumulate ? y[row] : 0.0;
+    double dv = 0.0;
+    if (FUSE_DOT) dv = dotvec[row];
+    const int64_t bnd = abase + ((lo - abase) / SPMV_TILE + 1) * (int64_t)SPMV_TILE;  // first chunk boundary after lo
+    if (bnd >= hi) {
+      const double s = row_piece_sum<I>(crd, val, x, lo, hi);
+      y[row] = __dadd_rn(s, yin);
+      if (FUSE_DOT) dot_local = __dadd_rn(dot_local, __dmul_rn(s, dv));
+    } else {  // (piece in the later chunk + y_in) + carried piece; rows of at most 32 entries cross one boundary
+      const double s_first = row_piece_sum<I>(crd, val, x, lo, bnd);
+      double carried = s_first;
+      int64_t b0 = bnd;
+      while (b0 + SPMV_TILE < hi) {  // longer rows (not selected by the tuner): middle pieces, in chunk order
+        carried = __dadd_rn(carried, row_piece_sum<I>(crd, val, x, b0, b0 + SPMV_TILE));
+        b0 += SPMV_TILE;
+      }
+      const double s_last = row_piece_sum<I>(crd, val, x, b0, hi);
+      y[row] = __dadd_rn(__dadd_rn(s_last, yin), carried);
+      if (FUSE_DOT) dot_local = __dadd_rn(dot_local, __dmul_rn(__dadd_rn(carried, s_last), dv));
+    }
+  }
+  if (FUSE_DOT) {
+    const double t = block_sum(dot_local, s_red);
+    if (threadIdx.x == 0) blk_partial[blockIdx.x] = t;
+  }
+}
+
+template <typename I>
+__global__ void max_row_len_kernel(const I *__restrict__ pos, int64_t nrows, unsigned long long *out) {
+  unsigned long long m = 0;
+  for (int64_t r = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; r < nrows; r += (int64_t)gridDim.x * blockDim.x) {
+    const unsigned long long len = (unsigned long long)((int64_t)pos[r + 1] - (int64_t)pos[r]);
+    m = len > m ? len : m;
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) {
+    const unsigned long long o = __shfl_xor_sync(0xffffffffu, m, off);
+    m = o > m ? o : m;
+  }
+  if ((threadIdx.x & 31) == 0 && m > 0) atomicMax(out, m);
+}
+
+// ---------------------------------------------------------------------------
 // SpMM: C[r, :] = (accumulate ? C[r, :] : 0) + sum_j val[j] * B[crd[j], :].
 // One warp per row; lane l owns columns {2l, 2l+1} of a 64-column panel, so a B
 // row is fetched as one coalesced 512-byte request and every output element is
@@ -633,7 +717,9 @@ static SpmvVariant &spmv_override() {  // threads == 0: no override
   }();
   return v;
 }
+constexpr int SPMV_ROWTHREAD_MAX_LEN = 32;
 static bool spmv_variant_known(int threads, int minb) {
+  if (threads == 1) return minb == 0;  // one thread per row
   if (threads == -256 || threads == -512) return minb >= 1 && minb <= 8;
   return (threads == 256 && (minb == 4 || minb == 6)) || (threads == 512 && minb == 3);
 }
@@ -693,6 +779,24 @@ static int launch_spmv(const lapis_b200_csr *h, const double *x, double *y, int 
                        cudaStream_t st) {
   SpmvVariant v = spmv_override();
   if (v.threads == 0) v = h->tuned_threads != 0 ? SpmvVariant{h->tuned_threads, h->tuned_minb, h->tuned_hint} : SPMV_DEFAULT;
+  if (v.threads == 1) {
+    // one thread per row: only where it returns the chunk kernels' bits (rows of at most 32 entries, which the
+    // tuner has checked); otherwise the default kernel runs
+    if (h->max_row_len >= 0 && h->max_row_len <= SPMV_ROWTHREAD_MAX_LEN) {
+      const I *pos = static_cast<const I *>(h->pos);
+      const I *crd = static_cast<const I *>(h->crd);
+      const int64_t abase = h->base & ~(int64_t)3, ntiles = (h->nrows + 255) / 256;
+      if (dotvec != nullptr)
+        spmv_rowthread_kernel<I, true><<<(unsigned)h->nblk, 256, 0, st>>>(pos, crd, h->val, abase, h->nrows, ntiles, x, y,
+                                                                          accumulate, dotvec, blk_partial, skip_flag);
+      else
+        spmv_rowthread_kernel<I, false><<<(unsigned)h->nblk, 256, 0, st>>>(pos, crd, h->val, abase, h->nrows, ntiles, x, y,
+                                                                           accumulate, nullptr, nullptr, skip_flag);
+      LAPIS_CUDA_TRY(cudaGetLastError());
+      return LAPIS_OK;
+    }
+    v = SPMV_DEFAULT;
+  }
   if (v.threads < 0) {  // persistent bulk-copy kernel: threads = -256 or -512, minb = blocks per SM
     int rc;
     if (v.threads == -256)
@@ -852,6 +956,7 @@ extern "C" int lapis_b200_csr_create(lapis_b200_csr_t *out, int idx_bytes, int64
   h->blk_partial = nullptr;
   h->carry = nullptr;
   h->tuned_threads = h->tuned_minb = h->tuned_hint = 0;
+  h->max_row_len = -1;
   h->device = dev;
   cudaError_t e = cudaMalloc(&h->blk_row, (size_t)(nblk + 1) * sizeof(int64_t));
   if (e == cudaSuccess) e = cudaMalloc(&h->blk_partial, (size_t)nblk * sizeof(double));
@@ -904,8 +1009,20 @@ extern "C" int lapis_b200_csr_tune(lapis_b200_csr_t h, void *stream) {
     return fail(LAPIS_ECUDA, "csr_tune: cudaMalloc failed: %s", cudaGetErrorString(e));
   }
   cudaMemsetAsync(x, 0, (size_t)(h->ncols > 0 ? h->ncols : 1) * 8, st);
+  if (h->max_row_len < 0) {  // the longest row decides whether the one-thread-per-row kernel is a candidate
+    unsigned long long *d_max = reinterpret_cast<unsigned long long *>(y), h_max = 0;
+    cudaMemsetAsync(d_max, 0, 8, st);
+    const unsigned g = (unsigned)std::min<int64_t>((h->nrows + 255) / 256, (int64_t)sm_count() * 8);
+    if (h->idx_bytes == 4)
+      max_row_len_kernel<int32_t><<<g, 256, 0, st>>>(static_cast<const int32_t *>(h->pos), h->nrows, d_max);
+    else
+      max_row_len_kernel<int64_t><<<g, 256, 0, st>>>(static_cast<const int64_t *>(h->pos), h->nrows, d_max);
+    if (cudaMemcpyAsync(&h_max, d_max, 8, cudaMemcpyDeviceToHost, st) == cudaSuccess && cudaStreamSynchronize(st) == cudaSuccess)
+      h->max_row_len = (int64_t)h_max;
+  }
   const int pipe_blocks = h->idx_bytes == 4 ? 4 : 3;  // what fits in shared memory
-  const SpmvVariant cand[] = {{256, 4, 1}, {256, 6, 1}, {512, 3, 1}, {-256, pipe_blocks, 1}};
+  const bool short_rows = h->max_row_len >= 0 && h->max_row_len <= SPMV_ROWTHREAD_MAX_LEN;
+  const SpmvVariant cand[] = {{256, 4, 1}, {256, 6, 1}, {512, 3, 1}, {-256, pipe_blocks, 1}, {1, 0, 1}};
   const SpmvVariant saved = spmv_override();
   cudaEvent_t e0, e1;
   cudaEventCreate(&e0);
@@ -913,6 +1030,7 @@ extern "C" int lapis_b200_csr_tune(lapis_b200_csr_t h, void *stream) {
   float best = 0.f;
   int status = LAPIS_OK;
   for (const SpmvVariant &c : cand) {
+    if (c.threads == 1 && !short_rows) continue;
     spmv_override() = c;
     status = spmv_launch(h, x, y, 0, nullptr, nullptr, nullptr, st);  // warm-up
     if (status != LAPIS_OK) break;
@@ -1084,6 +1202,7 @@ extern "C" int lapis_b200_spmv_f64_noalloc(int idx_bytes, int64_t nrows, int64_t
   h.blk_partial = nullptr;
   h.carry = reinterpret_cast<double *>(plan + NOALLOC_MAX_TILES + 1);
   h.tuned_threads = h.tuned_minb = h.tuned_hint = 0;
+  h.max_row_len = -1;
   h.device = 0;
   const unsigned pgrid = (unsigned)((nblk + 1 + 255) / 256);
   if (idx_bytes == 4)

@@ -182,10 +182,62 @@ def test_spmv_tuning_keeps_the_bits():
         y0 = torch.zeros(n, dtype=torch.float64, device=dev)
         A.spmv(x, y0, accumulate=False)
         threads, blocks = A.tune()
-        assert (threads, blocks) in ((256, 4), (256, 6), (512, 3), (-256, 3), (-256, 4))
+        assert (threads, blocks) in ((256, 4), (256, 6), (512, 3), (-256, 3), (-256, 4), (1, 0))
         y1 = torch.zeros(n, dtype=torch.float64, device=dev)
         A.spmv(x, y1, accumulate=False)
         assert torch.equal(y0, y1)
+
+
+@pytest.mark.parametrize("idx", [np.int32, np.int64])
+def test_spmv_one_thread_per_row_kernel_keeps_the_bits(idx):
+    """Matrices whose rows have at most 32 entries may run with one thread per row; rows that cross a chunk
+    boundary of the plan are joined as the chunk kernels join them, so y and the accumulate path are
+    bit-identical.  Matrices with a longer row keep the chunk kernels even when the variant is forced."""
+    from lapis_b200._lib import check, load
+    from lapis_b200.device import CsrMatrix
+    dev, lib = _dev(), load()
+    rng = np.random.default_rng(77)
+    cases = []
+    lap = w.pcg_laplacian(300, idx_dtype=idx)
+    cases.append((lap["pos"], lap["crd"], lap["val"], lap["shape"][0]))
+    lens = rng.integers(0, 33, size=50_000)              # 0..32 entries, many rows crossing chunk boundaries
+    pos, crd, val = _random_csr(rng, lens, 50_000, idx)
+    cases.append((pos, crd, val, 50_000))
+    for pos, crd, val, n in cases:
+        x = rng.uniform(-1, 1, n)
+        y_in = rng.uniform(-1, 1, n)
+        A = CsrMatrix.from_host(pos, crd, val, (n, n), dev)
+        xd = torch.as_tensor(x).to(dev)
+        ref = [torch.zeros(n, dtype=torch.float64, device=dev), torch.as_tensor(y_in).to(dev)]
+        A.spmv(xd, ref[0], accumulate=False)
+        A.spmv(xd, ref[1], accumulate=True)
+        A.tune()                                          # finds the longest row; may or may not pick (1, 0)
+        check(lib.lapis_b200_spmv_select_kernel(1, 0, 1))
+        try:
+            got = [torch.zeros(n, dtype=torch.float64, device=dev), torch.as_tensor(y_in).to(dev)]
+            A.spmv(xd, got[0], accumulate=False)
+            A.spmv(xd, got[1], accumulate=True)
+        finally:
+            check(lib.lapis_b200_spmv_select_kernel(0, 0, 0))
+        assert torch.equal(got[0], ref[0]) and torch.equal(got[1], ref[1])
+        yo = oracle.spmv(pos, crd, val, x, y_in)
+        _assert_spmv_close(got[1].cpu().numpy(), yo, _row_scale(pos, crd, val, x, y_in))
+    # a matrix with one long row: the request is not honoured, the result is the chunk kernels'
+    lens = rng.integers(0, 20, size=4000)
+    lens[1234] = 700
+    pos, crd, val = _random_csr(rng, lens, 4000, idx)
+    A = CsrMatrix.from_host(pos, crd, val, (4000, 4000), dev)
+    xd = torch.as_tensor(rng.uniform(-1, 1, 4000)).to(dev)
+    y0 = torch.zeros(4000, dtype=torch.float64, device=dev)
+    A.spmv(xd, y0, accumulate=False)
+    assert A.tune()[0] != 1
+    check(lib.lapis_b200_spmv_select_kernel(1, 0, 1))
+    try:
+        y1 = torch.zeros(4000, dtype=torch.float64, device=dev)
+        A.spmv(xd, y1, accumulate=False)
+    finally:
+        check(lib.lapis_b200_spmv_select_kernel(0, 0, 0))
+    assert torch.equal(y0, y1)
 
 
 def test_spmv_row_block_in_place(spmv_kernel):
