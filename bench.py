@@ -432,7 +432,7 @@ def run_ours(args, d, rank, world, local_rank):
         # The timed region is one solve of K iterations.  Warm-up is a whole untimed solve with the same
         # solver (it also captures the CUDA graph of one iteration that the timed solve replays).
         solver.solve(0.0, args.steps)
-        kernel_name = "spmv_pipe_kernel|spmv_chunk_kernel (pass A) + pcg_update_kernel + pcg_direction_kernel"
+        kernel_name = "spmv_rowthread_kernel|spmv_pipe_kernel|spmv_chunk_kernel (pass A) + pcg_update_kernel + pcg_direction_kernel"
         # ours per iteration: SpMV + its fix-up, three vector passes... 6 on one rank; the NCCL transport adds
         # two scalar-step kernels, the peer-to-peer one six exchange kernels
         launches_per_step = 6 if world == 1 else (8 if solver.comm == "nccl" else 12)
@@ -511,7 +511,7 @@ NCU_TRAFFIC = {
     "spmm": 3.387e10,   # profiles/spmm_row_kernel_config3.md
     "bgemm": 1.036e9,   # profiles/bgemm_tcgen05_kernel.md (4096 x 128^3)
     "gemm": 3.455e9,    # profiles/bgemm_tcgen05_kernel.md (8192^3)
-    "pcg": 2.71e9,      # profiles/pcg_iteration_config5.md (all kernels of one iteration)
+    "pcg": 2.69e9,      # profiles/pcg_iteration_config5.md (all kernels of one iteration)
 }
 
 
