@@ -436,6 +436,9 @@ def run_ours(args, d, rank, world, local_rank):
         # ours per iteration: SpMV + its fix-up, three vector passes... 6 on one rank; the NCCL transport adds
         # two scalar-step kernels, the peer-to-peer one six exchange kernels
         launches_per_step = 6 if world == 1 else (8 if solver.comm == "nccl" else 12)
+        if solver.matrix.tuned_kernel()[0] == 1:
+            launches_per_step -= 1  # the one-thread-per-row SpMV kernel has no carry fix-up launch
+        extra_cfg = dict(extra_cfg or {}, spmv_kernel_tuned=list(solver.matrix.tuned_kernel()))
         steps_holder = {"k": args.steps}
         ms, clocks = timed(lambda: solve(steps_holder["k"]), 1, 0)
         it = state["out"][1]

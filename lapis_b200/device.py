@@ -68,6 +68,12 @@ class CsrMatrix:
         self._lib.lapis_b200_csr_tuned_kernel(self._h, ctypes.byref(t), ctypes.byref(b))
         return int(t.value), int(b.value)
 
+    def tuned_kernel(self):
+        """(threads, blocks_per_sm) stored by the last :meth:`tune` ((0, 0): never tuned)."""
+        t, b = c_int(0), c_int(0)
+        self._lib.lapis_b200_csr_tuned_kernel(self._h, ctypes.byref(t), ctypes.byref(b))
+        return int(t.value), int(b.value)
+
     @classmethod
     def from_host(cls, pos, crd, val, shape, device="cuda", tune: bool = False):
         return cls(torch.as_tensor(np.ascontiguousarray(pos)).to(device), torch.as_tensor(np.ascontiguousarray(crd)).to(device),
