@@ -292,6 +292,44 @@ class LAPISModule:
         self._plans[key] = (tuple(weakref.ref(o) for o in (pos, crd, val)), versions, shape, A)
         return A
 
+    def _row_blocks(self, A, pos_dv, nblocks: int = 4):
+        """Handles over nnz-balanced row blocks of a planned matrix (they share its device arrays; a handle
+        may start at any row because the plan is built from pos[r0:r1+1]), kept with the plan."""
+        from . import partition as part
+        from .device import CsrMatrix
+        blocks = getattr(A, "_row_blocks", None)
+        if blocks is None:
+            bounds = part.partition_rows(pos_dv.host_view(), nblocks)
+            blocks = []
+            for g in range(nblocks):
+                r0, r1 = int(bounds[g]), int(bounds[g + 1])
+                if r1 > r0:
+                    blocks.append((r0, r1, CsrMatrix(A.pos[r0:r1 + 1], A.crd, A.val, (r1 - r0, A.ncols), tune=True)))
+            A._row_blocks = blocks
+        return blocks
+
+    def _run_and_download(self, A, pos_dv, out_dv, run_block):
+        """Runs ``run_block(handle, r0, r1)`` row block by row block and copies each finished block of the
+        result to the host on a second stream while the next block computes; returns with the host side of
+        ``out_dv`` current.  With a page-locked host array the copies are asynchronous and overlap."""
+        import torch
+        dev_out, host = out_dv.device_view(), torch.from_numpy(out_dv.host_view())
+        main = torch.cuda.current_stream()
+        copy = getattr(self, "_copy_stream", None)
+        if copy is None:
+            copy = self._copy_stream = torch.cuda.Stream()
+        for r0, r1, Ab in self._row_blocks(A, pos_dv):
+            run_block(Ab, r0, r1)
+            done = torch.cuda.Event()
+            done.record(main)
+            with torch.cuda.stream(copy):
+                copy.wait_event(done)
+                host[r0:r1].copy_(dev_out[r0:r1], non_blocking=True)
+        copy.synchronize()
+        out_dv.modifyDevice()       # version bump: the contents changed ...
+        out_dv._mod_device = False  # ... and both sides already agree
+        out_dv.downloads += 1
+
     def _bind(self, kind, sfx, idx_dtype):
         lib = self.libHandle
 
@@ -305,10 +343,17 @@ class LAPISModule:
         if kind == "spmv":
             fn = getattr(lib, f"py_spmv_f64_{sfx}")
 
-            def spmv(pos, crd, val, spec, x, y):
+            def spmv(pos, crd, val, spec, x, y, sync_host=False):
+                """``sync_host=True`` (resident path only): return with y already on the host; the matrix is
+                processed in row blocks and each finished block of y is downloaded while the next computes."""
                 if _resident(pos, crd, val, x, y):
                     A = self._plan(pos, crd, val, spec, idx_dtype)
                     x, y = self._dv(x, np.float64), self._dv(y, np.float64)
+                    if sync_host and A.nrows > 0:
+                        xd, yd = x.device_view(), y.device_view()
+                        self._run_and_download(A, self._dv(pos, idx_dtype), y,
+                                               lambda Ab, r0, r1: Ab.spmv(xd, yd[r0:r1], accumulate=True))
+                        return y
                     A.spmv(x.device_view(), y.device_view(), accumulate=True)
                     y.modifyDevice()
                     return y
@@ -325,10 +370,16 @@ class LAPISModule:
         if kind == "spmm":
             fn = getattr(lib, f"py_spmm_f64_{sfx}")
 
-            def spmm(pos, crd, val, spec, B, C):
+            def spmm(pos, crd, val, spec, B, C, sync_host=False):
+                """``sync_host=True`` (resident path only): as for spmv, C comes back block by block."""
                 if _resident(pos, crd, val, B, C):
                     A = self._plan(pos, crd, val, spec, idx_dtype)
                     B, C = self._dv(B, np.float64), self._dv(C, np.float64)
+                    if sync_host and A.nrows > 0:
+                        Bd, Cd = B.device_view(), C.device_view()
+                        self._run_and_download(A, self._dv(pos, idx_dtype), C,
+                                               lambda Ab, r0, r1: Ab.spmm(Bd, Cd[r0:r1], accumulate=True))
+                        return C
                     A.spmm(B.device_view(), C.device_view(), accumulate=True)
                     C.modifyDevice()
                     return C

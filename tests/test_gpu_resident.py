@@ -42,6 +42,15 @@ def test_spmv_resident_matches_upload_path_and_skips_copies():
     ref = oracle.spmv(d["pos"], d["crd"], d["val"], x.host_view(), np.zeros(n))
     scale = oracle.spmv(d["pos"], d["crd"], np.abs(d["val"]), np.abs(x.host_view()), np.zeros(n))
     assert np.all(np.abs(y2.numpy() - ref) <= 1e-12 * np.maximum(scale, 1e-300))
+    # sync_host=True: the result arrives on the host with the call, block by block behind the kernel
+    y4 = DualView(np.ones(n))
+    out = module.spmv(pos, crd, val, _spec(d), x, y4, sync_host=True)
+    assert out is y4 and not y4.modifiedDevice() and not y4.modifiedHost() and y4.downloads == 1
+    ref4 = oracle.spmv(d["pos"], d["crd"], d["val"], x.host_view(), np.ones(n))
+    assert np.all(np.abs(y4.host_view() - ref4) <= 1e-12 * np.maximum(scale + 1.0, 1e-300))
+    assert torch.equal(y4.device_view().cpu(), torch.from_numpy(y4.host_view())) and y4.uploads == 1
+    module.spmv(pos, crd, val, _spec(d), x, y4, sync_host=True)          # accumulates on the resident copy
+    assert np.all(np.abs(y4.host_view() - (2 * ref4 - 1.0)) <= 4e-12 * np.maximum(scale + 1.0, 1e-300))
     # changing the matrix values rebuilds the plan
     val.host_view()[:] *= -1.0
     val.modifyHost()
@@ -73,6 +82,9 @@ def test_spmm_matmul_and_pcg_resident():
     module = KB.KokkosBackend(decompose_tensors=True).compile(mm.spmm(mm.CSR64))
     C = module.spmm(DualView(d["pos"]), DualView(d["crd"]), DualView(d["val"]), _spec(d), DualView(B), DualView(np.zeros((n, 64))))
     assert np.array_equal(C.numpy(), oracle.spmm(d["pos"], d["crd"], d["val"], B, np.zeros((n, 64))))
+    C2 = module.spmm(DualView(d["pos"]), DualView(d["crd"]), DualView(d["val"]), _spec(d), DualView(B), DualView(np.zeros((n, 64))),
+                     sync_host=True)
+    assert not C2.modifiedDevice() and np.array_equal(C2.host_view(), C.numpy())      # SpMM rows are independent: same bits
 
     a = rng.standard_normal((4, 48, 40)).astype(np.float32)
     b = rng.standard_normal((4, 40, 56)).astype(np.float32)
