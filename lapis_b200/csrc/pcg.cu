@@ -813,6 +813,8 @@ extern "C" int lapis_b200_mht_f64(lapis_b200_csr_t h, const double *d_mask, cons
   if (d_mask == nullptr || d_d == nullptr || d_mom1 == nullptr || d_mom2 == nullptr)
     return fail(LAPIS_EBADARG, "mht: null operand");
   cudaStream_t st = as_stream(stream);
+  // two solves run the SpMV pass many times: pick the kernel variant for this matrix first
+  if (h->tuned_threads == 0 && (maxiter == 0 || maxiter >= 16)) LAPIS_TRY(lapis_b200_csr_tune(h, st));
   const unsigned G = vec_grid(n);
   const size_t work_doubles = 16 + 3 * (size_t)G + 5 * (size_t)n;
   // [work][b][pad][scaled values][pad]: the SpMV kernels stream the values with 16-byte accesses starting at
