@@ -625,6 +625,35 @@ def probe_gather(args, d):
     return 0
 
 
+def probe_flatdot(args, d):
+    """Floor for the SpMV: the library's flat-dot yardstick kernel over the workload's own crd / val / x (same
+    streams, same gathers, four entries per thread, no row structure, no per-entry store)."""
+    import ctypes
+    import torch
+    from lapis_b200._lib import check, load
+    dev = torch.device("cuda:0")
+    lib = load()
+    x, crd, val = (torch.as_tensor(d[k]).to(dev) for k in ("x", "crd", "val"))
+    out = torch.zeros(1, dtype=torch.float64, device=dev)
+    vp = lambda t: ctypes.c_void_p(t.data_ptr())
+    run = lambda: check(lib.lapis_b200_probe_flat_dot_f64(crd.element_size(), crd.numel(), vp(crd), vp(val), vp(x), vp(out),
+                                                          ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))
+    for _ in range(max(3, args.warmup)):
+        run()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        run()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    nbytes = crd.numel() * (8 + crd.element_size()) + x.numel() * 8
+    print(json.dumps({"probe": "flatdot", "entries": int(crd.numel()), "ms": ms, "gathers_per_s": crd.numel() / (ms * 1e-3),
+                      "stream_plus_x_gbs": nbytes / (ms * 1e-3) * 1e-9}), flush=True)
+    return 0
+
+
 def probe_formats(args):
     """Timings of the neighbouring kernels (hitting-time moments, CSRV batched SpMM, DCSR SpMM): device time
     with operands resident, algorithmic GB/s against the measured copy bandwidth, and the CPU restatement on
@@ -741,9 +770,11 @@ def main():
     ap.add_argument("--small", action="store_true", help="reduced sizes (for profiler captures and quick checks)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiler captures)")
-    ap.add_argument("--probe", choices=["gather", "formats"], default=None,
+    ap.add_argument("--probe", choices=["gather", "flatdot", "formats"], default=None,
                     help="diagnostic instead of the benchmark: 'gather' times out[j] = x[crd[j]] over the SpMV "
-                         "workload's own index stream (torch.index_select), the cost of the x gathers alone; "
+                         "workload's own index stream (torch.index_select: index read, gather, 8-byte store per entry); "
+                         "'flatdot' times the library's store-free yardstick sum_j val[j]*x[crd[j]] over the same "
+                         "arrays, the floor for an SpMV; "
                          "'formats' times the hitting-time moments, CSRV batched SpMM and DCSR SpMM kernels")
     ap.add_argument("--shrink", type=int, default=0, help="divide the SpMV/SpMM row count by 2^SHRINK (profiler captures)")
     args = ap.parse_args()
@@ -777,6 +808,8 @@ def main():
     d = make_workload(args.workload, args.small, args.shrink)
     if args.probe == "gather":
         return probe_gather(args, d)
+    if args.probe == "flatdot":
+        return probe_flatdot(args, d)
     run_ours(args, d, rank, world, local_rank)
     if world > 1:
         # All ranks have reported; leave without communicator teardown (destroy_process_group() has

@@ -190,6 +190,12 @@ int lapis_b200_spmv_select_kernel(int threads, int blocks_per_sm, int l2_hint);
  * returns LAPIS_ECUDA if a block gave up (then y of that launch is invalid), clearing the flag. */
 int lapis_b200_spmv_status(void *stream);
 
+/* Measurement aid (no counterpart in the reference, not on any product path): reads the first nnz & ~3
+ * entries of crd and val, gathers x and sums the products per thread without row structure and without a
+ * store per entry.  Its duration is the floor for an SpMV over the same arrays; bench.py --probe flatdot. */
+int lapis_b200_probe_flat_dot_f64(int idx_bytes, int64_t nnz, const void *d_crd, const double *d_val, const double *d_x,
+                                  double *d_out, void *stream);
+
 /* The same SpMV for callers that must not allocate device memory in the call -- code
  * running inside a pool that already owns the whole GPU, or a steady-state loop where
  * a cudaMalloc could stall the device or fail.  No counterpart in the reference (its

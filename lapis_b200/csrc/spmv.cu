@@ -36,7 +36,10 @@
 
 namespace lapis_b200 {
 
-constexpr int SPMV_TILE = 2048;       // stored entries per chunk == per thread block (part of the plan's meaning)
+#ifndef LAPIS_SPMV_TILE
+#define LAPIS_SPMV_TILE 2048
+#endif
+constexpr int SPMV_TILE = LAPIS_SPMV_TILE;       // stored entries per chunk == per thread block (part of the plan's meaning)
 constexpr int SPMV_POS_CACHE = 1024;  // row offsets staged per block; further rows read global memory
 constexpr int SPMV_LONG_ROW = 32;     // rows with more in-chunk entries than this are reduced by a whole warp
 
@@ -721,7 +724,7 @@ constexpr int SPMV_ROWTHREAD_MAX_LEN = 32;
 static bool spmv_variant_known(int threads, int minb) {
   if (threads == 1) return minb == 0;  // one thread per row
   if (threads == -256 || threads == -512) return minb >= 1 && minb <= 8;
-  return (threads == 256 && (minb == 4 || minb == 6)) || (threads == 512 && minb == 3);
+  return (threads == 256 && (minb == 4 || minb == 6)) || (threads == 512 && minb == 3 && SPMV_TILE >= 1024);
 }
 
 template <typename I, int THREADS, int MINB, bool HINT>
@@ -818,7 +821,10 @@ static int launch_spmv(const lapis_b200_csr *h, const double *x, double *y, int 
   } else
   LAPIS_V(256, 6)
   LAPIS_V(256, 4)
+#if LAPIS_SPMV_TILE >= 1024
   LAPIS_V(512, 3)
+#endif
+
   { return fail(LAPIS_EBADARG, "LAPIS_B200_SPMV names an unknown kernel variant"); }
 #undef LAPIS_V
   LAPIS_CUDA_TRY(cudaGetLastError());
@@ -898,6 +904,27 @@ static int launch_spmm(const lapis_b200_csr *h, int64_t k, const double *B, doub
   }
   LAPIS_CUDA_TRY(cudaGetLastError());
   return LAPIS_OK;
+}
+
+// Yardstick, not part of the product path: sum_j val[j] * x[crd[j]] with no row structure and no per-entry
+// store -- the same value and index streams and the same gathers as the SpMV, four entries per thread, every
+// thread independent.  What it takes is the floor for any SpMV over these arrays.
+template <typename I>
+__global__ void __launch_bounds__(256)
+flat_dot_probe_kernel(const I *__restrict__ crd, const double *__restrict__ val, const double *__restrict__ x,
+                      double *__restrict__ out, int64_t n) {
+  const int64_t base = ((int64_t)blockIdx.x * 256 + threadIdx.x) * 4;
+  if (base + 4 > n) return;
+  using Pair = typename IndexPair<I>::type;
+  double s = 0.0;
+#pragma unroll
+  for (int u = 0; u < 4; u += 2) {
+    const Pair c = __ldcs(reinterpret_cast<const Pair *>(crd + base + u));
+    const double2 a = __ldcs(reinterpret_cast<const double2 *>(val + base + u));
+    s = __dadd_rn(s, __dmul_rn(a.x, __ldg(x + (int64_t)c.x)));
+    s = __dadd_rn(s, __dmul_rn(a.y, __ldg(x + (int64_t)c.y)));
+  }
+  if (s == 1.2345e300) out[0] = s;  // keeps the loads alive without a store per thread
 }
 
 }  // namespace lapis_b200
@@ -1031,6 +1058,7 @@ extern "C" int lapis_b200_csr_tune(lapis_b200_csr_t h, void *stream) {
   int status = LAPIS_OK;
   for (const SpmvVariant &c : cand) {
     if (c.threads == 1 && !short_rows) continue;
+    if (!spmv_variant_known(c.threads, c.minb)) continue;
     spmv_override() = c;
     status = spmv_launch(h, x, y, 0, nullptr, nullptr, nullptr, st);  // warm-up
     if (status != LAPIS_OK) break;
@@ -1211,4 +1239,23 @@ extern "C" int lapis_b200_spmv_f64_noalloc(int idx_bytes, int64_t nrows, int64_t
     spmv_plan_kernel<int64_t><<<pgrid, 256, 0, st>>>(static_cast<const int64_t *>(d_pos), nrows, nblk, plan);
   LAPIS_CUDA_TRY(cudaGetLastError());
   return spmv_launch(&h, d_x, d_y, accumulate, nullptr, nullptr, nullptr, st);
+}
+
+// Launches the flat-dot yardstick over the first nnz & ~3 entries (crd, val 16-byte aligned).
+extern "C" int lapis_b200_probe_flat_dot_f64(int idx_bytes, int64_t nnz, const void *d_crd, const double *d_val,
+                                             const double *d_x, double *d_out, void *stream) {
+  clear_error();
+  if ((idx_bytes != 4 && idx_bytes != 8) || nnz < 0 || d_crd == nullptr || d_val == nullptr || d_x == nullptr || d_out == nullptr)
+    return fail(LAPIS_EBADARG, "probe_flat_dot: bad arguments");
+  if ((reinterpret_cast<uintptr_t>(d_val) % 16) || (reinterpret_cast<uintptr_t>(d_crd) % 16))
+    return fail(LAPIS_EBADARG, "probe_flat_dot: val and crd must be 16-byte aligned");
+  const int64_t n = nnz & ~(int64_t)3;
+  if (n == 0) return LAPIS_OK;
+  const unsigned grid = (unsigned)((n / 4 + 255) / 256);
+  if (idx_bytes == 4)
+    flat_dot_probe_kernel<int32_t><<<grid, 256, 0, as_stream(stream)>>>(static_cast<const int32_t *>(d_crd), d_val, d_x, d_out, n);
+  else
+    flat_dot_probe_kernel<int64_t><<<grid, 256, 0, as_stream(stream)>>>(static_cast<const int64_t *>(d_crd), d_val, d_x, d_out, n);
+  LAPIS_CUDA_TRY(cudaGetLastError());
+  return LAPIS_OK;
 }
