@@ -330,6 +330,84 @@ class LAPISModule:
         out_dv._mod_device = False  # ... and both sides already agree
         out_dv.downloads += 1
 
+    # An SpMV whose x arrives from the host every call cannot start before x is on the device -- unless the
+    # matrix is also kept as two column halves: the half that only reads x[:mid] runs while x[mid:] is still
+    # on its way.  Used by spmv(..., sync_host=True) for large x whose host side was modified.
+    PIPELINE_MIN_X_BYTES = 8 << 20
+
+    def _column_halves(self, A, pos_dv, crd_dv, val_dv, nblocks: int = 4):
+        """(mid, handle over columns [0, mid), row-block handles over columns [mid, ncols)), kept with the plan."""
+        import torch
+        from . import partition as part
+        from .device import CsrMatrix
+        halves = getattr(A, "_col_halves", None)
+        if halves is None:
+            pos, crd, val = pos_dv.host_view(), crd_dv.host_view(), val_dv.host_view()
+            mid = A.ncols // 2
+            left = crd < mid
+            before = np.zeros(len(crd) + 1, dtype=np.int64)
+            np.cumsum(left, out=before[1:])
+            pos1 = before[pos].astype(pos.dtype)          # entries of each row that fall into the left half
+            pos2 = (pos - pos1).astype(pos.dtype)
+            del before
+            dev = A.pos.device
+            A1 = CsrMatrix.from_host(pos1, crd[left], val[left], (A.nrows, A.ncols), dev, tune=True)
+            right = ~left
+            del left
+            dpos2 = torch.as_tensor(pos2).to(dev)
+            dcrd2 = torch.as_tensor(np.ascontiguousarray(crd[right])).to(dev)
+            dval2 = torch.as_tensor(np.ascontiguousarray(val[right])).to(dev)
+            bounds = part.partition_rows(pos2, nblocks)  # bounds[0] = 0, bounds[-1] = nrows: the blocks cover every row
+            blocks = []
+            for g in range(nblocks):
+                r0, r1 = int(bounds[g]), int(bounds[g + 1])
+                if r1 > r0:
+                    blocks.append((r0, r1, CsrMatrix(dpos2[r0:r1 + 1], dcrd2, dval2, (r1 - r0, A.ncols), tune=True)))
+            halves = A._col_halves = (mid, A1, blocks)
+        return halves
+
+    def _spmv_pipelined(self, A, pos_dv, crd_dv, val_dv, x, y):
+        """y += A x with x uploaded in two pieces: the left column half of A runs on x[:mid] while x[mid:] is
+        uploaded; the right half runs row block by row block and each finished block of y goes back to the
+        host while the next computes.  Returns with both sides of x and y in agreement.  A row's sum is formed as
+        (y_in + left part) + right part: it agrees with the unsplit call to rounding, not bit for bit."""
+        import torch
+        mid, A1, blocks = self._column_halves(A, pos_dv, crd_dv, val_dv)
+        yd, yh = y.device_view(), torch.from_numpy(y.host_view())
+        if x._device is None:
+            x._device = torch.empty(x.shape, dtype=torch.float64, device=A.pos.device)
+        xd, xh = x._device, torch.from_numpy(x.host_view())
+        main = torch.cuda.current_stream()
+        for name in ("_copy_stream", "_upload_stream"):
+            if getattr(self, name, None) is None:
+                setattr(self, name, torch.cuda.Stream())
+        copy, up = self._copy_stream, self._upload_stream
+        up.wait_stream(main)  # earlier kernels may still read x
+        with torch.cuda.stream(up):
+            xd[:mid].copy_(xh[:mid], non_blocking=True)
+            first = torch.cuda.Event()
+            first.record(up)
+            xd[mid:].copy_(xh[mid:], non_blocking=True)
+            second = torch.cuda.Event()
+            second.record(up)
+        main.wait_event(first)
+        A1.spmv(xd, yd, accumulate=True)
+        main.wait_event(second)
+        for r0, r1, Ab in blocks:
+            Ab.spmv(xd, yd[r0:r1], accumulate=True)
+            done = torch.cuda.Event()
+            done.record(main)
+            with torch.cuda.stream(copy):
+                copy.wait_event(done)
+                yh[r0:r1].copy_(yd[r0:r1], non_blocking=True)
+        copy.synchronize()
+        up.synchronize()
+        x._mod_host = False
+        x.uploads += 1
+        y.modifyDevice()
+        y._mod_device = False
+        y.downloads += 1
+
     def _bind(self, kind, sfx, idx_dtype):
         lib = self.libHandle
 
@@ -350,6 +428,10 @@ class LAPISModule:
                     A = self._plan(pos, crd, val, spec, idx_dtype)
                     x, y = self._dv(x, np.float64), self._dv(y, np.float64)
                     if sync_host and A.nrows > 0:
+                        if x.modifiedHost() and x.host_view().nbytes >= self.PIPELINE_MIN_X_BYTES:
+                            self._spmv_pipelined(A, self._dv(pos, idx_dtype), self._dv(crd, idx_dtype),
+                                                 self._dv(val, np.float64), x, y)
+                            return y
                         xd, yd = x.device_view(), y.device_view()
                         self._run_and_download(A, self._dv(pos, idx_dtype), y,
                                                lambda Ab, r0, r1: Ab.spmv(xd, yd[r0:r1], accumulate=True))

@@ -59,6 +59,39 @@ def test_spmv_resident_matches_upload_path_and_skips_copies():
     assert np.array_equal(y3.numpy(), -y2.numpy()) and val.uploads == 2
 
 
+def test_spmv_pipelined_upload_matches_oracle():
+    """x large enough for the two-piece upload: the left column half of the matrix runs while the second
+    piece of x is still being copied; result on the host with the call, correct to rounding, repeatable."""
+    n = 1 << 21                                          # x is 16 MiB: above the pipelining threshold
+    d = w.spmv_power_law(n, mean=4.0)
+    module = KB.KokkosBackend(decompose_tensors=True).compile(mm.spmv(mm.CSR64))
+    assert d["x"].nbytes >= module.PIPELINE_MIN_X_BYTES
+    pos, crd, val, x = (DualView(a) for a in (d["pos"], d["crd"], d["val"], d["x"]))
+    y_in = np.random.default_rng(3).uniform(-1, 1, n)
+    y = DualView(y_in.copy())
+    out = module.spmv(pos, crd, val, _spec(d), x, y, sync_host=True)
+    assert out is y and not y.modifiedDevice() and not x.modifiedHost() and x.uploads == 1 and y.downloads == 1
+    ref = oracle.spmv(d["pos"], d["crd"], d["val"], d["x"], y_in)
+    scale = oracle.spmv(d["pos"], d["crd"], np.abs(d["val"]), np.abs(d["x"]), np.abs(y_in))
+    assert np.all(np.abs(y.host_view() - ref) <= 2e-12 * np.maximum(scale, 1e-300))
+    assert torch.equal(y.device_view().cpu(), torch.from_numpy(y.host_view()))
+    first = y.host_view().copy()
+    # a new x: the same pipeline again, on top of the resident y
+    x.host_view()[:] = -x.host_view()
+    x.modifyHost()
+    module.spmv(pos, crd, val, _spec(d), x, y, sync_host=True)
+    assert x.uploads == 2 and pos.uploads == 1
+    assert np.all(np.abs(y.host_view() - y_in) <= 4e-12 * np.maximum(scale, 1e-300))   # +Ax then -Ax
+    # unchanged x: no upload, the plain overlapped-download path
+    module.spmv(pos, crd, val, _spec(d), x, y, sync_host=True)
+    assert x.uploads == 2
+    y2 = DualView(y_in.copy())
+    x.host_view()[:] = -x.host_view()
+    x.modifyHost()
+    module.spmv(pos, crd, val, _spec(d), x, y2, sync_host=True)
+    assert np.array_equal(y2.host_view(), first)                                        # repeatable bit for bit
+
+
 def test_mixed_arguments_and_bad_specifier():
     d = w.spmv_power_law(1 << 10, idx_dtype=np.int32)
     module = KB.KokkosBackend(decompose_tensors=True).compile(mm.spmv(mm.CSR32))
