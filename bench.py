@@ -338,14 +338,17 @@ def run_ours(args, d, rank, world, local_rank):
         r0, r1 = int(bounds[rank]), int(bounds[rank + 1])
         lpos, lcrd, lval = part.row_block(pos, crd, val, r0, r1)
         A = D.CsrMatrix.from_host(lpos, lcrd, lval, (r1 - r0, n), dev)
-        extra_cfg_kernel = A.tune() if name != "spmm" else (0, 0)  # per-matrix choice of the SpMV kernel
+        # per-matrix choice of the SpMV kernel; relaxed: the segmented-scan kernel (within 1e-12 of the others,
+        # the parity bar of this metric, but not their bits) is a candidate
+        extra_cfg_kernel = A.tune(relaxed=True) if name != "spmm" else (0, 0)
         extra_cfg = {"partition": "contiguous row blocks, equal nnz", "rows_rank0": int(bounds[1] - bounds[0]),
                      "replicated": "B" if name == "spmm" else "x", "spmv_kernel_tuned": list(extra_cfg_kernel)}
         if name != "spmm":
             xd = torch.as_tensor(d["x"]).to(dev)
             yd = torch.zeros(r1 - r0, dtype=torch.float64, device=dev)
             step = lambda: A.spmv(xd, yd, accumulate=False)
-            kernel_name = "spmv_chunk_kernel"
+            kernel_name = {2: "spmv_scan_kernel", 1: "spmv_rowthread_kernel"}.get(
+                extra_cfg_kernel[0], "spmv_pipe_kernel" if extra_cfg_kernel[0] < 0 else "spmv_chunk_kernel")
             host_in = [lpos, lcrd, lval, d["x"]]
             module = KB.KokkosBackend(decompose_tensors=True).compile(mm.spmv(mm.CSR64))
         else:
@@ -529,11 +532,14 @@ def emit(args, d, value, ms_step, clocks, e2e, launches, kernel_name, algo_bytes
          world, rank, extra_cfg, bound):
     if rank != 0:
         return
+    traffic = NCU_TRAFFIC[d["name"]] / world if d["name"] in NCU_TRAFFIC else None
+    if d["name"] == "spmv" and kernel_name != "spmv_chunk_kernel":
+        traffic = None  # the committed capture is of the chunk kernel
     if bound == "hbm":
         achieved = algo_bytes_rank / (kernel_ms * 1e-3) * 1e-9
         peak = float(peaks["hbm_gbs"])
         roof = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                "traffic": (NCU_TRAFFIC[d["name"]] / world if d["name"] in NCU_TRAFFIC else None), "kernel": kernel_name,
+                "traffic": traffic, "kernel": kernel_name,
                 "peak_source": f"{peak_kind} copy bandwidth",
                 "algorithmic_bytes_per_launch": algo_bytes_rank, "frac_of_8TBs": achieved / 8000.0}
     else:
@@ -542,7 +548,7 @@ def emit(args, d, value, ms_step, clocks, e2e, launches, kernel_name, algo_bytes
         tf32_peak = float(peaks["bf16_tflops"]) / 2.0
         achieved = 3.0 * d["work"] / world / (kernel_ms * 1e-3) * 1e-12
         roof = {"bound": "tensor", "achieved": achieved, "peak": tf32_peak, "unit": "TFLOP/s", "frac": achieved / tf32_peak,
-                "traffic": (NCU_TRAFFIC[d["name"]] / world if d["name"] in NCU_TRAFFIC else None), "kernel": kernel_name,
+                "traffic": traffic, "kernel": kernel_name,
                 "peak_source": f"{peak_kind} bf16 burst / 2 (TF32); achieved counts the 3 TF32 products per fp32 product"}
     line = {
         "metric": d["metric"], "value": value, "unit": d["unit"], "n_gpus": world, "steps": args.steps,

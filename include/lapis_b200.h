@@ -182,8 +182,15 @@ int lapis_b200_spmv_f64(lapis_b200_csr_t h, const double *d_x, double *d_y, int 
  * A third kind, threads = 1 and blocks_per_sm = 0, gives every row to one thread; the tuner considers it
  * (and the launch honours it) only for matrices whose longest row has at most 32 entries -- up to there it
  * returns the same bits as the others -- and such matrices (stencils, bounded-degree graphs) are where it
- * wins.  On other matrices, and on handles that were never tuned, a request for it runs (256,4). */
+ * wins.  On other matrices, and on handles that were never tuned, a request for it runs (256,4).
+ * A fourth kind, threads = 2 with blocks_per_sm in {4, 5}, is the chunk kernel with the row sums done by a
+ * segmented scan in registers instead of one lane per row over shared memory (less shared-memory traffic
+ * when the gathers of x already saturate L1).  It adds a row's products in scan order, so y agrees with the
+ * other kernels to 1e-12 of the row's magnitude but not bit for bit; lapis_b200_csr_tune therefore leaves it
+ * out, and lapis_b200_csr_tune_relaxed is the same tuner with it among the candidates, for callers who want
+ * the fastest kernel within the tolerance rather than one set of bits whichever kernel runs. */
 int lapis_b200_csr_tune(lapis_b200_csr_t h, void *stream);
+int lapis_b200_csr_tune_relaxed(lapis_b200_csr_t h, void *stream);
 int lapis_b200_csr_tuned_kernel(lapis_b200_csr_t h, int *threads, int *blocks_per_sm);
 int lapis_b200_spmv_select_kernel(int threads, int blocks_per_sm, int l2_hint);
 /* The persistent kernel bounds its waits on the bulk copies; this synchronises `stream` and
@@ -200,7 +207,7 @@ int lapis_b200_probe_flat_dot_f64(int idx_bytes, int64_t nnz, const void *d_crd,
  * running inside a pool that already owns the whole GPU, or a steady-state loop where
  * a cudaMalloc could stall the device or fail.  No counterpart in the reference (its
  * emitted kernels need no plan).  Takes the raw CSR arrays instead of a handle and
- * keeps the streaming plan in a fixed 2 MiB array inside the library's device image,
+ * keeps the streaming plan and the carries in a fixed 4 MiB array inside the library's device image,
  * so it calls neither cudaMalloc nor cudaFree.
  *   - Limit: 2^29 (536,870,912) stored entries; larger matrices get LAPIS_ETOOBIG.
  *   - The first call on a device looks the array's address up (cudaGetSymbolAddress);

@@ -38,6 +38,7 @@ _PROTOS = {
     "lapis_b200_csr_nnz": (c_i64, [c_vp]),
     "lapis_b200_spmv_f64": (c_int, [c_vp, c_vp, c_vp, c_int, c_vp]),
     "lapis_b200_csr_tune": (c_int, [c_vp, c_vp]),
+    "lapis_b200_csr_tune_relaxed": (c_int, [c_vp, c_vp]),
     "lapis_b200_csr_tuned_kernel": (c_int, [c_vp, ctypes.POINTER(c_int), ctypes.POINTER(c_int)]),
     "lapis_b200_spmv_select_kernel": (c_int, [c_int, c_int, c_int]),
     "lapis_b200_spmv_status": (c_int, [c_vp]),

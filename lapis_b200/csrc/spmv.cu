@@ -277,6 +277,149 @@ spmv_chunk_kernel(const I *__restrict__ pos, const I *__restrict__ crd, const do
   }
 }
 
+// ---------------------------------------------------------------------------
+// Segmented-scan variant of the chunk kernel.  The chunk kernel's row sums read the
+// staged products with one lane per row, which costs about one shared-memory wavefront
+// for every two entries (lanes of a warp walk different rows and collide on banks); with
+// random columns the gathers of x already use one L1 wavefront per entry, so that extra
+// traffic is a third of the kernel's time.  Here the products never leave the registers
+// before they are summed: row starts are marked in a bit mask (one shared atomic per row),
+// every warp runs a segmented inclusive scan over each 64-entry group it holds (a pair per
+// lane, five shuffle steps), and only the scanned values are stored -- one conflict-free
+// 16-byte store per pair.  A row then costs one thread one read: the scanned value at its
+// last entry, plus the closing values ("tails") of the earlier groups it spans.
+//
+// Same plan, carry array and fix-up kernel as the chunk kernel.  A row is summed in scan
+// order, not entry order: results are identical from run to run and within 1e-12 of the
+// row's magnitude of the sequential sum, but not bit-identical to the other variants
+// (rows of a single entry and empty rows are).
+// ---------------------------------------------------------------------------
+template <typename I, int MINB, bool FUSE_DOT, bool HINT>
+__global__ void __launch_bounds__(256, MINB)
+spmv_scan_kernel(const I *__restrict__ pos, const I *__restrict__ crd, const double *__restrict__ val,
+                 const int64_t *__restrict__ plan, int64_t abase, int64_t nnz_end, int64_t nrows,
+                 const double *__restrict__ x, double *__restrict__ y, int accumulate,
+                 double *__restrict__ carry, const double *__restrict__ dotvec,
+                 double *__restrict__ blk_partial, const int *__restrict__ skip_flag) {
+  constexpr int T = SPMV_TILE, THREADS = 256;
+  constexpr int PAIRS = T / (2 * THREADS);
+  constexpr int NGROUPS = T / 64;  // group g = entries [64 g, 64 g + 64): the pairs one warp holds for one k
+  static_assert(T % (2 * THREADS) == 0, "a chunk is a whole number of pairs per thread");
+  __shared__ __align__(16) double s_scan[T];
+  __shared__ int s_rel[SPMV_POS_CACHE + 2];
+  __shared__ unsigned s_head[T / 32];
+  __shared__ double s_tail[NGROUPS];
+  __shared__ double s_red[THREADS / 32];
+  using Pair = typename IndexPair<I>::type;
+
+  asm volatile("griddepcontrol.launch_dependents;");
+  if (skip_flag != nullptr && *skip_flag != 0) return;
+
+  const int tid = threadIdx.x, lane = tid & 31;
+  const int chunk = (int)blockIdx.x;
+  ChunkCtx c;
+  c.c0 = abase + (int64_t)blockIdx.x * T;
+  const int64_t left = nnz_end - c.c0;
+  c.len = (int)(left < T ? (left < 0 ? 0 : left) : T);
+  c.row0 = plan[blockIdx.x];
+  const int64_t rn = plan[blockIdx.x + 1];
+  c.has_tail = rn < nrows;
+  const int64_t nr64 = rn - c.row0 + (c.has_tail ? 1 : 0);
+  c.nr = (int)(nr64 > 0x7fffffff ? 0x7fffffff : nr64);
+  c.ncached = (int)(nr64 + 1 < SPMV_POS_CACHE + 2 ? nr64 + 1 : SPMV_POS_CACHE + 2);
+
+  uint64_t policy = 0;
+  if (HINT) asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(policy));
+
+  // ---- stream phase: the chunk's (val, crd) pairs into registers ---------------------------
+  const double *vb = val + c.c0;
+  const I *cb = crd + c.c0;
+  double2 v[PAIRS];
+  Pair ci[PAIRS];
+#pragma unroll
+  for (int k = 0; k < PAIRS; ++k) {
+    const int j = 2 * (tid + k * THREADS);
+    v[k] = make_double2(0.0, 0.0);
+    ci[k].x = 0;
+    ci[k].y = 0;
+    if (j + 1 < c.len) {
+      v[k] = __ldcs(reinterpret_cast<const double2 *>(vb + j));
+      ci[k] = __ldcs(reinterpret_cast<const Pair *>(cb + j));
+    } else if (j < c.len) {  // odd tail of the last chunk
+      v[k].x = __ldcs(vb + j);
+      ci[k].x = __ldcs(cb + j);
+    }
+  }
+  if (tid < T / 32) s_head[tid] = 0u;
+  __syncthreads();
+  // row offsets (chunk-relative, clamped) and the row-start marks, while the loads are in flight
+  for (int i = tid; i < c.nr || i < c.ncached; i += THREADS) {
+    int64_t d = (int64_t)pos[c.row0 + i] - c.c0;
+    d = d < 0 ? 0 : d;
+    const int rel = (int)(d > c.len ? c.len : d);
+    if (i < c.ncached) s_rel[i] = rel;
+    if (i < c.nr && rel < c.len) atomicOr(&s_head[rel >> 5], 1u << (rel & 31));
+  }
+  // gathers: entries past the chunk's end have val = 0 and crd = 0 (x[0] is a valid address when ncols > 0;
+  // the product is computed only for entries inside the chunk)
+  double2 xv[PAIRS];
+#pragma unroll
+  for (int k = 0; k < PAIRS; ++k) {
+    const int j = 2 * (tid + k * THREADS);
+    xv[k].x = (j < c.len) ? load_x(x + ci[k].x, policy, HINT) : 0.0;
+    xv[k].y = (j + 1 < c.len) ? load_x(x + ci[k].y, policy, HINT) : 0.0;
+  }
+  __syncthreads();  // the marks are complete
+
+  // ---- segmented inclusive scan of every 64-entry group, in registers ------------------------
+#pragma unroll
+  for (int k = 0; k < PAIRS; ++k) {
+    const int j = 2 * (tid + k * THREADS);
+    const double a = __dmul_rn(v[k].x, xv[k].x), b = __dmul_rn(v[k].y, xv[k].y);
+    const unsigned hw = s_head[j >> 5] >> (j & 31);
+    const bool h0 = hw & 1u, h1 = hw & 2u;
+    // t: the sum of the still open row piece at the end of this pair
+    double t = h1 ? b : __dadd_rn(a, b);
+    const unsigned heads = __ballot_sync(0xffffffffu, h0 || h1);
+    const unsigned below = heads & (0xffffffffu >> (31 - lane));
+    const int first = below ? 31 - __clz(below) : 0;  // nearest lane at or below this one whose pair holds a row start
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const double u = __shfl_up_sync(0xffffffffu, t, off);
+      if (lane - off >= first) t = __dadd_rn(t, u);
+    }
+    double before = __shfl_up_sync(0xffffffffu, t, 1);  // open piece at the end of the previous lane's pair
+    if (lane == 0) before = 0.0;
+    double2 s;
+    s.x = h0 ? a : __dadd_rn(before, a);
+    s.y = h1 ? b : __dadd_rn(s.x, b);
+    *reinterpret_cast<double2 *>(s_scan + j) = s;
+    if (lane == 31) s_tail[j >> 6] = s.y;
+  }
+  __syncthreads();
+
+  // ---- one thread per row: value at the row's last entry + tails of the earlier groups it spans ----
+  double dot_local = 0.0;
+  for (int i = tid; i < c.nr; i += THREADS) {
+    const int s = rel_at<I>(c, s_rel, pos, i), e = rel_at<I>(c, s_rel, pos, i + 1);
+    const bool is_tail = c.has_tail && i == c.nr - 1;
+    double yin = 0.0, dv = 0.0;
+    if (accumulate && !is_tail) yin = y[c.row0 + i];
+    if (FUSE_DOT) dv = dotvec[c.row0 + i];
+    double acc = 0.0;
+    if (e > s) {
+      const int g = (e - 1) >> 6;
+      for (int q = s >> 6; q < g; ++q) acc = __dadd_rn(acc, s_tail[q]);
+      acc = __dadd_rn(acc, s_scan[e - 1]);
+    }
+    finish_row<FUSE_DOT>(c, i, s, acc, yin, dv, y, carry, dot_local, chunk);
+  }
+
+  if (FUSE_DOT) {
+    const double t = block_sum(dot_local, s_red);
+    if (tid == 0) blk_partial[blockIdx.x] = t;
+  }
+}
 
 // ---------------------------------------------------------------------------
 // Persistent variant: each block walks chunks b, b + grid, ... and keeps the next
@@ -699,7 +842,8 @@ spmm_row_direct_kernel(const I *__restrict__ pos, const I *__restrict__ crd, con
 // ---------------------------------------------------------------------------
 // Host side
 // ---------------------------------------------------------------------------
-// Kernel variant: {threads, blocks per SM, L2 hint}.  threads > 0: one chunk per block;
+// Kernel variant: {threads, blocks per SM, L2 hint}.  threads >= 256: one chunk per block; threads == 2: the
+// segmented-scan chunk kernel (256 threads, minb blocks per SM); threads == 1: one thread per row;
 // threads < 0: the persistent bulk-copy kernel with |threads| threads.  Which one is faster
 // depends on the matrix (the persistent kernel wins when x is served from L1/L2, as for banded
 // matrices; the one-chunk kernel when the gathers of x dominate), so lapis_b200_csr_tune times
@@ -723,6 +867,7 @@ static SpmvVariant &spmv_override() {  // threads == 0: no override
 constexpr int SPMV_ROWTHREAD_MAX_LEN = 32;
 static bool spmv_variant_known(int threads, int minb) {
   if (threads == 1) return minb == 0;  // one thread per row
+  if (threads == 2) return minb >= 4 && minb <= 6;  // segmented-scan chunk kernel (256 threads), blocks per SM
   if (threads == -256 || threads == -512) return minb >= 1 && minb <= 8;
   return (threads == 256 && (minb == 4 || minb == 6)) || (threads == 512 && minb == 3 && SPMV_TILE >= 1024);
 }
@@ -739,6 +884,22 @@ static void launch_chunks(const lapis_b200_csr *h, const double *x, double *y, i
         skip_flag);
   else
     spmv_chunk_kernel<I, THREADS, MINB, false, HINT><<<(unsigned)h->nblk, THREADS, 0, st>>>(
+        pos, crd, h->val, h->blk_row, abase, nnz_end, h->nrows, x, y, accumulate, h->carry, nullptr, nullptr,
+        skip_flag);
+}
+
+template <typename I, int MINB, bool HINT>
+static void launch_scan(const lapis_b200_csr *h, const double *x, double *y, int accumulate, const double *dotvec,
+                        double *blk_partial, const int *skip_flag, cudaStream_t st) {
+  const I *pos = static_cast<const I *>(h->pos);
+  const I *crd = static_cast<const I *>(h->crd);
+  const int64_t abase = h->base & ~(int64_t)3, nnz_end = h->base + h->nnz;
+  if (dotvec != nullptr)
+    spmv_scan_kernel<I, MINB, true, HINT><<<(unsigned)h->nblk, 256, 0, st>>>(
+        pos, crd, h->val, h->blk_row, abase, nnz_end, h->nrows, x, y, accumulate, h->carry, dotvec, blk_partial,
+        skip_flag);
+  else
+    spmv_scan_kernel<I, MINB, false, HINT><<<(unsigned)h->nblk, 256, 0, st>>>(
         pos, crd, h->val, h->blk_row, abase, nnz_end, h->nrows, x, y, accumulate, h->carry, nullptr, nullptr,
         skip_flag);
 }
@@ -811,6 +972,18 @@ static int launch_spmv(const lapis_b200_csr *h, const double *x, double *y, int 
     else
       return fail(LAPIS_EBADARG, "LAPIS_B200_SPMV names an unknown kernel variant");
     LAPIS_TRY(rc);
+  } else if (v.threads == 2) {  // segmented-scan chunk kernel, minb = blocks per SM
+    if (v.minb == 6)
+      v.hint ? launch_scan<I, 6, true>(h, x, y, accumulate, dotvec, blk_partial, skip_flag, st)
+             : launch_scan<I, 6, false>(h, x, y, accumulate, dotvec, blk_partial, skip_flag, st);
+    else if (v.minb == 5)
+      v.hint ? launch_scan<I, 5, true>(h, x, y, accumulate, dotvec, blk_partial, skip_flag, st)
+             : launch_scan<I, 5, false>(h, x, y, accumulate, dotvec, blk_partial, skip_flag, st);
+    else if (v.minb == 4)
+      v.hint ? launch_scan<I, 4, true>(h, x, y, accumulate, dotvec, blk_partial, skip_flag, st)
+             : launch_scan<I, 4, false>(h, x, y, accumulate, dotvec, blk_partial, skip_flag, st);
+    else
+      return fail(LAPIS_EBADARG, "LAPIS_B200_SPMV names an unknown kernel variant");
   } else
 #define LAPIS_V(T, M)                                                                                     \
   if (v.threads == T && v.minb == M) {                                                                    \
@@ -1023,7 +1196,9 @@ extern "C" int lapis_b200_spmv_select_kernel(int threads, int blocks_per_sm, int
 }
 
 // Times the candidate kernels on this matrix (y = A x with scratch x = 0, y) and keeps the fastest.
-extern "C" int lapis_b200_csr_tune(lapis_b200_csr_t h, void *stream) {
+// relaxed: the segmented-scan kernel is a candidate too (row sums in scan order: within the 1e-12 bound of
+// the sequential sum, not the bits of the other variants).
+static int csr_tune_impl(lapis_b200_csr_t h, void *stream, bool relaxed) {
   clear_error();
   if (h == nullptr) return fail(LAPIS_EBADARG, "csr_tune: null matrix handle");
   if (h->nrows == 0 || h->nnz == 0) return LAPIS_OK;
@@ -1049,7 +1224,8 @@ extern "C" int lapis_b200_csr_tune(lapis_b200_csr_t h, void *stream) {
   }
   const int pipe_blocks = h->idx_bytes == 4 ? 4 : 3;  // what fits in shared memory
   const bool short_rows = h->max_row_len >= 0 && h->max_row_len <= SPMV_ROWTHREAD_MAX_LEN;
-  const SpmvVariant cand[] = {{256, 4, 1}, {256, 6, 1}, {512, 3, 1}, {-256, pipe_blocks, 1}, {1, 0, 1}};
+  const SpmvVariant cand[] = {{256, 4, 1}, {256, 6, 1}, {512, 3, 1}, {-256, pipe_blocks, 1}, {1, 0, 1},
+                              {2, 4, 1}, {2, 5, 1}, {2, 6, 1}};
   const SpmvVariant saved = spmv_override();
   cudaEvent_t e0, e1;
   cudaEventCreate(&e0);
@@ -1058,6 +1234,7 @@ extern "C" int lapis_b200_csr_tune(lapis_b200_csr_t h, void *stream) {
   int status = LAPIS_OK;
   for (const SpmvVariant &c : cand) {
     if (c.threads == 1 && !short_rows) continue;
+    if (c.threads == 2 && !relaxed) continue;
     if (!spmv_variant_known(c.threads, c.minb)) continue;
     spmv_override() = c;
     status = spmv_launch(h, x, y, 0, nullptr, nullptr, nullptr, st);  // warm-up
@@ -1085,6 +1262,9 @@ extern "C" int lapis_b200_csr_tune(lapis_b200_csr_t h, void *stream) {
   cudaFree(y);
   return status;
 }
+
+extern "C" int lapis_b200_csr_tune(lapis_b200_csr_t h, void *stream) { return csr_tune_impl(h, stream, false); }
+extern "C" int lapis_b200_csr_tune_relaxed(lapis_b200_csr_t h, void *stream) { return csr_tune_impl(h, stream, true); }
 
 extern "C" int lapis_b200_csr_tuned_kernel(lapis_b200_csr_t h, int *threads, int *blocks_per_sm) {
   if (h == nullptr) return LAPIS_EBADARG;

@@ -59,11 +59,14 @@ class CsrMatrix:
         if tune:
             self.tune()
 
-    def tune(self):
+    def tune(self, relaxed: bool = False):
         """Times the SpMV kernel candidates on this matrix and keeps the fastest; returns
-        (threads, blocks_per_sm) of the winner (negative threads: the persistent kernel)."""
+        (threads, blocks_per_sm) of the winner (negative threads: the persistent kernel).
+        ``relaxed=True`` adds the segmented-scan kernel (threads == 2), whose row sums agree with the
+        others to 1e-12 of the row's magnitude but not bit for bit."""
+        fn = self._lib.lapis_b200_csr_tune_relaxed if relaxed else self._lib.lapis_b200_csr_tune
         with torch.cuda.device(self.pos.device):
-            check(self._lib.lapis_b200_csr_tune(self._h, _stream()))
+            check(fn(self._h, _stream()))
         t, b = c_int(0), c_int(0)
         self._lib.lapis_b200_csr_tuned_kernel(self._h, ctypes.byref(t), ctypes.byref(b))
         return int(t.value), int(b.value)

@@ -67,7 +67,7 @@ def test_spmv_known_answer_through_backend(golden_dir):
     assert np.allclose(y, 2 * g["ycorrect"])
 
 
-@pytest.fixture(params=[(256, 4, 1), (-256, 3, 1), (-512, 2, 0)], ids=["chunk", "pipe256", "pipe512"])
+@pytest.fixture(params=[(256, 4, 1), (-256, 3, 1), (-512, 2, 0), (2, 4, 1)], ids=["chunk", "pipe256", "pipe512", "scan"])
 def spmv_kernel(request):
     """Runs the test once per SpMV kernel variant and restores the default afterwards."""
     from lapis_b200._lib import check, load
@@ -131,8 +131,9 @@ def test_spmv_matches_oracle(idx, case, spmv_kernel):
         A.spmv(xd, yd2, accumulate=accumulate)
         assert torch.equal(yd, yd2), "SpMV is not run-to-run deterministic"
     # rows of up to 32 entries inside one chunk of 2048 are summed in the CPU order: identical bits for all
-    # but the (at most one per chunk) rows cut by a chunk boundary
-    if case in ("uniform10", "empty_rows"):
+    # but the (at most one per chunk) rows cut by a chunk boundary (the segmented-scan kernel sums in scan
+    # order and is held to the tolerance above only)
+    if case in ("uniform10", "empty_rows") and spmv_kernel[0] != 2:
         yd = torch.as_tensor(y0).to(dev)
         A.spmv(xd, yd, accumulate=True)
         same = yd.cpu().numpy() == oracle.spmv(pos, crd, val, x, y0)
@@ -186,6 +187,31 @@ def test_spmv_tuning_keeps_the_bits():
         y1 = torch.zeros(n, dtype=torch.float64, device=dev)
         A.spmv(x, y1, accumulate=False)
         assert torch.equal(y0, y1)
+
+
+def test_spmv_relaxed_tuning_stays_within_the_tolerance():
+    """The relaxed tuner may also pick the segmented-scan kernel, which sums a row in scan order: the result
+    stays within the bound of the other SpMV tests and repeats bit for bit; any other pick keeps the bits."""
+    from lapis_b200.device import CsrMatrix
+    dev = _dev()
+    d = w.spmv_power_law(1 << 16, idx_dtype=np.int64)
+    pos, crd, val, x = d["pos"], d["crd"], d["val"], d["x"]
+    n = d["shape"][0]
+    xd = torch.as_tensor(x).to(dev)
+    A = CsrMatrix.from_host(pos, crd, val, (n, n), dev)
+    y0 = torch.zeros(n, dtype=torch.float64, device=dev)
+    A.spmv(xd, y0, accumulate=False)
+    threads, blocks = A.tune(relaxed=True)
+    assert (threads, blocks) in ((256, 4), (256, 6), (512, 3), (-256, 3), (-256, 4), (1, 0), (2, 4), (2, 5), (2, 6))
+    y1 = torch.zeros(n, dtype=torch.float64, device=dev)
+    A.spmv(xd, y1, accumulate=False)
+    y2 = torch.zeros(n, dtype=torch.float64, device=dev)
+    A.spmv(xd, y2, accumulate=False)
+    assert torch.equal(y1, y2)
+    if threads != 2:
+        assert torch.equal(y0, y1)
+    zero = np.zeros(n)
+    _assert_spmv_close(y1.cpu().numpy(), oracle.spmv(pos, crd, val, x, zero), _row_scale(pos, crd, val, x, zero))
 
 
 @pytest.mark.parametrize("idx", [np.int32, np.int64])
