@@ -347,7 +347,7 @@ def run_ours(args, d, rank, world, local_rank):
             xd = torch.as_tensor(d["x"]).to(dev)
             yd = torch.zeros(r1 - r0, dtype=torch.float64, device=dev)
             step = lambda: A.spmv(xd, yd, accumulate=False)
-            kernel_name = {2: "spmv_scan_kernel", 1: "spmv_rowthread_kernel"}.get(
+            kernel_name = {2: "spmv_scan_kernel", 3: "spmv_scan_kernel", 1: "spmv_rowthread_kernel"}.get(
                 extra_cfg_kernel[0], "spmv_pipe_kernel" if extra_cfg_kernel[0] < 0 else "spmv_chunk_kernel")
             host_in = [lpos, lcrd, lval, d["x"]]
             module = KB.KokkosBackend(decompose_tensors=True).compile(mm.spmv(mm.CSR64))

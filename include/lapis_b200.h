@@ -183,7 +183,8 @@ int lapis_b200_spmv_f64(lapis_b200_csr_t h, const double *d_x, double *d_y, int 
  * (and the launch honours it) only for matrices whose longest row has at most 32 entries -- up to there it
  * returns the same bits as the others -- and such matrices (stencils, bounded-degree graphs) are where it
  * wins.  On other matrices, and on handles that were never tuned, a request for it runs (256,4).
- * A fourth kind, threads = 2 with blocks_per_sm in {4, 5}, is the chunk kernel with the row sums done by a
+ * A fourth kind, threads = 2 (256 threads, blocks_per_sm in {4, 5}) or threads = 3 (512 threads,
+ * blocks_per_sm in {2, 3, 4}), is the chunk kernel with the row sums done by a
  * segmented scan in registers instead of one lane per row over shared memory (less shared-memory traffic
  * when the gathers of x already saturate L1).  It adds a row's products in scan order, so y agrees with the
  * other kernels to 1e-12 of the row's magnitude but not bit for bit; lapis_b200_csr_tune therefore leaves it

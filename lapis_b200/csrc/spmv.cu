@@ -18,6 +18,9 @@
 //     sequential CPU order (measured: more lanes per short row only add instructions),
 //     longer rows by a whole warp in a second pass, so one long row among short ones
 //     does not serialise a thread.
+//     A variant (spmv_scan_kernel) keeps the products in registers and sums the rows by a
+//     warp-level segmented scan instead; it is offered by the relaxed tuner only, because it
+//     adds a row's products in scan order.
 //   * A row that runs past the end of its chunk leaves its partial sum in carry[b];
 //     a tiny second kernel adds the carries to the row's y in chunk order.  No
 //     atomics on the data path: results are run-to-run identical.
@@ -294,15 +297,15 @@ spmv_chunk_kernel(const I *__restrict__ pos, const I *__restrict__ crd, const do
 // row's magnitude of the sequential sum, but not bit-identical to the other variants
 // (rows of a single entry and empty rows are).
 // ---------------------------------------------------------------------------
-template <typename I, int MINB, bool FUSE_DOT, bool HINT>
-__global__ void __launch_bounds__(256, MINB)
+template <typename I, int THREADS, int MINB, bool FUSE_DOT, bool HINT>
+__global__ void __launch_bounds__(THREADS, MINB)
 spmv_scan_kernel(const I *__restrict__ pos, const I *__restrict__ crd, const double *__restrict__ val,
                  const int64_t *__restrict__ plan, int64_t abase, int64_t nnz_end, int64_t nrows,
                  const double *__restrict__ x, double *__restrict__ y, int accumulate,
                  double *__restrict__ carry, const double *__restrict__ dotvec,
                  double *__restrict__ blk_partial, const int *__restrict__ skip_flag) {
-  constexpr int T = SPMV_TILE, THREADS = 256;
-  constexpr int PAIRS = T / (2 * THREADS);
+  constexpr int T = SPMV_TILE;
+  constexpr int PAIRS = T / (2 * THREADS);  // 256 threads: eight entries per thread; 512: four
   constexpr int NGROUPS = T / 64;  // group g = entries [64 g, 64 g + 64): the pairs one warp holds for one k
   static_assert(T % (2 * THREADS) == 0, "a chunk is a whole number of pairs per thread");
   __shared__ __align__(16) double s_scan[T];
@@ -842,8 +845,8 @@ spmm_row_direct_kernel(const I *__restrict__ pos, const I *__restrict__ crd, con
 // ---------------------------------------------------------------------------
 // Host side
 // ---------------------------------------------------------------------------
-// Kernel variant: {threads, blocks per SM, L2 hint}.  threads >= 256: one chunk per block; threads == 2: the
-// segmented-scan chunk kernel (256 threads, minb blocks per SM); threads == 1: one thread per row;
+// Kernel variant: {threads, blocks per SM, L2 hint}.  threads >= 256: one chunk per block; threads == 2 / 3: the
+// segmented-scan chunk kernel with 256 / 512 threads (minb blocks per SM); threads == 1: one thread per row;
 // threads < 0: the persistent bulk-copy kernel with |threads| threads.  Which one is faster
 // depends on the matrix (the persistent kernel wins when x is served from L1/L2, as for banded
 // matrices; the one-chunk kernel when the gathers of x dominate), so lapis_b200_csr_tune times
@@ -867,7 +870,8 @@ static SpmvVariant &spmv_override() {  // threads == 0: no override
 constexpr int SPMV_ROWTHREAD_MAX_LEN = 32;
 static bool spmv_variant_known(int threads, int minb) {
   if (threads == 1) return minb == 0;  // one thread per row
-  if (threads == 2) return minb >= 4 && minb <= 6;  // segmented-scan chunk kernel (256 threads), blocks per SM
+  if (threads == 2) return minb == 4 || minb == 5;  // segmented-scan chunk kernel, 256 threads, blocks per SM
+  if (threads == 3) return minb >= 2 && minb <= 4 && SPMV_TILE >= 1024;  // the same with 512 threads
   if (threads == -256 || threads == -512) return minb >= 1 && minb <= 8;
   return (threads == 256 && (minb == 4 || minb == 6)) || (threads == 512 && minb == 3 && SPMV_TILE >= 1024);
 }
@@ -888,18 +892,18 @@ static void launch_chunks(const lapis_b200_csr *h, const double *x, double *y, i
         skip_flag);
 }
 
-template <typename I, int MINB, bool HINT>
+template <typename I, int THREADS, int MINB, bool HINT>
 static void launch_scan(const lapis_b200_csr *h, const double *x, double *y, int accumulate, const double *dotvec,
                         double *blk_partial, const int *skip_flag, cudaStream_t st) {
   const I *pos = static_cast<const I *>(h->pos);
   const I *crd = static_cast<const I *>(h->crd);
   const int64_t abase = h->base & ~(int64_t)3, nnz_end = h->base + h->nnz;
   if (dotvec != nullptr)
-    spmv_scan_kernel<I, MINB, true, HINT><<<(unsigned)h->nblk, 256, 0, st>>>(
+    spmv_scan_kernel<I, THREADS, MINB, true, HINT><<<(unsigned)h->nblk, THREADS, 0, st>>>(
         pos, crd, h->val, h->blk_row, abase, nnz_end, h->nrows, x, y, accumulate, h->carry, dotvec, blk_partial,
         skip_flag);
   else
-    spmv_scan_kernel<I, MINB, false, HINT><<<(unsigned)h->nblk, 256, 0, st>>>(
+    spmv_scan_kernel<I, THREADS, MINB, false, HINT><<<(unsigned)h->nblk, THREADS, 0, st>>>(
         pos, crd, h->val, h->blk_row, abase, nnz_end, h->nrows, x, y, accumulate, h->carry, nullptr, nullptr,
         skip_flag);
 }
@@ -972,18 +976,23 @@ static int launch_spmv(const lapis_b200_csr *h, const double *x, double *y, int 
     else
       return fail(LAPIS_EBADARG, "LAPIS_B200_SPMV names an unknown kernel variant");
     LAPIS_TRY(rc);
-  } else if (v.threads == 2) {  // segmented-scan chunk kernel, minb = blocks per SM
-    if (v.minb == 6)
-      v.hint ? launch_scan<I, 6, true>(h, x, y, accumulate, dotvec, blk_partial, skip_flag, st)
-             : launch_scan<I, 6, false>(h, x, y, accumulate, dotvec, blk_partial, skip_flag, st);
-    else if (v.minb == 5)
-      v.hint ? launch_scan<I, 5, true>(h, x, y, accumulate, dotvec, blk_partial, skip_flag, st)
-             : launch_scan<I, 5, false>(h, x, y, accumulate, dotvec, blk_partial, skip_flag, st);
-    else if (v.minb == 4)
-      v.hint ? launch_scan<I, 4, true>(h, x, y, accumulate, dotvec, blk_partial, skip_flag, st)
-             : launch_scan<I, 4, false>(h, x, y, accumulate, dotvec, blk_partial, skip_flag, st);
-    else
-      return fail(LAPIS_EBADARG, "LAPIS_B200_SPMV names an unknown kernel variant");
+  } else if (v.threads == 2 || v.threads == 3) {  // segmented-scan chunk kernel with 256 / 512 threads
+#define LAPIS_S(T, M)                                                                                     \
+  if ((v.threads == 2 ? 256 : 512) == T && v.minb == M) {                                                 \
+    if (v.hint)                                                                                           \
+      launch_scan<I, T, M, true>(h, x, y, accumulate, dotvec, blk_partial, skip_flag, st);                \
+    else                                                                                                  \
+      launch_scan<I, T, M, false>(h, x, y, accumulate, dotvec, blk_partial, skip_flag, st);               \
+  } else
+    LAPIS_S(256, 4)
+    LAPIS_S(256, 5)
+#if LAPIS_SPMV_TILE >= 1024
+    LAPIS_S(512, 2)
+    LAPIS_S(512, 3)
+    LAPIS_S(512, 4)
+#endif
+    { return fail(LAPIS_EBADARG, "LAPIS_B200_SPMV names an unknown kernel variant"); }
+#undef LAPIS_S
   } else
 #define LAPIS_V(T, M)                                                                                     \
   if (v.threads == T && v.minb == M) {                                                                    \
@@ -1225,7 +1234,7 @@ static int csr_tune_impl(lapis_b200_csr_t h, void *stream, bool relaxed) {
   const int pipe_blocks = h->idx_bytes == 4 ? 4 : 3;  // what fits in shared memory
   const bool short_rows = h->max_row_len >= 0 && h->max_row_len <= SPMV_ROWTHREAD_MAX_LEN;
   const SpmvVariant cand[] = {{256, 4, 1}, {256, 6, 1}, {512, 3, 1}, {-256, pipe_blocks, 1}, {1, 0, 1},
-                              {2, 4, 1}, {2, 5, 1}, {2, 6, 1}};
+                              {2, 5, 1}, {2, 5, 0}, {3, 4, 1}, {3, 4, 0}};
   const SpmvVariant saved = spmv_override();
   cudaEvent_t e0, e1;
   cudaEventCreate(&e0);
@@ -1234,7 +1243,7 @@ static int csr_tune_impl(lapis_b200_csr_t h, void *stream, bool relaxed) {
   int status = LAPIS_OK;
   for (const SpmvVariant &c : cand) {
     if (c.threads == 1 && !short_rows) continue;
-    if (c.threads == 2 && !relaxed) continue;
+    if ((c.threads == 2 || c.threads == 3) && !relaxed) continue;
     if (!spmv_variant_known(c.threads, c.minb)) continue;
     spmv_override() = c;
     status = spmv_launch(h, x, y, 0, nullptr, nullptr, nullptr, st);  // warm-up

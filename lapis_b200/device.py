@@ -62,7 +62,7 @@ class CsrMatrix:
     def tune(self, relaxed: bool = False):
         """Times the SpMV kernel candidates on this matrix and keeps the fastest; returns
         (threads, blocks_per_sm) of the winner (negative threads: the persistent kernel).
-        ``relaxed=True`` adds the segmented-scan kernel (threads == 2), whose row sums agree with the
+        ``relaxed=True`` adds the segmented-scan kernel (threads == 2 or 3), whose row sums agree with the
         others to 1e-12 of the row's magnitude but not bit for bit."""
         fn = self._lib.lapis_b200_csr_tune_relaxed if relaxed else self._lib.lapis_b200_csr_tune
         with torch.cuda.device(self.pos.device):
