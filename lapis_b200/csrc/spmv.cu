@@ -609,6 +609,263 @@ spmv_pipe_kernel(const I *__restrict__ pos, const I *__restrict__ crd, const dou
   }
 }
 
+// ---------------------------------------------------------------------------
+// Warp-walk variant: no shared memory, no block barrier.
+//
+// What bounds an SpMV whose columns are spread over a vector much larger than L1 is the load/store path of
+// the SM, not HBM: every gathered x element is its own request from L1 to the crossbar (one per cycle per SM),
+// and the number of such misses in flight is proportional to the L1 capacity, which every kilobyte of shared
+// memory takes away.  A store-free dot product over the same arrays (the floor) runs 1.4x slower with 64 KB of
+// shared memory per SM carved out and 4.5x slower with 192 KB.  So this kernel keeps everything in registers:
+//
+//   * One warp owns one chunk of the plan (2048 stored entries) and walks it in steps of 128 entries; a lane
+//     holds four consecutive entries, fetched with one 32-byte load per array (marked evict-first in L1 and
+//     L2), and the next step's entries are requested before the current step's gathers are consumed.
+//   * The row ends inside a step come from pos: lane i looks at row r_cur + i, a ballot counts the rows that
+//     end in the step, and four warp OR-reductions build the 128-bit mask of row-start offsets.
+//   * Products are summed by a segmented scan: sequentially inside a lane, five shuffle levels across lanes.
+//     The running sum of the row that is still open leaves the step on the scan's last shuffle (a rotation)
+//     and enters the next step in lane 0's first product.
+//   * A row is stored by the lane that holds its last entry; its row number is r_cur plus the number of row
+//     ends before that entry (popcounts of the mask).  Steps that contain empty rows cannot rank rows that
+//     way and fetch each row's sum with indexed shuffles instead.
+//   * The piece of a row that runs past the chunk goes to carry[chunk]; spmv_fixup_kernel adds the carries.
+//
+// Rows are summed in scan order: run-to-run identical, within 1e-12 of the row's magnitude of the sequential
+// sum, not the bits of the chunk kernels (relaxed tuner only).  val and crd must be 32-byte aligned.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void load_stream_256(const void *p, uint64_t &a, uint64_t &b, uint64_t &c, uint64_t &d) {
+  asm volatile("ld.global.nc.L1::evict_first.L2::evict_first.v4.b64 {%0,%1,%2,%3}, [%4];"
+               : "=l"(a), "=l"(b), "=l"(c), "=l"(d)
+               : "l"(p));
+}
+__device__ __forceinline__ void load_entries4(const int64_t *crd, const double *val, int64_t j, int64_t c[4], double a[4]) {
+  uint64_t q0, q1, q2, q3, v0, v1, v2, v3;
+  load_stream_256(crd + j, q0, q1, q2, q3);
+  load_stream_256(val + j, v0, v1, v2, v3);
+  c[0] = (int64_t)q0; c[1] = (int64_t)q1; c[2] = (int64_t)q2; c[3] = (int64_t)q3;
+  a[0] = __longlong_as_double((long long)v0); a[1] = __longlong_as_double((long long)v1);
+  a[2] = __longlong_as_double((long long)v2); a[3] = __longlong_as_double((long long)v3);
+}
+__device__ __forceinline__ void load_entries4(const int32_t *crd, const double *val, int64_t j, int64_t c[4], double a[4]) {
+  uint64_t v0, v1, v2, v3;
+  const int4 q = __ldcs(reinterpret_cast<const int4 *>(crd + j));
+  load_stream_256(val + j, v0, v1, v2, v3);
+  c[0] = q.x; c[1] = q.y; c[2] = q.z; c[3] = q.w;
+  a[0] = __longlong_as_double((long long)v0); a[1] = __longlong_as_double((long long)v1);
+  a[2] = __longlong_as_double((long long)v2); a[3] = __longlong_as_double((long long)v3);
+}
+__device__ __forceinline__ double load_x_ordered(const double *p) {  // volatile: stays behind the loads issued before it
+  double v;
+  asm volatile("ld.global.nc.f64 %0, [%1];" : "=d"(v) : "l"(p));
+  return v;
+}
+
+constexpr int SPMV_WALK_THREADS = 128;
+constexpr int SPMV_WALK_STEP = 128;  // entries per step: four per lane
+
+template <typename I, bool FUSE_DOT>
+__global__ void __launch_bounds__(SPMV_WALK_THREADS, FUSE_DOT ? 6 : 8)
+spmv_walk_kernel(const I *__restrict__ pos, const I *__restrict__ crd, const double *__restrict__ val,
+                 const int64_t *__restrict__ plan, int64_t abase, int64_t base, int64_t nnz_end, int64_t nrows,
+                 int64_t nblk, const double *__restrict__ x, double *__restrict__ y, int accumulate,
+                 double *__restrict__ carry, const double *__restrict__ dotvec, double *__restrict__ blk_partial,
+                 const int *__restrict__ skip_flag) {
+  constexpr unsigned FULL = 0xffffffffu;
+  constexpr int S = SPMV_WALK_STEP;
+  asm volatile("griddepcontrol.launch_dependents;");
+  if (skip_flag != nullptr && *skip_flag != 0) return;
+  const int lane = threadIdx.x & 31;
+  const int64_t w = (int64_t)blockIdx.x * (SPMV_WALK_THREADS / 32) + (threadIdx.x >> 5);
+  if (w >= nblk) return;
+  const int64_t c_begin = abase + w * SPMV_TILE;
+  const int64_t c_end = (c_begin + SPMV_TILE < nnz_end) ? c_begin + SPMV_TILE : nnz_end;
+  int64_t r_cur = plan[w];
+  double open = 0.0;  // sum so far of the row that is still open; meaningful in lane 0
+  double dot_local = 0.0;
+  const int wsel = lane >> 3, shift = 4 * (lane & 7);
+
+  auto fetch = [&](int64_t c, int64_t cc[4], double aa[4]) {
+    const int64_t j0 = c + 4 * lane;
+    if (j0 + 4 <= c_end) {
+      load_entries4(crd, val, j0, cc, aa);
+    } else {  // ragged end of the arrays
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        cc[k] = 0;
+        aa[k] = 0.0;
+        if (j0 + k < c_end) {
+          cc[k] = (int64_t)crd[j0 + k];
+          aa[k] = val[j0 + k];
+        }
+      }
+    }
+  };
+  // row-end offset of row r relative to c, S + 1 for "beyond this step"
+  auto end_offset = [&](int64_t r, int64_t c) {
+    int e = S + 1;
+    if (r < nrows) {
+      const int64_t d = (int64_t)pos[r + 1] - c;
+      e = d > S ? S + 1 : (d < 0 ? 0 : (int)d);
+    }
+    return e;
+  };
+
+  if (c_begin >= c_end) {  // a matrix without stored entries (one chunk, one warp): every row is empty
+    if (!accumulate)
+      for (int64_t r = lane; r < nrows; r += 32) y[r] = 0.0;
+    if (lane == 0) {
+      carry[w] = 0.0;
+      if (FUSE_DOT) blk_partial[w] = 0.0;
+    }
+    return;
+  }
+  int64_t cn[4];
+  double an[4];
+  fetch(c_begin, cn, an);
+
+  for (int64_t c = c_begin; c < c_end; c += S) {
+    int64_t ci[4];
+    double a[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      ci[k] = cn[k];
+      a[k] = an[k];
+    }
+    const int e = end_offset(r_cur + lane, c);
+    double xv[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) xv[k] = load_x_ordered(x + ci[k]);
+    if (c + S < c_end) fetch(c + S, cn, an);
+
+    // ---- rows that end in this step; bit e of the mask for every end offset e < S ------------------
+    int nfin = __popc(__ballot_sync(FULL, e <= S));
+    unsigned any_full = __ballot_sync(FULL, e == S);
+    unsigned hm0, hm1, hm2, hm3;
+    {
+      const unsigned bit = (e < S) ? (1u << (e & 31)) : 0u;
+      const int q = e >> 5;
+      hm0 = __reduce_or_sync(FULL, q == 0 ? bit : 0u);
+      hm1 = __reduce_or_sync(FULL, q == 1 ? bit : 0u);
+      hm2 = __reduce_or_sync(FULL, q == 2 ? bit : 0u);
+      hm3 = __reduce_or_sync(FULL, q == 3 ? bit : 0u);
+    }
+    int total_fin = nfin;
+    for (int64_t rbase = r_cur + 32; nfin == 32; rbase += 32) {  // more than 32 rows may end in one step
+      const int e2 = end_offset(rbase + lane, c);
+      nfin = __popc(__ballot_sync(FULL, e2 <= S));
+      any_full |= __ballot_sync(FULL, e2 == S);
+      total_fin += nfin;
+      const unsigned bit = (e2 < S) ? (1u << (e2 & 31)) : 0u;
+      const int q = e2 >> 5;
+      hm0 |= __reduce_or_sync(FULL, q == 0 ? bit : 0u);
+      hm1 |= __reduce_or_sync(FULL, q == 1 ? bit : 0u);
+      hm2 |= __reduce_or_sync(FULL, q == 2 ? bit : 0u);
+      hm3 |= __reduce_or_sync(FULL, q == 3 ? bit : 0u);
+    }
+    const unsigned hcur = wsel == 0 ? hm0 : (wsel == 1 ? hm1 : (wsel == 2 ? hm2 : hm3));
+    const unsigned hnext = wsel == 0 ? hm1 : (wsel == 1 ? hm2 : (wsel == 2 ? hm3 : (any_full ? 1u : 0u)));
+    const unsigned h5 = __funnelshift_r(hcur, hnext, shift) & 0x1fu;  // mask bits 4*lane .. 4*lane + 4
+    const unsigned h = h5 & 0xfu;                                     // a row starts at this lane's entry k
+    const int p0 = __popc(hm0), p1 = p0 + __popc(hm1), p2 = p1 + __popc(hm2);
+    const int distinct = p2 + __popc(hm3) + (any_full ? 1 : 0);
+    // every finished row has its own end offset and none ends at offset 0: no empty rows among them
+    const bool simple = (distinct == total_fin) && !(hm0 & 1u);
+    // rows that end at or before this lane's first entry
+    const int below = (wsel == 0 ? 0 : (wsel == 1 ? p0 : (wsel == 2 ? p1 : p2))) + __popc(hcur & ((2u << shift) - 1u));
+
+    double yin[4] = {0.0, 0.0, 0.0, 0.0}, dv[4] = {0.0, 0.0, 0.0, 0.0};
+    if (simple) {
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        if (h5 & (2u << k)) {
+          const int64_t row = r_cur + below + __popc(h & (((2u << k) - 1u) & ~1u));
+          if (accumulate) yin[k] = y[row];
+          if (FUSE_DOT) dv[k] = dotvec[row];
+        }
+    }
+
+    // ---- segmented scan ----------------------------------------------------------------------------
+    double p[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) p[k] = __dmul_rn(a[k], xv[k]);
+    if (c < base || c + S > c_end) {
+      // the chunks start on a multiple of four entries, up to three in front of pos[0]; the last step may reach
+      // past the arrays' end: neither kind of slot belongs to a row
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int64_t j = c + 4 * lane + k;
+        if (j < base || j >= c_end) p[k] = 0.0;
+      }
+    }
+    if (lane == 0 && !(h & 1u)) p[0] = __dadd_rn(open, p[0]);
+    double t = p[0];
+    t = (h & 2u) ? p[1] : __dadd_rn(t, p[1]);
+    t = (h & 4u) ? p[2] : __dadd_rn(t, p[2]);
+    t = (h & 8u) ? p[3] : __dadd_rn(t, p[3]);
+    const unsigned heads = __ballot_sync(FULL, h != 0u);
+    const unsigned at_or_below = heads & (0xffffffffu >> (31 - lane));
+    const int first = at_or_below ? 31 - __clz(at_or_below) : 0;  // nearest lane at or below this one with a row start
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const double u = __shfl_up_sync(FULL, t, off);
+      if (lane - off >= first) t = __dadd_rn(t, u);
+    }
+    // lane l receives the open piece at the end of lane l - 1; lane 0 receives lane 31's: the step's open piece
+    const double rot = __shfl_sync(FULL, t, (lane + 31) & 31);
+    const double before = lane == 0 ? 0.0 : rot;
+    double s[4];
+    s[0] = (h & 1u) ? p[0] : __dadd_rn(before, p[0]);
+    s[1] = (h & 2u) ? p[1] : __dadd_rn(s[0], p[1]);
+    s[2] = (h & 4u) ? p[2] : __dadd_rn(s[1], p[2]);
+    s[3] = (h & 8u) ? p[3] : __dadd_rn(s[2], p[3]);
+    open = any_full ? 0.0 : rot;  // a row that ends with the step leaves nothing open
+
+    if (simple) {
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        if (h5 & (2u << k)) {  // entry k is the last entry of its row
+          const int64_t row = r_cur + below + __popc(h & (((2u << k) - 1u) & ~1u));
+          y[row] = __dadd_rn(s[k], yin[k]);
+          if (FUSE_DOT) dot_local = __dadd_rn(dot_local, __dmul_rn(s[k], dv[k]));
+        }
+    } else {
+      int prev_e = 0;
+      int64_t rbase = r_cur;
+      for (int done = 0; done < total_fin; done += 32, rbase += 32) {
+        const int re = done == 0 ? e : end_offset(rbase + lane, c);
+        int st = __shfl_up_sync(FULL, re, 1);  // where this lane's row starts = where the previous row ends
+        if (lane == 0) st = prev_e;
+        const bool finished = re <= S;
+        const int idx = finished && re > 0 ? re - 1 : 0;
+        const int src = idx >> 2, kk = idx & 3;
+        const double v0 = __shfl_sync(FULL, s[0], src), v1 = __shfl_sync(FULL, s[1], src);
+        const double v2 = __shfl_sync(FULL, s[2], src), v3 = __shfl_sync(FULL, s[3], src);
+        if (finished) {
+          double sum = kk == 0 ? v0 : (kk == 1 ? v1 : (kk == 2 ? v2 : v3));
+          if (re <= st) sum = 0.0;  // an empty row
+          const int64_t row = rbase + lane;
+          const double yi = accumulate ? y[row] : 0.0;
+          y[row] = __dadd_rn(sum, yi);
+          if (FUSE_DOT) dot_local = __dadd_rn(dot_local, __dmul_rn(sum, dotvec[row]));
+        }
+        prev_e = __shfl_sync(FULL, re, 31);
+      }
+    }
+    r_cur += total_fin;
+  }
+  if (lane == 0) {
+    const bool has_tail = r_cur < nrows && c_end < nnz_end;  // row r_cur runs past this chunk (or starts at its end: open == 0)
+    carry[w] = has_tail ? open : 0.0;
+    if (FUSE_DOT && has_tail) dot_local = __dadd_rn(dot_local, __dmul_rn(open, dotvec[r_cur]));
+  }
+  if (FUSE_DOT) {
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) dot_local = __dadd_rn(dot_local, __shfl_xor_sync(FULL, dot_local, off));
+    if (lane == 0) blk_partial[w] = dot_local;
+  }
+}
+
 template <typename I>
 constexpr int spmv_pipe_smem_bytes(int threads) {
   return 2 * SPMV_TILE * 8 + 2 * SPMV_TILE * (int)sizeof(I) + (SPMV_POS_CACHE + 2) * 4 + (SPMV_TILE / SPMV_LONG_ROW) * 4 +
@@ -873,6 +1130,7 @@ static SpmvVariant &spmv_override() {  // threads == 0: no override
 constexpr int SPMV_ROWTHREAD_MAX_LEN = 32;
 static bool spmv_variant_known(int threads, int minb) {
   if (threads == 1) return minb == 0;  // one thread per row
+  if (threads == 4) return minb == 0;  // one warp per chunk, no shared memory
   if (threads == 2) return minb == 4 || minb == 5;  // segmented-scan chunk kernel, 256 threads, blocks per SM
   if (threads == 3) return minb >= 2 && minb <= 4 && SPMV_TILE >= 1024;  // the same with 512 threads
   if (threads == -256 || threads == -512) return minb >= 1 && minb <= 8;
@@ -968,7 +1226,25 @@ static int launch_spmv(const lapis_b200_csr *h, const double *x, double *y, int 
     }
     v = SPMV_DEFAULT;
   }
-  if (v.threads < 0) {  // persistent bulk-copy kernel: threads = -256 or -512, minb = blocks per SM
+  if (v.threads == 4) {
+    // one warp per chunk: its 32-byte loads need val and crd 32-byte aligned; otherwise the default kernel runs
+    if (((reinterpret_cast<uintptr_t>(h->val) | reinterpret_cast<uintptr_t>(h->crd)) & 31) != 0) v = SPMV_DEFAULT;
+  }
+  if (v.threads == 4) {
+    const I *pos = static_cast<const I *>(h->pos);
+    const I *crd = static_cast<const I *>(h->crd);
+    const int64_t abase = h->base & ~(int64_t)3, nnz_end = h->base + h->nnz;
+    constexpr int WPB = SPMV_WALK_THREADS / 32;
+    const unsigned grid = (unsigned)((h->nblk + WPB - 1) / WPB);
+    if (dotvec != nullptr)
+      spmv_walk_kernel<I, true><<<grid, SPMV_WALK_THREADS, 0, st>>>(pos, crd, h->val, h->blk_row, abase, h->base, nnz_end,
+                                                                    h->nrows, h->nblk, x, y, accumulate, h->carry, dotvec,
+                                                                    blk_partial, skip_flag);
+    else
+      spmv_walk_kernel<I, false><<<grid, SPMV_WALK_THREADS, 0, st>>>(pos, crd, h->val, h->blk_row, abase, h->base, nnz_end,
+                                                                     h->nrows, h->nblk, x, y, accumulate, h->carry, nullptr,
+                                                                     nullptr, skip_flag);
+  } else if (v.threads < 0) {  // persistent bulk-copy kernel: threads = -256 or -512, minb = blocks per SM
     int rc;
     if (v.threads == -256)
       rc = v.hint ? launch_pipe<I, 256, true>(h, v.minb, x, y, accumulate, dotvec, blk_partial, skip_flag, st)
@@ -1237,7 +1513,7 @@ static int csr_tune_impl(lapis_b200_csr_t h, void *stream, bool relaxed) {
   const int pipe_blocks = h->idx_bytes == 4 ? 4 : 3;  // what fits in shared memory
   const bool short_rows = h->max_row_len >= 0 && h->max_row_len <= SPMV_ROWTHREAD_MAX_LEN;
   const SpmvVariant cand[] = {{256, 4, 1}, {256, 6, 1}, {512, 3, 1}, {-256, pipe_blocks, 1}, {1, 0, 1},
-                              {2, 5, 1}, {2, 5, 0}, {3, 4, 1}, {3, 4, 0}};
+                              {2, 5, 1}, {2, 5, 0}, {3, 4, 1}, {3, 4, 0}, {4, 0, 0}};
   const SpmvVariant saved = spmv_override();
   cudaEvent_t e0, e1;
   cudaEventCreate(&e0);
@@ -1246,7 +1522,8 @@ static int csr_tune_impl(lapis_b200_csr_t h, void *stream, bool relaxed) {
   int status = LAPIS_OK;
   for (const SpmvVariant &c : cand) {
     if (c.threads == 1 && !short_rows) continue;
-    if ((c.threads == 2 || c.threads == 3) && !relaxed) continue;
+    if ((c.threads == 2 || c.threads == 3 || c.threads == 4) && !relaxed) continue;
+    if (c.threads == 4 && ((reinterpret_cast<uintptr_t>(h->val) | reinterpret_cast<uintptr_t>(h->crd)) & 31) != 0) continue;
     if (!spmv_variant_known(c.threads, c.minb)) continue;
     spmv_override() = c;
     status = spmv_launch(h, x, y, 0, nullptr, nullptr, nullptr, st);  // warm-up

@@ -67,8 +67,8 @@ def test_spmv_known_answer_through_backend(golden_dir):
     assert np.allclose(y, 2 * g["ycorrect"])
 
 
-@pytest.fixture(params=[(256, 4, 1), (-256, 3, 1), (-512, 2, 0), (2, 4, 1), (3, 4, 0)],
-                ids=["chunk", "pipe256", "pipe512", "scan", "scan512"])
+@pytest.fixture(params=[(256, 4, 1), (-256, 3, 1), (-512, 2, 0), (2, 4, 1), (3, 4, 0), (4, 0, 0)],
+                ids=["chunk", "pipe256", "pipe512", "scan", "scan512", "walk"])
 def spmv_kernel(request):
     """Runs the test once per SpMV kernel variant and restores the default afterwards."""
     from lapis_b200._lib import check, load
@@ -132,9 +132,9 @@ def test_spmv_matches_oracle(idx, case, spmv_kernel):
         A.spmv(xd, yd2, accumulate=accumulate)
         assert torch.equal(yd, yd2), "SpMV is not run-to-run deterministic"
     # rows of up to 32 entries inside one chunk of 2048 are summed in the CPU order: identical bits for all
-    # but the (at most one per chunk) rows cut by a chunk boundary (the segmented-scan kernel sums in scan
-    # order and is held to the tolerance above only)
-    if case in ("uniform10", "empty_rows") and spmv_kernel[0] not in (2, 3):
+    # but the (at most one per chunk) rows cut by a chunk boundary (the segmented-scan and warp-walk kernels sum
+    # in scan order and are held to the tolerance above only)
+    if case in ("uniform10", "empty_rows") and spmv_kernel[0] not in (2, 3, 4):
         yd = torch.as_tensor(y0).to(dev)
         A.spmv(xd, yd, accumulate=True)
         same = yd.cpu().numpy() == oracle.spmv(pos, crd, val, x, y0)
@@ -147,12 +147,17 @@ def test_spmv_matches_oracle(idx, case, spmv_kernel):
         assert np.array_equal(yd.cpu().numpy()[short], oracle.spmv(pos, crd, val, x, y0)[short])
 
 
-def test_spmv_random_shapes_property():
+@pytest.mark.parametrize("forced", [None, (4, 0, 0)], ids=["default", "walk"])
+def test_spmv_random_shapes_property(forced):
     """Random small CSR shapes (hypothesis): empty rows, rows longer than a warp's threshold, rows cut by the
-    2048-entry chunk boundary, ncols == 1, int32 and int64 -- all against the oracle."""
+    2048-entry chunk boundary, ncols == 1, int32 and int64 -- all against the oracle; once with the default
+    kernel and once with the warp-walk kernel forced."""
     from hypothesis import given, settings, strategies as st
+    from lapis_b200._lib import check, load
     from lapis_b200.device import CsrMatrix
     dev = _dev()
+    if forced is not None:
+        check(load().lapis_b200_spmv_select_kernel(*forced))
 
     @settings(max_examples=40, deadline=None)
     @given(lens=st.lists(st.one_of(st.integers(0, 6), st.integers(0, 90), st.just(2500)), min_size=1, max_size=400),
@@ -170,7 +175,10 @@ def test_spmv_random_shapes_property():
         y_in = y0 if acc else np.zeros(len(lens))
         _assert_spmv_close(yd.cpu().numpy(), oracle.spmv(pos, crd, val, x, y_in), _row_scale(pos, crd, val, x, y_in))
 
-    run()
+    try:
+        run()
+    finally:
+        check(load().lapis_b200_spmv_select_kernel(0, 0, 0))
 
 
 def test_spmv_tuning_keeps_the_bits():
@@ -191,7 +199,7 @@ def test_spmv_tuning_keeps_the_bits():
 
 
 def test_spmv_relaxed_tuning_stays_within_the_tolerance():
-    """The relaxed tuner may also pick the segmented-scan kernel, which sums a row in scan order: the result
+    """The relaxed tuner may also pick the segmented-scan or the warp-walk kernel, which sum a row in scan order: the result
     stays within the bound of the other SpMV tests and repeats bit for bit; any other pick keeps the bits."""
     from lapis_b200.device import CsrMatrix
     dev = _dev()
@@ -203,13 +211,13 @@ def test_spmv_relaxed_tuning_stays_within_the_tolerance():
     y0 = torch.zeros(n, dtype=torch.float64, device=dev)
     A.spmv(xd, y0, accumulate=False)
     threads, blocks = A.tune(relaxed=True)
-    assert (threads, blocks) in ((256, 4), (256, 6), (512, 3), (-256, 3), (-256, 4), (1, 0), (2, 4), (2, 5), (3, 3), (3, 4))
+    assert (threads, blocks) in ((256, 4), (256, 6), (512, 3), (-256, 3), (-256, 4), (1, 0), (2, 4), (2, 5), (3, 3), (3, 4), (4, 0))
     y1 = torch.zeros(n, dtype=torch.float64, device=dev)
     A.spmv(xd, y1, accumulate=False)
     y2 = torch.zeros(n, dtype=torch.float64, device=dev)
     A.spmv(xd, y2, accumulate=False)
     assert torch.equal(y1, y2)
-    if threads not in (2, 3):
+    if threads not in (2, 3, 4):
         assert torch.equal(y0, y1)
     zero = np.zeros(n)
     _assert_spmv_close(y1.cpu().numpy(), oracle.spmv(pos, crd, val, x, zero), _row_scale(pos, crd, val, x, zero))
@@ -286,41 +294,76 @@ def test_spmv_row_block_in_place(spmv_kernel):
     _assert_spmv_close(yd.cpu().numpy(), ref[r0:r1], scale)
 
 
-def test_spmv_full_size_properties():
-    """Config 2 at full size (2^23 rows, ~1.34e8 entries): linearity and a row-sum identity,
-    which need no CPU pass over the whole matrix."""
+@pytest.fixture(scope="module")
+def config2_full():
+    """Config 2 at full size (2^23 rows, ~1.34e8 entries, int64 indices) on the device, with the host-side
+    quantities the size-independent checks need (computed once for all kernel variants)."""
     from lapis_b200.device import CsrMatrix
     dev = _dev()
     d = w.spmv_power_law()
     pos, crd, val, x = d["pos"], d["crd"], d["val"], d["x"]
     n = len(pos) - 1
+    starts = pos[:-1].astype(np.int64)
+    ref = {
+        "absum_x": np.add.reduceat(np.abs(val * x[crd]), starts),
+        "rowsum": np.add.reduceat(val, starts),
+        "absum": np.add.reduceat(np.abs(val), starts),
+        "rows": np.random.default_rng(5).integers(0, n, 2000),
+    }
+    ref["sample"] = np.array([
+        oracle.spmv(np.array([0, int(pos[r + 1] - pos[r])], dtype=np.int64), crd[pos[r]:pos[r + 1]], val[pos[r]:pos[r + 1]], x,
+                    np.zeros(1))[0] for r in ref["rows"]])
     A = CsrMatrix.from_host(pos, crd, val, (n, n), dev)
-    xd = torch.as_tensor(x).to(dev)
-    y1 = torch.zeros(n, dtype=torch.float64, device=dev)
-    A.spmv(xd, y1, accumulate=False)
-    # A(2x) = 2 A x exactly (scaling by 2 is exact in binary floating point)
-    y2 = torch.zeros(n, dtype=torch.float64, device=dev)
-    A.spmv(2.0 * xd, y2, accumulate=False)
-    assert torch.equal(y2, 2.0 * y1)
-    # accumulate: y1 + A x == 2 A x up to the rounding of the final adds
-    y3 = y1.clone()
-    A.spmv(xd, y3, accumulate=True)
-    absum_x = np.add.reduceat(np.abs(val * x[crd]), pos[:-1].astype(np.int64))
-    assert np.all(np.abs((y3 - 2.0 * y1).cpu().numpy()) <= TOL_F64 * absum_x)
-    # x = 1: y = row sums of val, checked against numpy's reduceat on the host
-    ones = torch.ones(n, dtype=torch.float64, device=dev)
-    ys = torch.zeros(n, dtype=torch.float64, device=dev)
-    A.spmv(ones, ys, accumulate=False)
-    rowsum = np.add.reduceat(val, pos[:-1].astype(np.int64))
-    absum = np.add.reduceat(np.abs(val), pos[:-1].astype(np.int64))
-    assert np.all(np.abs(ys.cpu().numpy() - rowsum) <= TOL_F64 * absum)
-    # a sample of rows against the oracle
-    rows = np.random.default_rng(5).integers(0, n, 2000)
-    yh = y1.cpu().numpy()
-    for r in rows:
-        lo, hi = int(pos[r]), int(pos[r + 1])
-        ref = oracle.spmv(np.array([0, hi - lo], dtype=np.int64), crd[lo:hi], val[lo:hi], x, np.zeros(1))[0]
-        assert abs(yh[r] - ref) <= TOL_F64 * np.sum(np.abs(val[lo:hi] * x[crd[lo:hi]]))
+    yield {"A": A, "x": torch.as_tensor(x).to(dev), "n": n, "ref": ref, "dev": dev}
+    del A
+    torch.cuda.empty_cache()
+
+
+_FULL_VARIANTS = ["default", "tuned", "tuned_relaxed"] + [(t, b, h) for (t, b) in ((2, 4), (2, 5), (3, 3), (3, 4)) for h in (0, 1)] + [(4, 0, 0)]
+
+
+@pytest.mark.parametrize("variant", _FULL_VARIANTS, ids=[v if isinstance(v, str) else "k%d_%d_%d" % v for v in _FULL_VARIANTS])
+def test_spmv_full_size_properties(config2_full, variant):
+    """Config 2 at full size through every kernel the tuners can pick for it -- the default chunk kernel, the
+    strict and the relaxed tuner's choice, each segmented-scan instantiation and the warp-walk kernel: exact
+    linearity, the accumulate identity, row sums against numpy's reduceat, and 2000 rows against the oracle.
+    None of these needs a CPU pass over the whole matrix per variant."""
+    from lapis_b200._lib import check, load
+    c = config2_full
+    A, xd, n, ref, dev = c["A"], c["x"], c["n"], c["ref"], c["dev"]
+    lib = load()
+    if variant == "tuned":
+        A.tune()
+    elif variant == "tuned_relaxed":
+        A.tune(relaxed=True)
+    elif variant != "default":
+        check(lib.lapis_b200_spmv_select_kernel(*variant))
+    try:
+        y1 = torch.zeros(n, dtype=torch.float64, device=dev)
+        A.spmv(xd, y1, accumulate=False)
+        y1b = torch.full((n,), 7.0, dtype=torch.float64, device=dev)
+        A.spmv(xd, y1b, accumulate=False)
+        assert torch.equal(y1, y1b), "not run-to-run identical / depends on the old contents of y"
+        # A(2x) = 2 A x exactly (scaling by 2 is exact in binary floating point)
+        y2 = torch.zeros(n, dtype=torch.float64, device=dev)
+        A.spmv(2.0 * xd, y2, accumulate=False)
+        assert torch.equal(y2, 2.0 * y1)
+        # accumulate: y1 + A x == 2 A x up to the rounding of the final adds
+        y3 = y1.clone()
+        A.spmv(xd, y3, accumulate=True)
+        assert np.all(np.abs((y3 - 2.0 * y1).cpu().numpy()) <= TOL_F64 * ref["absum_x"])
+        # x = 1: y = row sums of val, checked against numpy's reduceat on the host
+        ones = torch.ones(n, dtype=torch.float64, device=dev)
+        ys = torch.zeros(n, dtype=torch.float64, device=dev)
+        A.spmv(ones, ys, accumulate=False)
+        assert np.all(np.abs(ys.cpu().numpy() - ref["rowsum"]) <= TOL_F64 * ref["absum"])
+        # a sample of rows against the oracle
+        yh = y1.cpu().numpy()
+        rows = ref["rows"]
+        err = np.abs(yh[rows] - ref["sample"])
+        assert np.all(err <= TOL_F64 * ref["absum_x"][rows]), f"max err/scale {np.max(err / ref['absum_x'][rows]):.3e}"
+    finally:
+        check(lib.lapis_b200_spmv_select_kernel(0, 0, 0))
 
 
 # ---------------------------------------------------------------------------
