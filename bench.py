@@ -295,7 +295,7 @@ def run_ours(args, d, rank, world, local_rank):
     from lapis_b200 import KokkosBackend as KB
     from lapis_b200 import device as D
     from lapis_b200 import partition as part
-    from tests import mlir_modules as mm
+    from lapis_b200 import modules as mm
 
     dev = torch.device(f"cuda:{local_rank}")
     torch.cuda.set_device(dev)

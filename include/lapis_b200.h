@@ -198,24 +198,23 @@ int lapis_b200_spmv_select_kernel(int threads, int blocks_per_sm, int l2_hint);
  * returns LAPIS_ECUDA if a block gave up (then y of that launch is invalid), clearing the flag. */
 int lapis_b200_spmv_status(void *stream);
 
-/* Measurement aid (no counterpart in the reference, not on any product path): reads the first nnz & ~3
- * entries of crd and val, gathers x and sums the products per thread without row structure and without a
- * store per entry.  Its duration is the floor for an SpMV over the same arrays; bench.py --probe flatdot. */
-int lapis_b200_probe_flat_dot_f64(int idx_bytes, int64_t nnz, const void *d_crd, const double *d_val, const double *d_x,
-                                  double *d_out, void *stream);
-
 /* The same SpMV for callers that must not allocate device memory in the call -- code
  * running inside a pool that already owns the whole GPU, or a steady-state loop where
  * a cudaMalloc could stall the device or fail.  No counterpart in the reference (its
  * emitted kernels need no plan).  Takes the raw CSR arrays instead of a handle and
  * keeps the streaming plan and the carries in a fixed 4 MiB array inside the library's device image,
  * so it calls neither cudaMalloc nor cudaFree.
- *   - Limit: 2^29 (536,870,912) stored entries; larger matrices get LAPIS_ETOOBIG.
- *   - The first call on a device looks the array's address up (cudaGetSymbolAddress);
- *     make that first call before any stream capture on that device.
+ *   - Limit: 2^18 chunks of 2048 stored entries counted from pos[0] rounded down to a multiple of 4: 2^29
+ *     (536,870,912) entries when pos[0] is a multiple of 4, up to 3 fewer otherwise; larger matrices get
+ *     LAPIS_ETOOBIG.
+ *   - The first call on a device looks the array's address up (cudaGetSymbolAddress); make that first call
+ *     outside any stream capture.  Every call, not only the first, copies pos[0] and pos[nrows] back to the
+ *     host and synchronises `stream`, so no call to this entry point can sit inside a stream capture.
  *   - All calls on a device share the one array: calls that can overlap on the GPU
  *     (different streams, no ordering between them) race.  Calls on one stream are safe.
- *   - Reads pos[0] and pos[nrows] back, which synchronises `stream` once per call.
+ *   - Like the rest of the library: one caller thread per process at a time (the per-device address cache
+ *     is a plain static).
+ *   - The device arrays are trusted (see lapis_b200_validate_csr_host).
  * Arguments as lapis_b200_csr_create followed by lapis_b200_spmv_f64. */
 int lapis_b200_spmv_f64_noalloc(int idx_bytes, int64_t nrows, int64_t ncols, const void *d_pos, const void *d_crd,
                                 const double *d_val, const double *d_x, double *d_y, int accumulate, void *stream);
@@ -333,6 +332,14 @@ int lapis_b200_pcg_status(void *d_work, int *done, uint64_t *iters, double *relr
 int lapis_b200_read_matrix_market(const char *path, int idx_bytes, int64_t *nrows, int64_t *ncols, int64_t *nnz,
                                   void **pos, void **crd, double **val);
 void lapis_b200_mm_free(void *p);
+
+/* Host-side validation the py_* wrappers run on a CSR operand before any kernel sees it (host arrays, no CUDA
+ * call): pos[0] == 0, pos non-decreasing, pos[nrows] == nnz, and 0 <= crd[j] < ncols for every stored entry;
+ * LAPIS_EBADSHAPE otherwise.  The emitted code aborts on bad descriptors (LAPISSupport.hpp:76-89) and indexes
+ * with crd unchecked.  The layer-2 entry points that take device pointers (lapis_b200_csr_create, ..._noalloc)
+ * cannot look at the arrays and trust them: callers holding host copies validate with this first. */
+int lapis_b200_validate_csr_host(int idx_bytes, int64_t nrows, int64_t ncols, int64_t nnz, const void *pos,
+                                 const void *crd);
 
 /* nnz-balanced contiguous row partition of a CSR matrix over G devices (host
  * arrays): bounds[g] = first row whose start offset is >= pos[0] + g*nnz/G,

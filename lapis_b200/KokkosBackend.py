@@ -6,7 +6,7 @@ with CMake and returns a generated ``LAPISModule`` whose methods call the
 ``py_<func>`` symbols of the built library
 (mlir/lib/Target/KokkosCpp/TranslateToKokkosCpp.cpp:2757-2977, :4393-4411).
 
-Here nothing is compiled at call time.  ``compile()`` reads the MLIR text, finds
+Here no kernel is compiled at call time.  ``compile()`` reads the MLIR text, finds
 the public functions, and binds each one that lies on the accelerated path --
 CSR ``linalg.matvec`` (SpMV), CSR x dense ``linalg.matmul`` (SpMM), dense
 ``linalg.matmul`` / ``linalg.batch_matmul`` in f32, and the ``@pcg`` solve loop of
@@ -28,7 +28,9 @@ import re
 
 import numpy as np
 
+from . import _forms
 from . import _memref as rt
+from . import _shim
 from ._lib import LapisError, check_last, load
 
 _PAR_STRATEGIES = ("none", "dense-outer-loop", "any-storage-outer-loop", "dense-any-loop", "any-storage-any-loop")
@@ -159,58 +161,73 @@ def _indexing_maps(text: str):
     return out
 
 
+def _off_path(fn: dict, why: str = ""):
+    return Exception(
+        f"function @{fn['name']} is not on the accelerated path (CSR matvec/matmul in f64, dense matmul / "
+        "batch_matmul in f32, the Jacobi PCG loop, the hitting-time moments, CSRV batched SpMM, DCSR SpMM)"
+        + (f": {why}" if why else "") + "; lapis_b200 has no general MLIR lowering and no fallback")
+
+
 def _classify(fn: dict, all_funcs: dict, module_text: str = ""):
-    """Returns (kind, index suffix, index dtype) or raises for an off-path function."""
+    """Returns (kind, index suffix, index dtype) or raises for an off-path function.
+
+    The argument and result types select a candidate kind; the body must then BE that operation
+    (lapis_b200/_forms.py): exactly one named linalg operation for the single-operation kinds, a canonical
+    form with an accepted digest for the loops.  A function that only resembles a known one -- a matvec
+    followed by a scale, a PCG loop with another stop test -- is refused, as it would compute something the
+    bound kernel does not."""
     a, r, body = fn["args"], fn["results"], fn["body"]
+    text = _forms.function_texts(module_text).get(fn["name"], "") if module_text else ""
+
+    def one_op(op):
+        if not _forms.single_named_op(text, op):
+            raise _off_path(fn, f"its body is not a single linalg.{op} on its arguments")
+
+    def known_form():
+        if _forms.closure_digest(fn["name"], module_text) not in _forms.accepted_digests():
+            raise _off_path(fn, "it differs from every accepted form of that operation")
+
     # a function that only prints its sparse argument (examples/bspmm.py:54-58, spmm_dcsr_opdsl.py:66-68): host work
     if len(a) == 1 and a[0].sparse is not None and len(r) == 0 and "sparse_tensor.print" in body and "linalg." not in body:
         return "print", "x".join(a[0].sparse["levels"]), None
     # batched SpMM over a CSRV tensor (examples/bspmm.py:14-52): out(n1,dh,nh) = sum_n2 A(n1,n2,nh) * B(n2,dh,nh)
-    if (len(a) == 2 and _is_csrv(a[0]) and a[0].elem == "f32" and _dense(a[1], 3, "f32") and len(r) == 1
-            and "linalg.generic" in body and "arith.mulf" in body and "arith.addf" in body and "linalg.fill" in body
-            and [(0, 1, 3), (1, 2, 3), (0, 2, 3)] in _indexing_maps(module_text)):
+    if len(a) == 2 and _is_csrv(a[0]) and a[0].elem == "f32" and _dense(a[1], 3, "f32") and len(r) == 1:
+        known_form()
         dt, sfx = _index_dtype(a[0].sparse)
         return "bspmm", sfx, dt
-    if (len(a) == 3 and _is_dcsr(a[0]) and a[0].elem == "f64" and _dense(a[1], 2, "f64") and _dense(a[2], 2, "f64")
-            and len(r) == 1 and ("linalg.matmul" in body or [(1, 0), (0, 2), (1, 2)] in _indexing_maps(body))):
+    if len(a) == 3 and _is_dcsr(a[0]) and a[0].elem == "f64" and _dense(a[1], 2, "f64") and _dense(a[2], 2, "f64") and len(r) == 1:
+        one_op("matmul")
         dt, sfx = _index_dtype(a[0].sparse)
         return "spmm_dcsr", sfx, dt
-    if (len(a) == 3 and _is_csr(a[0]) and a[0].elem == "f64" and _dense(a[1], 1, "f64") and _dense(a[2], 1, "f64")
-            and "linalg.matvec" in body and len(r) == 1):
+    if len(a) == 3 and _is_csr(a[0]) and a[0].elem == "f64" and _dense(a[1], 1, "f64") and _dense(a[2], 1, "f64") and len(r) == 1:
+        one_op("matvec")
         dt, sfx = _index_dtype(a[0].sparse)
         return "spmv", sfx, dt
-    if (len(a) == 3 and _is_csr(a[0]) and a[0].elem == "f64" and _dense(a[1], 2, "f64") and _dense(a[2], 2, "f64")
-            and "linalg.matmul" in body and len(r) == 1):
+    if len(a) == 3 and _is_csr(a[0]) and a[0].elem == "f64" and _dense(a[1], 2, "f64") and _dense(a[2], 2, "f64") and len(r) == 1:
+        one_op("matmul")
         dt, sfx = _index_dtype(a[0].sparse)
         return "spmm", sfx, dt
-    if (len(a) == 3 and all(_dense(t, 2, "f32") for t in a) and "linalg.matmul" in body and len(r) == 1):
+    if len(a) == 3 and all(_dense(t, 2, "f32") for t in a) and len(r) == 1:
+        one_op("matmul")
         return "matmul", "", None
-    if (len(a) == 3 and all(_dense(t, 3, "f32") for t in a) and "linalg.batch_matmul" in body and len(r) == 1):
+    if len(a) == 3 and all(_dense(t, 3, "f32") for t in a) and len(r) == 1:
+        one_op("batch_matmul")
         return "batch_matmul", "", None
     if (len(a) == 5 and _is_csr(a[0]) and a[0].elem == "f64" and _dense(a[1], 1, "f64") and _dense(a[2], 1, "f64")
-            and a[3].elem == "f64" and a[4].elem == "index" and len(r) == 3 and "scf.while" in body
-            and all(f"@{h}" in body for h in ("spmv", "dot", "axpby", "mult"))
-            and all(h in all_funcs for h in ("spmv", "dot", "axpby", "mult"))
-            and "linalg.matvec" in all_funcs["spmv"]["body"] and "linalg.dot" in all_funcs["dot"]["body"]):
+            and a[3].elem == "f64" and a[4].elem == "index" and len(r) == 3):
+        known_form()  # examples/pcg_solve.py:52-101
         dt, sfx = _index_dtype(a[0].sparse)
         return "pcg", sfx, dt
     # hitting-time moments (examples/hitting_times.py:151-194): scale, two masked-Laplacian PCG solves
     if (len(a) == 6 and _is_csr(a[0]) and a[0].elem == "f64" and _dense(a[1], 1, "f64") and _dense(a[2], 1, "f64")
-            and a[3].elem == "f64" and a[4].elem == "f64" and a[5].elem == "index" and len(r) == 2
-            and all(f"@{h}" in body for h in ("scale_csr", "pcg", "spmv", "mult"))
-            and all(h in all_funcs for h in ("scale_csr", "pcg", "plpt", "spmv", "dot", "axpby", "mult"))
-            and body.count("@pcg(") == 2 and "@plpt" in all_funcs["pcg"]["body"] and "linalg.div" in all_funcs["pcg"]["body"]
-            and "scf.while" in all_funcs["pcg"]["body"] and "arith.subf" in all_funcs["plpt"]["body"]
-            and "linalg.matvec" in all_funcs["spmv"]["body"]):
+            and a[3].elem == "f64" and a[4].elem == "f64" and a[5].elem == "index" and len(r) == 2):
+        known_form()
         dt, sfx = _index_dtype(a[0].sparse)
         return "mht", sfx, dt
-    if (len(a) == 2 and _dense(a[0], 1, "f64") and _dense(a[1], 1, "f64") and len(r) == 1 and "math.sqrt" in body
-            and "arith.subf" in body and "arith.mulf" in body and "func.call" not in body):
+    if len(a) == 2 and _dense(a[0], 1, "f64") and _dense(a[1], 1, "f64") and len(r) == 1:
+        known_form()  # examples/hitting_times.py:196-218
         return "normalize_mom2", "", None
-    raise Exception(
-        f"function @{fn['name']} is not on the accelerated path (CSR matvec/matmul in f64, dense matmul / "
-        "batch_matmul in f32, the Jacobi PCG loop, the hitting-time moments); lapis_b200 has no general MLIR "
-        "lowering and no fallback")
+    raise _off_path(fn)
 
 
 # ---------------------------------------------------------------------------
@@ -248,14 +265,19 @@ class LAPISModule:
     ``numpy()``, and the in/out argument is returned as a DualView.
     """
 
-    def __init__(self, bindings: dict):
-        self.libHandle = load()
+    def __init__(self, libPath: str, bindings: dict):
+        # libPath: the module's own library (lapis_b200/_shim.py), exporting py_<func> under the names the
+        # emitter uses; it depends on liblapis_b200.so, loaded first so that a missing build fails loudly
+        load()
+        self.libPath = libPath
+        self.libHandle = ctypes.CDLL(libPath)
+        self.libHandle.lapis_last_error.restype = ctypes.c_int
         self.libHandle.lapis_initialize()
         check_last()
         self._live = True
         self._plans = {}  # (id(pos), id(crd), id(val)) -> (weakrefs, versions, shape, CsrMatrix)
         for name, (kind, sfx, idx_dtype) in bindings.items():
-            setattr(self, name, self._bind(kind, sfx, idx_dtype))
+            setattr(self, name, self._bind(name, kind, sfx, idx_dtype))
 
     def __del__(self):
         if getattr(self, "_live", False):
@@ -408,8 +430,9 @@ class LAPISModule:
         y._mod_device = False
         y.downloads += 1
 
-    def _bind(self, kind, sfx, idx_dtype):
+    def _bind(self, name, kind, sfx, idx_dtype):
         lib = self.libHandle
+        symbol = "py_" + _shim.export_name(name)  # the emitter's export name, from the module's own library
 
         def csr_args(pos, crd, val, spec):
             pos = np.require(pos, dtype=idx_dtype, requirements=["C"])
@@ -419,7 +442,7 @@ class LAPISModule:
             return (pos, crd, val, flat), (_desc(pos), _desc(crd), _desc(val), flat.ctypes.data_as(ctypes.c_void_p))
 
         if kind == "spmv":
-            fn = getattr(lib, f"py_spmv_f64_{sfx}")
+            fn = getattr(lib, symbol)
 
             def spmv(pos, crd, val, spec, x, y, sync_host=False):
                 """``sync_host=True`` (resident path only): return with y already on the host; the matrix is
@@ -450,7 +473,7 @@ class LAPISModule:
 
             return spmv
         if kind == "spmm":
-            fn = getattr(lib, f"py_spmm_f64_{sfx}")
+            fn = getattr(lib, symbol)
 
             def spmm(pos, crd, val, spec, B, C, sync_host=False):
                 """``sync_host=True`` (resident path only): as for spmv, C comes back block by block."""
@@ -476,7 +499,7 @@ class LAPISModule:
 
             return spmm
         if kind in ("matmul", "batch_matmul"):
-            fn = lib.py_matmul_f32 if kind == "matmul" else lib.py_batch_matmul_f32
+            fn = getattr(lib, symbol)
             rank = 2 if kind == "matmul" else 3
 
             def forward(A, B, C):
@@ -496,7 +519,7 @@ class LAPISModule:
 
             return forward
         if kind == "pcg":
-            fn = getattr(lib, f"py_pcg_f64_{sfx}")
+            fn = getattr(lib, symbol)
 
             def pcg(pos, crd, val, spec, b, dinv, tol, maxiter):
                 if _resident(pos, crd, val, b, dinv):
@@ -544,7 +567,7 @@ class LAPISModule:
 
             return print_tensor
         if kind == "bspmm":
-            fn = getattr(lib, f"py_bspmm_f32_{sfx}")
+            fn = getattr(lib, symbol)
 
             def bspmm(pos, crd, val, spec, B):
                 flat = np.array(list(spec[0]) + list(spec[1]), dtype=np.int64)
@@ -571,7 +594,7 @@ class LAPISModule:
 
             return bspmm
         if kind == "spmm_dcsr":
-            fn = getattr(lib, f"py_spmm_dcsr_f64_{sfx}")
+            fn = getattr(lib, symbol)
 
             def spmm_dcsr(p1, i1, p2, i2, val, spec, B, C):
                 flat = np.array(list(spec[0]) + list(spec[1]), dtype=np.int64)
@@ -598,7 +621,7 @@ class LAPISModule:
 
             return spmm_dcsr
         if kind == "mht":
-            fn = getattr(lib, f"py_mht_f64_{sfx}")
+            fn = getattr(lib, symbol)
 
             def mht(pos, crd, val, spec, mask, d, alpha, tol, maxiter):
                 if _resident(pos, crd, val, mask, d):
@@ -619,7 +642,7 @@ class LAPISModule:
 
             return mht
         if kind == "normalize_mom2":
-            fn = lib.py_normalize_mom2_f64
+            fn = getattr(lib, symbol)
 
             def normalize_mom2(mom1, mom2):
                 if _resident(mom1, mom2):
@@ -676,4 +699,5 @@ class KokkosBackend:
             print("== Bound ==")
             for name, (kind, sfx, _) in bindings.items():
                 print(f"@{name} -> {kind}{'_' + sfx if sfx else ''}")
-        return LAPISModule(bindings)
+        # the module's own library: py_<func> under the emitter's names, forwarding to the typed entry points
+        return LAPISModule(_shim.build(bindings, self.ws, self.package_name), bindings)

@@ -60,7 +60,6 @@ _PROTOS = {
     "lapis_b200_pcg_step_direction": (c_int, [c_vp, c_i64, c_i64, c_i64, c_vp]),
     "lapis_b200_bspmm_csrv_f32": (c_int, [c_int, c_i64, c_i64, c_i64, c_i64, c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_vp]),
     "lapis_b200_spmm_dcsr_f64": (c_int, [c_int, c_i64, c_i64, c_i64, c_i64, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp]),
-    "lapis_b200_probe_flat_dot_f64": (c_int, [c_int, c_i64, c_vp, c_vp, c_vp, c_vp, c_vp]),
     "lapis_b200_mht_f64": (c_int, [c_vp, c_vp, c_vp, c_dbl, c_dbl, c_u64, c_vp, c_vp, ctypes.POINTER(c_u64),
                                    ctypes.POINTER(c_dbl), c_vp]),
     "lapis_b200_normalize_mom2_f64": (c_int, [c_i64, c_vp, c_vp, c_vp, c_vp]),
@@ -80,6 +79,7 @@ _PROTOS = {
                                               ctypes.POINTER(c_vp)]),
     "lapis_b200_mm_free": (None, [c_vp]),
     "lapis_b200_partition_rows": (c_int, [c_int, c_i64, c_vp, c_int, c_vp]),
+    "lapis_b200_validate_csr_host": (c_int, [c_int, c_i64, c_i64, c_i64, c_vp, c_vp]),
 }
 
 _LIB = None

@@ -6,10 +6,12 @@
 // wraps host pointers in unmanaged Kokkos views and lets LAPIS::DualView copy them
 // to the device (LAPISSupport.hpp:193-282), this file stages the operands in device
 // buffers with cudaMemcpyAsync, runs the kernels and copies the result back.
+#include <algorithm>
 #include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <string>
+#include <thread>
 #include <vector>
 
 #include "common.h"
@@ -122,6 +124,42 @@ static int check_pos_host(const I *pos, int64_t nrows, int64_t nnz) {
   return LAPIS_OK;
 }
 
+// Validates the column indices on the host: 0 <= crd[j] < ncols for every stored entry.  The emitted code
+// indexes x with them unchecked (a bad index is undefined behaviour there); here a bad index must not
+// reach a gather on the device.  Min and max over slices of the array on a few host threads.
+template <typename I>
+static int check_crd_host(const I *crd, int64_t nnz, int64_t ncols) {
+  if (nnz <= 0) return LAPIS_OK;
+  const int nthreads = nnz < (1 << 20) ? 1 : (int)std::min<int64_t>(8, std::max(1u, std::thread::hardware_concurrency()));
+  std::vector<I> lo(nthreads), hi(nthreads);
+  auto scan = [&](int t) {
+    const int64_t b = nnz * t / nthreads, e = nnz * (t + 1) / nthreads;
+    I mn = crd[b], mx = crd[b];
+    for (int64_t j = b; j < e; ++j) {
+      mn = crd[j] < mn ? crd[j] : mn;
+      mx = crd[j] > mx ? crd[j] : mx;
+    }
+    lo[t] = mn;
+    hi[t] = mx;
+  };
+  if (nthreads == 1) {
+    scan(0);
+  } else {
+    std::vector<std::thread> pool;
+    for (int t = 0; t < nthreads; ++t) pool.emplace_back(scan, t);
+    for (auto &th : pool) th.join();
+  }
+  I mn = lo[0], mx = hi[0];
+  for (int t = 1; t < nthreads; ++t) {
+    mn = lo[t] < mn ? lo[t] : mn;
+    mx = hi[t] > mx ? hi[t] : mx;
+  }
+  if ((int64_t)mn < 0 || (int64_t)mx >= ncols)
+    return fail(LAPIS_EBADSHAPE, "column index out of range: crd holds values in [%lld, %lld], the matrix has %lld columns",
+                (long long)mn, (long long)mx, (long long)ncols);
+  return LAPIS_OK;
+}
+
 // Uploads a CSR matrix and builds its handle.
 struct DeviceCsr {
   DevBuf pos, crd, val;
@@ -141,7 +179,7 @@ static int upload_csr(const lapis_memref1 *pos, const lapis_memref1 *crd, const 
   LAPIS_CUDA_TRY(cudaMemcpyAsync(d->val.p, elem_ptr<double>(val), (size_t)a.nnz * sizeof(double), cudaMemcpyHostToDevice, st));
   // validated on the host while the copies are in flight (they are asynchronous from pinned memory);
   // no kernel has been given the offsets yet
-  if (check_pos_host<I>(hpos, a.nrows, a.nnz) != LAPIS_OK) {
+  if (check_pos_host<I>(hpos, a.nrows, a.nnz) != LAPIS_OK || check_crd_host<I>(elem_ptr<I>(crd), a.nnz, a.ncols) != LAPIS_OK) {
     const int code = lapis_last_error();
     char msg[512];
     snprintf(msg, sizeof(msg), "%s", lapis_last_error_message());
@@ -609,6 +647,19 @@ static void partition_rows(int64_t nrows, const I *pos, int G, int64_t *bounds) 
     }
     bounds[g] = lo;
   }
+}
+
+extern "C" int lapis_b200_validate_csr_host(int idx_bytes, int64_t nrows, int64_t ncols, int64_t nnz, const void *pos,
+                                           const void *crd) {
+  clear_error();
+  if ((idx_bytes != 4 && idx_bytes != 8) || nrows < 0 || ncols < 0 || nnz < 0 || pos == nullptr || (nnz > 0 && crd == nullptr))
+    return fail(LAPIS_EBADARG, "validate_csr_host: bad arguments");
+  if (idx_bytes == 4) {
+    LAPIS_TRY(check_pos_host<int32_t>(static_cast<const int32_t *>(pos), nrows, nnz));
+    return check_crd_host<int32_t>(static_cast<const int32_t *>(crd), nnz, ncols);
+  }
+  LAPIS_TRY(check_pos_host<int64_t>(static_cast<const int64_t *>(pos), nrows, nnz));
+  return check_crd_host<int64_t>(static_cast<const int64_t *>(crd), nnz, ncols);
 }
 
 extern "C" int lapis_b200_partition_rows(int idx_bytes, int64_t nrows, const void *pos, int G, int64_t *bounds) {

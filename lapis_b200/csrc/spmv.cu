@@ -1291,10 +1291,6 @@ static int launch_spmv(const lapis_b200_csr *h, const double *x, double *y, int 
   LAPIS_CUDA_TRY(cudaGetLastError());
   if (h->nblk > 1) {
     const I *pos = static_cast<const I *>(h->pos);
-    static const int pdl = [] {
-      const char *e = std::getenv("LAPIS_B200_PDL");
-      return e ? atoi(e) : 1;
-    }();
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)((h->nblk - 1 + 255) / 256));
     cfg.blockDim = dim3(256);
@@ -1303,7 +1299,7 @@ static int launch_spmv(const lapis_b200_csr *h, const double *x, double *y, int 
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = pdl ? 1 : 0;  // lets the fix-up blocks become resident while the SpMV kernel drains
+    cfg.numAttrs = 1;  // lets the fix-up blocks become resident while the SpMV kernel drains
     LAPIS_CUDA_TRY(cudaLaunchKernelEx(&cfg, spmv_fixup_kernel<I>, pos, (const int64_t *)h->blk_row,
                                       (int64_t)(h->base & ~(int64_t)3), (int64_t)h->nblk, (int64_t)h->nrows,
                                       (const double *)h->carry, y, skip_flag));
@@ -1332,60 +1328,25 @@ static void launch_spmm_variant(const lapis_b200_csr *h, int64_t k, const double
     spmm_row_kernel<I, false, WARPS, UNROLL><<<grid, WARPS * 32, 0, st>>>(pos, crd, h->val, h->nrows, k, B, C, accumulate);
 }
 
-// B rows in flight per warp (UNROLL) against resident warps: LAPIS_B200_SPMM="warps,unroll" picks a variant.
+// The direct-load kernel (four rows of B in flight per lane) needs k even and 16-byte aligned B, C; other
+// operands take the shuffle-broadcast kernel.  Measured on the 2^21-row, 32-per-row, k = 64 case: direct 5.10 ms
+// (5.12 ms with eight rows in flight), shuffle-broadcast 6.6 ms.
 template <typename I>
 static int launch_spmm(const lapis_b200_csr *h, int64_t k, const double *B, double *C, int accumulate,
                        cudaStream_t st) {
-  static const int variant = [] {
-    int w = 0, u = 1;
-    if (const char *e = std::getenv("LAPIS_B200_SPMM")) sscanf(e, "%d,%d", &w, &u);
-    return w * 100 + u;
-  }();
-  // Measured on the 2^21-row, 32-per-row, k = 64 case: the direct-load kernel 5.10 ms with four rows of B in
-  // flight per lane ("0,1", the default) and 5.12 ms with eight ("0,2"); the shuffle-broadcast kernel 6.6 ms
-  // as (8,4), 6.7 ms as (16,4), 10.0 ms as (8,8).  The direct kernel needs k even and 16-byte aligned B, C.
   const bool vec2 = (k % 2 == 0) && ((reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) % 16 == 0);
-  if (vec2 && (variant == 1 || variant == 2)) {
+  if (vec2) {
     const I *pos = static_cast<const I *>(h->pos);
     const I *crd = static_cast<const I *>(h->crd);
     const unsigned grid = (unsigned)((h->nrows + 7) / 8);
-    const double2 *B2 = reinterpret_cast<const double2 *>(B);
-    double2 *C2 = reinterpret_cast<double2 *>(C);
-    if (variant == 1)
-      spmm_row_direct_kernel<I, 8, 4><<<grid, 256, 0, st>>>(pos, crd, h->val, h->nrows, k / 2, B2, C2, accumulate);
-    else
-      spmm_row_direct_kernel<I, 8, 8><<<grid, 256, 0, st>>>(pos, crd, h->val, h->nrows, k / 2, B2, C2, accumulate);
-    LAPIS_CUDA_TRY(cudaGetLastError());
-    return LAPIS_OK;
-  }
-  switch (variant) {
-    case 808: launch_spmm_variant<I, 8, 8>(h, k, B, C, accumulate, st); break;
-    case 1604: launch_spmm_variant<I, 16, 4>(h, k, B, C, accumulate, st); break;
-    default: launch_spmm_variant<I, 8, 4>(h, k, B, C, accumulate, st); break;
+    spmm_row_direct_kernel<I, 8, 4><<<grid, 256, 0, st>>>(pos, crd, h->val, h->nrows, k / 2,
+                                                          reinterpret_cast<const double2 *>(B),
+                                                          reinterpret_cast<double2 *>(C), accumulate);
+  } else {
+    launch_spmm_variant<I, 8, 4>(h, k, B, C, accumulate, st);
   }
   LAPIS_CUDA_TRY(cudaGetLastError());
   return LAPIS_OK;
-}
-
-// Yardstick, not part of the product path: sum_j val[j] * x[crd[j]] with no row structure and no per-entry
-// store -- the same value and index streams and the same gathers as the SpMV, four entries per thread, every
-// thread independent.  What it takes is the floor for any SpMV over these arrays.
-template <typename I>
-__global__ void __launch_bounds__(256)
-flat_dot_probe_kernel(const I *__restrict__ crd, const double *__restrict__ val, const double *__restrict__ x,
-                      double *__restrict__ out, int64_t n) {
-  const int64_t base = ((int64_t)blockIdx.x * 256 + threadIdx.x) * 4;
-  if (base + 4 > n) return;
-  using Pair = typename IndexPair<I>::type;
-  double s = 0.0;
-#pragma unroll
-  for (int u = 0; u < 4; u += 2) {
-    const Pair c = __ldcs(reinterpret_cast<const Pair *>(crd + base + u));
-    const double2 a = __ldcs(reinterpret_cast<const double2 *>(val + base + u));
-    s = __dadd_rn(s, __dmul_rn(a.x, __ldg(x + (int64_t)c.x)));
-    s = __dadd_rn(s, __dmul_rn(a.y, __ldg(x + (int64_t)c.y)));
-  }
-  if (s == 1.2345e300) out[0] = s;  // keeps the loads alive without a store per thread
 }
 
 }  // namespace lapis_b200
@@ -1628,10 +1589,11 @@ static __device__ __align__(256) int64_t g_noalloc_plan[2 * NOALLOC_MAX_TILES + 
 
 // Device address of g_noalloc_plan per device.  In host code the array's name is only a
 // handle for the runtime, not an address a kernel may use; cudaGetSymbolAddress returns the
-// address in the device that is current when it is called.
+// address in the device that is current when it is called.  Plain statics without a lock, like
+// the rest of the library: one caller thread per process at a time.
 static int64_t *g_noalloc_plan_addr[64] = {nullptr};
 
-static int noalloc_plan_ptr(int64_t **out) {
+static int noalloc_plan_ptr(int64_t **out, int *device) {
   int dev = 0;
   LAPIS_CUDA_TRY(cudaGetDevice(&dev));
   if (dev < 0 || dev >= 64) return lapis_b200::fail(LAPIS_EBADARG, "spmv_noalloc: device index %d not supported", dev);
@@ -1641,6 +1603,7 @@ static int noalloc_plan_ptr(int64_t **out) {
     g_noalloc_plan_addr[dev] = static_cast<int64_t *>(p);
   }
   *out = g_noalloc_plan_addr[dev];
+  *device = dev;
   return LAPIS_OK;
 }
 
@@ -1657,7 +1620,8 @@ extern "C" int lapis_b200_spmv_f64_noalloc(int idx_bytes, int64_t nrows, int64_t
   if (d_y == nullptr) return fail(LAPIS_EBADARG, "spmv_noalloc: y is null");
   cudaStream_t st = as_stream(stream);
   int64_t *plan = nullptr;
-  LAPIS_TRY(noalloc_plan_ptr(&plan));
+  int dev = 0;
+  LAPIS_TRY(noalloc_plan_ptr(&plan, &dev));
 
   // pos[0] and pos[nrows] (copied into host variables: no allocation involved)
   int64_t ends[2] = {0, 0};
@@ -1681,9 +1645,11 @@ extern "C" int lapis_b200_spmv_f64_noalloc(int idx_bytes, int64_t nrows, int64_t
   if (nblk < 1) nblk = 1;
   if (nblk > NOALLOC_MAX_TILES)
     return fail(LAPIS_ETOOBIG,
-                "spmv_noalloc: %lld stored entries exceed the fixed plan buffer (limit %lld entries); "
+                "spmv_noalloc: %lld stored entries starting at offset %lld need %lld chunks of %d, the fixed plan "
+                "buffer holds %lld (at most %lld entries when pos[0] is a multiple of 4, up to 3 fewer otherwise); "
                 "use lapis_b200_csr_create + lapis_b200_spmv_f64 for larger matrices",
-                (long long)nnz, (long long)(NOALLOC_MAX_TILES * (int64_t)SPMV_TILE - 1));
+                (long long)nnz, (long long)ends[0], (long long)nblk, SPMV_TILE, (long long)NOALLOC_MAX_TILES,
+                (long long)(NOALLOC_MAX_TILES * (int64_t)SPMV_TILE));
 
   lapis_b200_csr h;
   h.idx_bytes = idx_bytes;
@@ -1700,7 +1666,7 @@ extern "C" int lapis_b200_spmv_f64_noalloc(int idx_bytes, int64_t nrows, int64_t
   h.carry = reinterpret_cast<double *>(plan + NOALLOC_MAX_TILES + 1);
   h.tuned_threads = h.tuned_minb = h.tuned_hint = 0;
   h.max_row_len = -1;
-  h.device = 0;
+  h.device = dev;
   const unsigned pgrid = (unsigned)((nblk + 1 + 255) / 256);
   if (idx_bytes == 4)
     spmv_plan_kernel<int32_t><<<pgrid, 256, 0, st>>>(static_cast<const int32_t *>(d_pos), nrows, nblk, plan);
@@ -1708,23 +1674,4 @@ extern "C" int lapis_b200_spmv_f64_noalloc(int idx_bytes, int64_t nrows, int64_t
     spmv_plan_kernel<int64_t><<<pgrid, 256, 0, st>>>(static_cast<const int64_t *>(d_pos), nrows, nblk, plan);
   LAPIS_CUDA_TRY(cudaGetLastError());
   return spmv_launch(&h, d_x, d_y, accumulate, nullptr, nullptr, nullptr, st);
-}
-
-// Launches the flat-dot yardstick over the first nnz & ~3 entries (crd, val 16-byte aligned).
-extern "C" int lapis_b200_probe_flat_dot_f64(int idx_bytes, int64_t nnz, const void *d_crd, const double *d_val,
-                                             const double *d_x, double *d_out, void *stream) {
-  clear_error();
-  if ((idx_bytes != 4 && idx_bytes != 8) || nnz < 0 || d_crd == nullptr || d_val == nullptr || d_x == nullptr || d_out == nullptr)
-    return fail(LAPIS_EBADARG, "probe_flat_dot: bad arguments");
-  if ((reinterpret_cast<uintptr_t>(d_val) % 16) || (reinterpret_cast<uintptr_t>(d_crd) % 16))
-    return fail(LAPIS_EBADARG, "probe_flat_dot: val and crd must be 16-byte aligned");
-  const int64_t n = nnz & ~(int64_t)3;
-  if (n == 0) return LAPIS_OK;
-  const unsigned grid = (unsigned)((n / 4 + 255) / 256);
-  if (idx_bytes == 4)
-    flat_dot_probe_kernel<int32_t><<<grid, 256, 0, as_stream(stream)>>>(static_cast<const int32_t *>(d_crd), d_val, d_x, d_out, n);
-  else
-    flat_dot_probe_kernel<int64_t><<<grid, 256, 0, as_stream(stream)>>>(static_cast<const int64_t *>(d_crd), d_val, d_x, d_out, n);
-  LAPIS_CUDA_TRY(cudaGetLastError());
-  return LAPIS_OK;
 }

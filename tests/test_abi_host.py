@@ -55,6 +55,50 @@ def test_no_device_fails_loudly():
         KB.KokkosBackend(decompose_tensors=True).compile(mm.spmv())
 
 
+def test_csr_validator_refuses_bad_offsets_and_columns():
+    """The check the py_* wrappers run on a CSR operand before any kernel sees it (host only, no CUDA call):
+    a column index outside [0, ncols) or a broken pos is LAPIS_EBADSHAPE."""
+    lib = _lib.load()
+    vp = lambda a: a.ctypes.data_as(ctypes.c_void_p)
+    for idx in (np.int32, np.int64):
+        pos = np.array([0, 2, 2, 5], dtype=idx)
+        crd = np.array([0, 3, 1, 2, 3], dtype=idx)
+        nb = np.dtype(idx).itemsize
+        assert lib.lapis_b200_validate_csr_host(nb, 3, 4, 5, vp(pos), vp(crd)) == 0
+        bad = crd.copy(); bad[3] = 4            # == ncols
+        assert lib.lapis_b200_validate_csr_host(nb, 3, 4, 5, vp(pos), vp(bad)) == 1
+        assert b"column index out of range" in lib.lapis_last_error_message()
+        bad = crd.copy(); bad[0] = -1
+        assert lib.lapis_b200_validate_csr_host(nb, 3, 4, 5, vp(pos), vp(bad)) == 1
+        badpos = np.array([0, 3, 2, 5], dtype=idx)   # decreasing
+        assert lib.lapis_b200_validate_csr_host(nb, 3, 4, 5, vp(badpos), vp(crd)) == 1
+        assert lib.lapis_b200_validate_csr_host(nb, 3, 4, 4, vp(pos), vp(crd)) == 1   # pos[rows] != nnz
+    # the threaded path (more than 2^20 entries): one bad index in the middle of the last slice
+    n = (1 << 20) + 12345
+    crd = (np.arange(n, dtype=np.int64) * 7) % 1000
+    pos = np.array([0, n], dtype=np.int64)
+    assert lib.lapis_b200_validate_csr_host(8, 1, 1000, n, vp(pos), vp(crd)) == 0
+    crd[n - 77] = 1000
+    assert lib.lapis_b200_validate_csr_host(8, 1, 1000, n, vp(pos), vp(crd)) == 1
+
+
+def test_module_library_exports_the_emitted_names(tmp_path):
+    """The per-module library that compile() builds exports py_<func> under the emitter's names
+    (TranslateToKokkosCpp.cpp:2541: `extern "C" void py_<funcName>(`; `main` becomes `lapis_main`, :2351-2355)
+    and resolves the lifecycle symbols through liblapis_b200.so.  No compute call."""
+    from lapis_b200 import _shim
+    bindings = {"spmv": ("spmv", "i64", np.int64), "pcg": ("pcg", "i32", np.int32), "main": ("batch_matmul", "", None),
+                "show": ("print", "densexcompressed", None)}
+    so = _shim.build(bindings, str(tmp_path), "lapis_package")
+    assert os.path.isfile(so) and _shim.build(bindings, str(tmp_path), "lapis_package") == so  # reused
+    h = ctypes.CDLL(so)
+    for name in ("py_spmv", "py_pcg", "py_lapis_main", "lapis_initialize", "lapis_finalize", "lapis_last_error"):
+        assert hasattr(h, name), name
+    assert not hasattr(h, "py_show") and not hasattr(h, "py_main")
+    text = _shim.source(bindings)
+    assert "py_spmv_f64_i64(ret0, pos, crd, val, spec, x, y)" in text and "py_pcg_f64_i32(" in text
+
+
 def test_compute_before_initialize_is_refused():
     lib = _lib.load()
     pos = np.array([0, 1], dtype=np.int32)
@@ -82,7 +126,7 @@ def test_backend_classifies_on_path_modules():
     by = {f["name"]: f for f in funcs}
     assert set(by) == {"spmv", "dot", "axpby", "mult", "pcg"}
     assert by["spmv"]["private"] and not by["pcg"]["private"]
-    assert KB._classify(by["pcg"], by)[:2] == ("pcg", "i32")
+    assert KB._classify(by["pcg"], by, mm.pcg())[:2] == ("pcg", "i32")
     for text, want in ((mm.spmv(mm.CSR32), ("spmv", "i32")), (mm.spmv(mm.CSR64), ("spmv", "i64")),
                        (mm.spmv(mm.CSRIDX), ("spmv", "i64")), (mm.spmm(), ("spmm", "i64")),
                        (mm.MATMUL, ("matmul", "")), (mm.BATCH_MATMUL, ("batch_matmul", ""))):
@@ -90,7 +134,60 @@ def test_backend_classifies_on_path_modules():
         funcs = KB._parse_functions(text, enc)
         public = [f for f in funcs if not f["private"]]
         assert len(public) == 1
-        assert KB._classify(public[0], {f["name"]: f for f in funcs})[:2] == want
+        assert KB._classify(public[0], {f["name"]: f for f in funcs}, text)[:2] == want
+
+
+def _classify_text(text):
+    funcs = KB._parse_functions(text, KB._parse_encodings(text))
+    by = {f["name"]: f for f in funcs}
+    return [KB._classify(f, by, text)[:2] for f in funcs if not f["private"]]
+
+
+def test_backend_refuses_functions_that_only_resemble_a_known_one():
+    """A function is bound to a kernel only if it IS the operation: near-misses would silently compute
+    something else than what was written."""
+    # a matvec followed by a scale of the result
+    scaled = mm.spmv().replace(
+        "return %r : tensor<?xf64>",
+        "%two = arith.constant 2.0 : f64\n    %s = linalg.generic {indexing_maps = [affine_map<(i) -> (i)>], "
+        "iterator_types = [\"parallel\"]} outs(%r : tensor<?xf64>) {\n    ^bb0(%o: f64):\n      %t = arith.mulf %o, %two : f64\n"
+        "      linalg.yield %t : f64\n    } -> tensor<?xf64>\n    return %s : tensor<?xf64>")
+    assert scaled != mm.spmv()
+    # operands wired differently: A^T-like use of y as the input vector
+    swapped = mm.spmv().replace("ins(%A, %x :", "ins(%A, %y :").replace("outs(%y :", "outs(%x :")
+    # two products in one function
+    twice = mm.MATMUL.replace(
+        "return %r : tensor<?x?xf32>",
+        "%r2 = linalg.matmul ins(%a, %b : tensor<?x?xf32>, tensor<?x?xf32>) outs(%r : tensor<?x?xf32>) -> tensor<?x?xf32>\n"
+        "    return %r2 : tensor<?x?xf32>")
+    # PCG with another stop test, another iteration start, another update
+    pcg = mm.pcg()
+    variants = [scaled, swapped, twice,
+                pcg.replace("arith.cmpf ogt, %rel, %tol", "arith.cmpf oge, %rel, %tol"),
+                pcg.replace("%i = %c1)", "%i = %c0)"),
+                pcg.replace("%alpha = arith.divf %rz, %pAp", "%alpha = arith.divf %pAp, %rz"),
+                pcg.replace("%x0 = tensor.splat %f0[%n]", "%x0 = tensor.splat %f1[%n]"),
+                mm.hitting_times().replace("math.sqrt", "math.absf")]
+    for text in variants:
+        with pytest.raises(Exception, match="not on the accelerated path"):
+            _classify_text(text)
+    # what is accepted stays accepted: renamed values, other alias names, extra dead bookkeeping
+    renamed = mm.pcg().replace("%alpha", "%step").replace("#id", "#identity")
+    assert _classify_text(renamed) == [("pcg", "i32")]
+    padded = mm.spmv().replace("%r = linalg.matvec", "%c7 = arith.constant 7 : index\n    %r = linalg.matvec")
+    assert _classify_text(padded) == [("spmv", "i32")]
+
+
+@pytest.mark.skipif(not os.path.isdir("/root/reference/examples"), reason="needs a checkout of the LAPIS project")
+def test_backend_accepts_the_reference_examples_as_written():
+    """The module texts of the LAPIS examples, read from the checkout, bind without an edit."""
+    want = {"pcg_solve.py": [("pcg", "i32")], "hitting_times.py": [("mht", "i32"), ("normalize_mom2", "")],
+            "spmv_noalloc.py": [("spmv", "i32")], "gemm_no_alloc.py": [("matmul", "")],
+            "batched_gemm_no_alloc.py": [("batch_matmul", "")]}
+    for fname, kinds in want.items():
+        text = open(os.path.join("/root/reference/examples", fname)).read()
+        module = re.search(r'=\s*"""(.*?)"""', text, re.S).group(1)
+        assert _classify_text(module) == kinds, fname
 
 
 def test_backend_classifies_the_hitting_times_module():
@@ -100,14 +197,14 @@ def test_backend_classifies_the_hitting_times_module():
         by = {f["name"]: f for f in funcs}
         public = sorted(f["name"] for f in funcs if not f["private"])
         assert public == ["mht", "normalize_mom2"]
-        assert KB._classify(by["mht"], by)[:2] == ("mht", sfx)
-        assert KB._classify(by["normalize_mom2"], by)[:2] == ("normalize_mom2", "")
+        assert KB._classify(by["mht"], by, text)[:2] == ("mht", sfx)
+        assert KB._classify(by["normalize_mom2"], by, text)[:2] == ("normalize_mom2", "")
     # the plain solver's module is not mistaken for it, and a module without the masked operator is refused
     text = mm.hitting_times().replace("@plpt", "@other")
     funcs = KB._parse_functions(text, KB._parse_encodings(text))
     by = {f["name"]: f for f in funcs}
     with pytest.raises(Exception, match="not on the accelerated path"):
-        KB._classify(by["mht"], by)
+        KB._classify(by["mht"], by, text)
 
 
 def test_backend_classifies_neighbouring_formats():
