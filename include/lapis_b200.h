@@ -321,6 +321,35 @@ int lapis_b200_pcg_p2p_wait_reduce(void *d_work, void *d_mbox, int phase, int wo
                                    uint64_t maxiter, void *stream);
 int lapis_b200_pcg_p2p_halo_push(void *d_work, int64_t n, int64_t n_p, const void *d_pieces, int npieces, void *stream);
 int lapis_b200_pcg_p2p_halo_wait(void *d_work, void *d_mbox, const void *d_srcs, int nsrc, void *stream);
+/* One iteration in three launches.  The passes above leave the sums to a single-block kernel (or to the
+ * caller's collective) between them; these variants add the per-block partial sums inside the pass, in the
+ * block that finishes last, and -- with an exchange description -- do the row-partitioned solver's exchanges
+ * inside the passes too: pass A waits for the neighbours' halo pieces of p and ends by storing this rank's
+ * p.Ap into every rank's mailbox; pass B starts by waiting for every rank's p.Ap (each block adds them in
+ * rank order and derives alpha itself) and ends by storing r.r and r.z; pass C starts by waiting for those,
+ * repeats the stop test, updates p, stores the rows its neighbours need straight into their windows of p,
+ * and its last block raises the halo flags and advances the iteration counter.  Plain peer stores and local
+ * polling only; every wait is bounded (lapis_b200_pcg_p2p_set_wait_limit polls, 0 = the default of 2^22,
+ * about a second) and a wait that runs out marks the mailbox and sets the done flag instead of hanging.
+ * exchange == NULL (or d_mbox == NULL): one device, scalars derived locally -- lapis_b200_pcg_f64 is these
+ * three calls in a loop.  The initial exchange still uses push_scalars / wait_reduce / halo_push above.
+ * Replaces the loop body of examples/pcg_solve.py:74-98 (host loop TranslateToKokkosCpp.cpp:1512-1593). */
+typedef struct {
+  int me, world;            /* this rank and the number of ranks (at most 16) */
+  void *d_mbox;             /* this rank's mailbox (NULL: no exchange) */
+  const void *d_peer_mbox;  /* device array of `world` mailbox addresses, own included */
+  const void *d_halo_srcs;  /* device int array: ranks whose halo pieces pass A waits for */
+  int nsrc;
+  const void *d_pieces;     /* device array of {dst address, source offset, length, flag address} (halo_push) */
+  int npieces;              /* at most 32 */
+} lapis_b200_pcg_exchange;
+int lapis_b200_pcg_fused_spmv(void *d_work, lapis_b200_csr_t h, int64_t n_p, int64_t p_offset, double tol, uint64_t maxiter,
+                              const lapis_b200_pcg_exchange *exchange, void *stream);
+int lapis_b200_pcg_fused_update(void *d_work, int64_t n, int64_t n_p, int64_t p_offset, const double *d_dinv, double *d_x,
+                                double tol, uint64_t maxiter, const lapis_b200_pcg_exchange *exchange, void *stream);
+int lapis_b200_pcg_fused_direction(void *d_work, int64_t n, int64_t n_p, int64_t p_offset, double tol, uint64_t maxiter,
+                                   const lapis_b200_pcg_exchange *exchange, void *stream);
+int lapis_b200_pcg_p2p_set_wait_limit(uint32_t polls);
 /* Copies {done, iters, relres} to the host; synchronises `stream`. */
 int lapis_b200_pcg_status(void *d_work, int *done, uint64_t *iters, double *relres, void *stream);
 

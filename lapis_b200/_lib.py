@@ -73,6 +73,10 @@ _PROTOS = {
     "lapis_b200_pcg_p2p_wait_reduce": (c_int, [c_vp, c_vp, c_int, c_int, c_int, c_dbl, c_u64, c_vp]),
     "lapis_b200_pcg_p2p_halo_push": (c_int, [c_vp, c_i64, c_i64, c_vp, c_int, c_vp]),
     "lapis_b200_pcg_p2p_halo_wait": (c_int, [c_vp, c_vp, c_vp, c_int, c_vp]),
+    "lapis_b200_pcg_fused_spmv": (c_int, [c_vp, c_vp, c_i64, c_i64, c_dbl, c_u64, c_vp, c_vp]),
+    "lapis_b200_pcg_fused_update": (c_int, [c_vp, c_i64, c_i64, c_i64, c_vp, c_vp, c_dbl, c_u64, c_vp, c_vp]),
+    "lapis_b200_pcg_fused_direction": (c_int, [c_vp, c_i64, c_i64, c_i64, c_dbl, c_u64, c_vp, c_vp]),
+    "lapis_b200_pcg_p2p_set_wait_limit": (c_int, [ctypes.c_uint32]),
     "lapis_b200_pcg_status": (c_int, [c_vp, ctypes.POINTER(c_int), ctypes.POINTER(c_u64), ctypes.POINTER(c_dbl), c_vp]),
     "lapis_b200_read_matrix_market": (c_int, [ctypes.c_char_p, c_int, ctypes.POINTER(c_i64), ctypes.POINTER(c_i64),
                                               ctypes.POINTER(c_i64), ctypes.POINTER(c_vp), ctypes.POINTER(c_vp),
@@ -81,6 +85,14 @@ _PROTOS = {
     "lapis_b200_partition_rows": (c_int, [c_int, c_i64, c_vp, c_int, c_vp]),
     "lapis_b200_validate_csr_host": (c_int, [c_int, c_i64, c_i64, c_i64, c_vp, c_vp]),
 }
+
+
+
+class PcgExchange(ctypes.Structure):
+    """``lapis_b200_pcg_exchange`` of include/lapis_b200.h."""
+    _fields_ = [("me", c_int), ("world", c_int), ("d_mbox", c_vp), ("d_peer_mbox", c_vp), ("d_halo_srcs", c_vp),
+                ("nsrc", c_int), ("d_pieces", c_vp), ("npieces", c_int)]
+
 
 _LIB = None
 

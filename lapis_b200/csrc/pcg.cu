@@ -12,9 +12,12 @@
 //
 // r.z at the top of an iteration equals the r.z' computed at the end of the
 // previous one (same operands), so it is carried instead of recomputed.
-// Between the passes a single-block kernel adds the per-block partials in a fixed
-// order (results are run-to-run identical) and derives alpha / relres / beta and
-// the stop flag.  Every kernel returns at once when the stop flag is set, so the
+// The per-block partial sums of a pass are added in a fixed order (results are run-to-run
+// identical) by the block of that pass that finishes last, which also derives alpha / relres /
+// beta and the stop flag -- or, in a row-partitioned solve, hands the sums to the other ranks
+// (pcg_fuse.h): three launches per iteration.  (The step-level entry points further down keep
+// the older form with a single-block summing kernel between the passes, for callers that put
+// their own collectives there.)  Every kernel returns at once when the stop flag is set, so the
 // host can enqueue iterations ahead and only look at the flag now and then.
 //
 // Arithmetic follows the emitted element-wise bodies: axpby is (x*a) + (y*b) with
@@ -22,20 +25,18 @@
 #include <cmath>
 
 #include "common.h"
+#include "pcg_fuse.h"
 
 namespace lapis_b200 {
 
 int spmv_launch(const lapis_b200_csr *h, const double *x, double *y, int accumulate, const double *dotvec,
                 double *blk_partial, const int *skip_flag, cudaStream_t st);
+bool spmv_fuses_pcg_pass(const lapis_b200_csr *h);
+int spmv_launch_pcg_pass(const lapis_b200_csr *h, const double *x, double *y, const double *dotvec, double *blk_partial,
+                         const int *skip_flag, cudaStream_t st, const PcgExchange &ex);
 
 constexpr int VEC_THREADS = 256;
 constexpr int SUM_THREADS = 1024;
-
-// Device scalar block at the head of a PCG workspace (doubles, then flags).
-enum { SC_PAP = 0, SC_RR = 1, SC_RZNEW = 2, SC_RZ = 3, SC_INITRES = 4, SC_RELRES = 5, SC_ALPHA = 6, SC_BETA = 7, SC_COUNT = 8 };
-enum { FL_DONE = 0, FL_ITERS = 1, FL_COUNT = 2 };  // int64 each
-enum { DERIVE_NONE = 0, DERIVE_INIT = 1, DERIVE_ALPHA = 2, DERIVE_DECIDE = 3, DERIVE_ALPHA_MASKED = 4 };
-constexpr int SC_DMP2 = 11;  // header slot: sum of d * (mask*p)^2 of the masked-Laplacian operator
 
 __device__ __forceinline__ double block_sum_vec(double v, double *s_red) {
 #pragma unroll
@@ -51,36 +52,6 @@ __device__ __forceinline__ double block_sum_vec(double v, double *s_red) {
     for (int off = 16; off > 0; off >>= 1) t = __dadd_rn(t, __shfl_xor_sync(0xffffffffu, t, off));
   }
   return t;  // valid in thread 0
-}
-
-// Scalar recurrences of one PCG iteration (examples/pcg_solve.py:70-71, 78, 84-90, 96).
-// The iteration counter lives on the device (fl[FL_ITERS]) so that one iteration can be
-// captured in a CUDA graph and replayed.
-__device__ void pcg_derive(int kind, double *sc, long long *fl, double tol, unsigned long long maxiter) {
-  if (kind == DERIVE_INIT) {
-    sc[SC_INITRES] = sqrt(sc[SC_RR]);
-    sc[SC_RZ] = sc[SC_RZNEW];
-    fl[FL_DONE] = 0;
-    fl[FL_ITERS] = 0;
-  } else if (kind == DERIVE_ALPHA) {
-    sc[SC_ALPHA] = sc[SC_RZ] / sc[SC_PAP];
-  } else if (kind == DERIVE_ALPHA_MASKED) {
-    // p.(M (D - A) M p) = sum d (m p)^2 - (m p).(A (m p)): the two sums arrive separately
-    sc[SC_ALPHA] = sc[SC_RZ] / __dsub_rn(sc[SC_DMP2], sc[SC_PAP]);
-  } else if (kind == DERIVE_DECIDE) {
-    const double relres = sqrt(sc[SC_RR]) / sc[SC_INITRES];
-    sc[SC_RELRES] = relres;
-    const unsigned long long iter = (unsigned long long)fl[FL_ITERS] + 1;  // i starts at 1
-    fl[FL_ITERS] = (long long)iter;
-    const bool not_converged = relres > tol;  // ordered compare: NaN stops the loop
-    const bool below_maxiter = iter != maxiter;
-    if (!(not_converged && below_maxiter)) {
-      fl[FL_DONE] = 1;
-    } else {
-      sc[SC_BETA] = sc[SC_RZNEW] / sc[SC_RZ];
-      sc[SC_RZ] = sc[SC_RZNEW];
-    }
-  }
 }
 
 // out[c] = sum_b partials[c*nb + b] for c < count (count <= 2), fixed order; then
@@ -231,6 +202,164 @@ static PcgWork carve(void *d_work, int64_t n, int64_t n_p) {
   return w;
 }
 
+
+// ---- fused passes: heads that wait for the other ranks' sums, tails in the last block (pcg_fuse.h) --------
+static unsigned g_p2p_spin_limit = P2P_SPIN_LIMIT;  // polls per bounded wait; lapis_b200_pcg_p2p_set_wait_limit
+
+// Pass B.  alpha comes from the scalar block (no exchange) or from every rank's p.Ap (exchange).
+__global__ void __launch_bounds__(VEC_THREADS)
+pcg_update_fused_kernel(int64_t n, PcgExchange ex, const double *__restrict__ p, const double *__restrict__ Ap,
+                        const double *__restrict__ dinv, double *__restrict__ x, double *__restrict__ r,
+                        double *__restrict__ z, double *__restrict__ partials) {
+  __shared__ double s_red[VEC_THREADS / 32];
+  __shared__ double s_vals[3];
+  __shared__ int s_flag;
+  if (ex.fl[FL_DONE] != 0) return;
+  double alpha;
+  if (ex.mbox != nullptr) {
+    double pap, unused;
+    if (!pcg_wait_sums(ex, PH_A, s_vals, pap, unused)) return;
+    alpha = ex.sc[SC_RZ] / pap;
+  } else {
+    alpha = ex.sc[SC_ALPHA];
+  }
+  const double malpha = -alpha;
+  double rr = 0.0, rz = 0.0;
+  for (int64_t i = (int64_t)blockIdx.x * VEC_THREADS + threadIdx.x; i < n; i += (int64_t)gridDim.x * VEC_THREADS) {
+    const double xi = __dadd_rn(__dmul_rn(x[i], 1.0), __dmul_rn(p[i], alpha));
+    const double ri = __dadd_rn(__dmul_rn(r[i], 1.0), __dmul_rn(Ap[i], malpha));
+    const double zi = __dmul_rn(ri, dinv[i]);
+    x[i] = xi;
+    r[i] = ri;
+    z[i] = zi;
+    rr = __dadd_rn(rr, __dmul_rn(ri, ri));
+    rz = __dadd_rn(rz, __dmul_rn(ri, zi));
+  }
+  const double t0 = block_sum_vec(rr, s_red);
+  const double t1 = block_sum_vec(rz, s_red);
+  if (threadIdx.x == 0) {
+    partials[blockIdx.x] = t0;
+    partials[gridDim.x + blockIdx.x] = t1;
+  }
+  if (!pcg_last_block(pcg_tickets(ex.sc) + 1, gridDim.x, &s_flag)) return;
+  const double srr = pcg_block_total(partials, gridDim.x, s_red);
+  const double srz = pcg_block_total(partials + gridDim.x, gridDim.x, s_red);
+  if (threadIdx.x == 0) {
+    s_vals[0] = srr;
+    s_vals[1] = srz;
+    ex.sc[SC_RR] = srr;  // this rank's parts when the sums are exchanged
+    ex.sc[SC_RZNEW] = srz;
+    if (ex.mbox == nullptr) pcg_derive(DERIVE_DECIDE, ex.sc, ex.fl, ex.tol, ex.maxiter);
+    else ex.sc[SC_ALPHA] = alpha;
+  }
+  __syncthreads();
+  if (ex.mbox != nullptr) pcg_push_sums(ex, PH_B, s_vals[0], s_vals[1], pcg_seq(ex));
+}
+
+// Pass C.  Without exchange the stop test ran in pass B's tail.  With it every block repeats the test on
+// every rank's r.r and r.z; rows that neighbours need are also stored into their windows of p, and the block
+// that finishes last raises the halo flags and advances the iteration.
+constexpr int PCG_MAX_FUSED_PIECES = 32;
+__global__ void __launch_bounds__(VEC_THREADS)
+pcg_direction_fused_kernel(int64_t n, int64_t p_off, PcgExchange ex, const double *__restrict__ z, double *__restrict__ pw) {
+  __shared__ double s_red[VEC_THREADS / 32];
+  __shared__ double s_vals[3];
+  __shared__ int s_flag;
+  __shared__ HaloPiece s_pieces[PCG_MAX_FUSED_PIECES];
+  if (ex.fl[FL_DONE] != 0) return;
+  double *p = pw + p_off;
+  if (ex.mbox == nullptr) {
+    const double beta = ex.sc[SC_BETA];
+    for (int64_t i = (int64_t)blockIdx.x * VEC_THREADS + threadIdx.x; i < n; i += (int64_t)gridDim.x * VEC_THREADS)
+      p[i] = __dadd_rn(__dmul_rn(z[i], 1.0), __dmul_rn(p[i], beta));
+    return;
+  }
+  double rr, rznew;
+  if (!pcg_wait_sums(ex, PH_B, s_vals, rr, rznew)) return;
+  const double seq = pcg_seq(ex);
+  const double relres = sqrt(rr) / ex.sc[SC_INITRES];
+  const unsigned long long iter = (unsigned long long)ex.fl[FL_ITERS] + 1;  // i starts at 1
+  const bool go = (relres > ex.tol) && (iter != ex.maxiter);                // ordered compare: NaN stops the loop
+  const double rz_old = ex.sc[SC_RZ];
+  const double beta = rznew / rz_old;
+  if (go) {
+    for (int q = threadIdx.x; q < ex.npieces; q += VEC_THREADS) s_pieces[q] = ex.pieces[q];
+    __syncthreads();
+    for (int64_t i = (int64_t)blockIdx.x * VEC_THREADS + threadIdx.x; i < n; i += (int64_t)gridDim.x * VEC_THREADS) {
+      const double pi = __dadd_rn(__dmul_rn(z[i], 1.0), __dmul_rn(p[i], beta));
+      p[i] = pi;
+      const int64_t wi = p_off + i;  // position in this rank's window
+      for (int q = 0; q < ex.npieces; ++q) {
+        const int64_t d = wi - s_pieces[q].src_off;
+        if (d >= 0 && d < s_pieces[q].len) reinterpret_cast<double *>(s_pieces[q].dst_addr)[d] = pi;
+      }
+    }
+    __threadfence_system();  // this thread's stores into the neighbours' windows, before the block's ticket
+  }
+  if (!pcg_last_block(pcg_tickets(ex.sc) + 2, gridDim.x, &s_flag)) return;
+  (void)s_red;
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    ex.sc[SC_RR] = rr;
+    ex.sc[SC_RZNEW] = rznew;
+    ex.sc[SC_RELRES] = relres;
+    if (go) {
+      ex.sc[SC_BETA] = beta;
+      ex.sc[SC_RZ] = rznew;
+      for (int q = 0; q < ex.npieces; ++q)  // the pieces of the next iteration have arrived
+        *reinterpret_cast<volatile double *>(ex.pieces[q].flag_addr) = seq + 1.0;
+    } else {
+      ex.fl[FL_DONE] = 1;
+    }
+    __threadfence();
+    ex.fl[FL_ITERS] = (long long)iter;
+  }
+}
+
+// Pass A's head and tail as kernels of their own, around SpMV kernels that do not carry them.
+__global__ void pcg_halo_wait_kernel(PcgExchange ex) {
+  __shared__ int s_flag;
+  if (ex.fl[FL_DONE] != 0) return;
+  pcg_wait_halo(ex, &s_flag);
+}
+__global__ void __launch_bounds__(SUM_THREADS)
+pcg_pass_a_tail_kernel(PcgExchange ex, const double *__restrict__ blk_partial, int64_t nb) {
+  __shared__ double s_red[SUM_THREADS / 32];
+  if (ex.fl[FL_DONE] != 0) return;
+  pcg_tail_pass_a(ex, blk_partial, nb, s_red);
+}
+
+static PcgExchange make_exchange(const PcgWork &w, const lapis_b200_pcg_exchange *e, double tol, uint64_t maxiter) {
+  PcgExchange ex = {};
+  ex.sc = w.sc;
+  ex.fl = w.fl;
+  ex.world = 1;
+  ex.spin_limit = g_p2p_spin_limit;
+  ex.tol = tol;
+  ex.maxiter = maxiter;
+  if (e != nullptr && e->d_mbox != nullptr) {
+    ex.mbox = static_cast<double *>(e->d_mbox);
+    ex.peer_mbox = static_cast<const unsigned long long *>(e->d_peer_mbox);
+    ex.halo_srcs = static_cast<const int *>(e->d_halo_srcs);
+    ex.pieces = static_cast<const HaloPiece *>(e->d_pieces);
+    ex.me = e->me;
+    ex.world = e->world;
+    ex.nsrc = e->nsrc;
+    ex.npieces = e->npieces;
+  }
+  return ex;
+}
+
+static int check_exchange(const lapis_b200_pcg_exchange *e, const char *what) {
+  if (e == nullptr || e->d_mbox == nullptr) return LAPIS_OK;
+  if (e->world < 1 || e->world > P2P_MAXW || e->me < 0 || e->me >= e->world || e->d_peer_mbox == nullptr || e->nsrc < 0 ||
+      e->nsrc > 32 || e->npieces < 0 || e->npieces > PCG_MAX_FUSED_PIECES || (e->nsrc > 0 && e->d_halo_srcs == nullptr) ||
+      (e->npieces > 0 && e->d_pieces == nullptr))
+    return fail(LAPIS_EBADARG, "%s: bad exchange description (up to %d ranks, 32 halo sources, %d halo pieces)", what,
+                P2P_MAXW, PCG_MAX_FUSED_PIECES);
+  return LAPIS_OK;
+}
+
 }  // namespace lapis_b200
 
 using namespace lapis_b200;
@@ -358,6 +487,57 @@ extern "C" int lapis_b200_pcg_step_direction(void *d_work, int64_t n, int64_t n_
   return LAPIS_OK;
 }
 
+// ---- fused step entry points ------------------------------------------------------------------------------
+extern "C" int lapis_b200_pcg_p2p_set_wait_limit(uint32_t polls) {
+  clear_error();
+  g_p2p_spin_limit = polls == 0 ? P2P_SPIN_LIMIT : polls;
+  return LAPIS_OK;
+}
+
+extern "C" int lapis_b200_pcg_fused_spmv(void *d_work, lapis_b200_csr_t h, int64_t n_p, int64_t p_offset, double tol,
+                                         uint64_t maxiter, const lapis_b200_pcg_exchange *exchange, void *stream) {
+  clear_error();
+  if (d_work == nullptr || h == nullptr) return fail(LAPIS_EBADARG, "pcg_fused_spmv: null argument");
+  LAPIS_TRY(check_exchange(exchange, "pcg_fused_spmv"));
+  const int64_t n = h->nrows;
+  PcgWork w = carve(d_work, n, n_p);
+  cudaStream_t st = as_stream(stream);
+  const PcgExchange ex = make_exchange(w, exchange, tol, maxiter);
+  const int *skip = reinterpret_cast<const int *>(w.fl);  // low word of the little-endian int64 flag
+  if (spmv_fuses_pcg_pass(h)) return spmv_launch_pcg_pass(h, w.p, w.Ap, w.p + p_offset, h->blk_partial, skip, st, ex);
+  if (ex.mbox != nullptr && ex.nsrc > 0) pcg_halo_wait_kernel<<<1, 32, 0, st>>>(ex);
+  LAPIS_TRY(spmv_launch(h, w.p, w.Ap, 0, w.p + p_offset, h->blk_partial, skip, st));
+  pcg_pass_a_tail_kernel<<<1, SUM_THREADS, 0, st>>>(ex, h->blk_partial, h->nblk);
+  LAPIS_CUDA_TRY(cudaGetLastError());
+  return LAPIS_OK;
+}
+
+extern "C" int lapis_b200_pcg_fused_update(void *d_work, int64_t n, int64_t n_p, int64_t p_offset, const double *d_dinv,
+                                           double *d_x, double tol, uint64_t maxiter,
+                                           const lapis_b200_pcg_exchange *exchange, void *stream) {
+  clear_error();
+  if (d_work == nullptr) return fail(LAPIS_EBADARG, "pcg_fused_update: null workspace");
+  LAPIS_TRY(check_exchange(exchange, "pcg_fused_update"));
+  PcgWork w = carve(d_work, n, n_p);
+  const PcgExchange ex = make_exchange(w, exchange, tol, maxiter);
+  pcg_update_fused_kernel<<<w.grid, VEC_THREADS, 0, as_stream(stream)>>>(n, ex, w.p + p_offset, w.Ap, d_dinv, d_x, w.r, w.z,
+                                                                         w.partials);
+  LAPIS_CUDA_TRY(cudaGetLastError());
+  return LAPIS_OK;
+}
+
+extern "C" int lapis_b200_pcg_fused_direction(void *d_work, int64_t n, int64_t n_p, int64_t p_offset, double tol,
+                                              uint64_t maxiter, const lapis_b200_pcg_exchange *exchange, void *stream) {
+  clear_error();
+  if (d_work == nullptr) return fail(LAPIS_EBADARG, "pcg_fused_direction: null workspace");
+  LAPIS_TRY(check_exchange(exchange, "pcg_fused_direction"));
+  PcgWork w = carve(d_work, n, n_p);
+  const PcgExchange ex = make_exchange(w, exchange, tol, maxiter);
+  pcg_direction_fused_kernel<<<w.grid, VEC_THREADS, 0, as_stream(stream)>>>(n, p_offset, ex, w.z, w.p);
+  LAPIS_CUDA_TRY(cudaGetLastError());
+  return LAPIS_OK;
+}
+
 // Reads {done, iters} and relres back (synchronises the stream).
 extern "C" int lapis_b200_pcg_status(void *d_work, int *done, uint64_t *iters, double *relres, void *stream) {
   clear_error();
@@ -400,14 +580,15 @@ extern "C" int lapis_b200_pcg_f64(lapis_b200_csr_t h, const double *d_b, const d
   const uint64_t limit = maxiter == 0 ? (1ull << 31) : maxiter;
   const uint64_t check_every = 16;
   for (uint64_t i = 1; status == LAPIS_OK && !done && i <= limit; ++i) {
-    status = lapis_b200_pcg_step_spmv(work, h, n, 0, 1, st);
-    if (status == LAPIS_OK)
-      status = lapis_b200_pcg_step_update(work, n, n, 0, d_dinv, d_x, 1, tol, maxiter, st);
-    if (status == LAPIS_OK) status = lapis_b200_pcg_step_direction(work, n, n, 0, st);
+    status = lapis_b200_pcg_fused_spmv(work, h, n, 0, tol, maxiter, nullptr, st);
+    if (status == LAPIS_OK) status = lapis_b200_pcg_fused_update(work, n, n, 0, d_dinv, d_x, tol, maxiter, nullptr, st);
+    if (status == LAPIS_OK) status = lapis_b200_pcg_fused_direction(work, n, n, 0, tol, maxiter, nullptr, st);
     if (status == LAPIS_OK && (i % check_every == 0 || i == limit))
       status = lapis_b200_pcg_status(work, &done, &it, &rel, st);
   }
   if (status == LAPIS_OK && !done) status = lapis_b200_pcg_status(work, &done, &it, &rel, st);
+  // a persistent SpMV block whose bounded wait gave up leaves Ap incomplete: the solve is not valid then
+  if (status == LAPIS_OK) status = lapis_b200_spmv_status(st);
   cudaFree(work);
   if (status != LAPIS_OK) return status;
   if (iters) *iters = it;
@@ -437,32 +618,9 @@ extern "C" int lapis_b200_pcg_f64(lapis_b200_csr_t h, const double *d_b, const d
 // ---------------------------------------------------------------------------------------------
 namespace lapis_b200 {
 
-constexpr int P2P_MAXW = 16;
-constexpr int P2P_HALO = 4 * P2P_MAXW * 4;
-constexpr int P2P_ERR = P2P_HALO + P2P_MAXW;
-constexpr int P2P_MBOX_DOUBLES = 512;
-constexpr int SC_EPOCH = 10;                   // workspace header slot holding epoch * 2^32
-constexpr unsigned P2P_SPIN_LIMIT = 1u << 22;  // polls with a short sleep: a few seconds at most
-enum { PH_A = 0, PH_B = 1, PH_INIT = 2 };
-
-struct HaloPiece {  // one contiguous piece of p this rank provides to a peer
-  unsigned long long dst_addr;   // address of the first destination element in the peer's p window
-  long long src_off;             // offset of the first source element in this rank's p window
-  long long len;
-  unsigned long long flag_addr;  // address of this rank's halo flag in the peer's mailbox
-};
-
 // Slot row of a phase: the initial exchange alternates between two rows by the parity of the epoch.
 __device__ __forceinline__ int p2p_slot_row(int phase, double base_seq) {
   return phase == PH_INIT ? PH_INIT + (int)((long long)(base_seq * (1.0 / 4294967296.0)) & 1) : phase;
-}
-
-__device__ __forceinline__ bool p2p_wait_equal(const volatile double *flag, double expected) {
-  for (unsigned i = 0; i < P2P_SPIN_LIMIT; ++i) {
-    if (*flag == expected) return true;
-    __nanosleep(200);
-  }
-  return false;
 }
 
 __global__ void p2p_push_scalars_kernel(const double *__restrict__ sc, const long long *__restrict__ fl, int phase, int me,
@@ -482,14 +640,14 @@ __global__ void p2p_push_scalars_kernel(const double *__restrict__ sc, const lon
 }
 
 __global__ void p2p_wait_reduce_kernel(double *sc, long long *fl, double *mbox, int phase, int world, int derive,
-                                       double tol, unsigned long long maxiter) {
+                                       double tol, unsigned long long maxiter, unsigned spin_limit) {
   const int j = threadIdx.x;  // one warp
   const double base_seq = sc[SC_EPOCH];
   if (phase != PH_INIT && fl[FL_DONE] != 0) return;
   const double expected = base_seq + (phase == PH_INIT ? 0.0 : (double)(fl[FL_ITERS] + 1));
   const int row = p2p_slot_row(phase, base_seq);
   bool ok = true;
-  if (j < world) ok = p2p_wait_equal(mbox + (row * P2P_MAXW + j) * 4 + 2, expected);
+  if (j < world) ok = p2p_wait_equal(mbox + (row * P2P_MAXW + j) * 4 + 2, expected, spin_limit);
   const bool all_ok = __all_sync(0xffffffffu, ok);
   if (j != 0) return;
   if (!all_ok) {  // a peer never delivered: stop the solve and let the host see why
@@ -526,13 +684,14 @@ p2p_halo_push_kernel(const double *__restrict__ p_window, const double *__restri
   if (threadIdx.x == 0) *reinterpret_cast<volatile double *>(pc.flag_addr) = base_seq + (double)(fl[FL_ITERS] + 1);
 }
 
-__global__ void p2p_halo_wait_kernel(const double *sc, long long *fl, double *mbox, const int *__restrict__ srcs, int nsrc) {
+__global__ void p2p_halo_wait_kernel(const double *sc, long long *fl, double *mbox, const int *__restrict__ srcs, int nsrc,
+                                     unsigned spin_limit) {
   const int j = threadIdx.x;  // one warp
   if (fl[FL_DONE] != 0) return;
   const double base_seq = sc[SC_EPOCH];
   const double expected = base_seq + (double)(fl[FL_ITERS] + 1);
   bool ok = true;
-  if (j < nsrc) ok = p2p_wait_equal(mbox + P2P_HALO + srcs[j], expected);
+  if (j < nsrc) ok = p2p_wait_equal(mbox + P2P_HALO + srcs[j], expected, spin_limit);
   const bool all_ok = __all_sync(0xffffffffu, ok);
   if (j == 0 && !all_ok) {
     mbox[P2P_ERR] = 9.0;
@@ -613,7 +772,8 @@ extern "C" int lapis_b200_pcg_p2p_wait_reduce(void *d_work, void *d_mbox, int ph
     return fail(LAPIS_EBADARG, "pcg_p2p_wait_reduce: bad arguments");
   double *base = static_cast<double *>(d_work);
   p2p_wait_reduce_kernel<<<1, 32, 0, as_stream(stream)>>>(base, reinterpret_cast<long long *>(base + SC_COUNT),
-                                                          static_cast<double *>(d_mbox), phase, world, derive, tol, maxiter);
+                                                          static_cast<double *>(d_mbox), phase, world, derive, tol, maxiter,
+                                                          g_p2p_spin_limit);
   LAPIS_CUDA_TRY(cudaGetLastError());
   return LAPIS_OK;
 }
@@ -637,7 +797,8 @@ extern "C" int lapis_b200_pcg_p2p_halo_wait(void *d_work, void *d_mbox, const vo
     return fail(LAPIS_EBADARG, "pcg_p2p_halo_wait: bad arguments");
   double *base = static_cast<double *>(d_work);
   p2p_halo_wait_kernel<<<1, 32, 0, as_stream(stream)>>>(base, reinterpret_cast<long long *>(base + SC_COUNT),
-                                                        static_cast<double *>(d_mbox), static_cast<const int *>(d_srcs), nsrc);
+                                                        static_cast<double *>(d_mbox), static_cast<const int *>(d_srcs), nsrc,
+                                                        g_p2p_spin_limit);
   LAPIS_CUDA_TRY(cudaGetLastError());
   return LAPIS_OK;
 }
@@ -845,6 +1006,7 @@ extern "C" int lapis_b200_mht_f64(lapis_b200_csr_t h, const double *d_mask, cons
   cudaFree(buf);
   if (status != LAPIS_OK) return status;
   if (e != cudaSuccess) return fail(LAPIS_ECUDA, "mht: %s", cudaGetErrorString(e));
+  LAPIS_TRY(lapis_b200_spmv_status(st));  // a persistent SpMV block that gave up leaves its output incomplete
   if (iters2) iters2[0] = it[0], iters2[1] = it[1];
   if (relres2) relres2[0] = rel[0], relres2[1] = rel[1];
   return LAPIS_OK;

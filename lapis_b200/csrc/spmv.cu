@@ -36,6 +36,7 @@
 #include <cstring>
 
 #include "common.h"
+#include "pcg_fuse.h"
 
 namespace lapis_b200 {
 
@@ -924,14 +925,19 @@ __device__ __forceinline__ double row_piece_sum(const I *__restrict__ crd, const
   return acc;
 }
 
-template <typename I, bool FUSE_DOT>
+// PCG_FUSED: the kernel is pass A of a PCG iteration: its blocks first wait for the neighbours' halo pieces of x
+// (row-partitioned solves), and the block that finishes last turns the per-block partial sums into p.Ap and
+// derives alpha or hands the sum to the other ranks (pcg_fuse.h).
+template <typename I, bool FUSE_DOT, bool PCG_FUSED>
 __global__ void __launch_bounds__(256)
 spmv_rowthread_kernel(const I *__restrict__ pos, const I *__restrict__ crd, const double *__restrict__ val,
                       int64_t abase, int64_t nrows, int64_t ntiles, const double *__restrict__ x,
                       double *__restrict__ y, int accumulate, const double *__restrict__ dotvec,
-                      double *__restrict__ blk_partial, const int *__restrict__ skip_flag) {
+                      double *__restrict__ blk_partial, const int *__restrict__ skip_flag, PcgExchange ex) {
   __shared__ double s_red[8];
+  __shared__ int s_flag;
   if (skip_flag != nullptr && *skip_flag != 0) return;
+  if (PCG_FUSED && ex.mbox != nullptr && !pcg_wait_halo(ex, &s_flag)) return;
   double dot_local = 0.0;
   for (int64_t tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
     const int64_t row = tile * 256 + threadIdx.x;
@@ -961,6 +967,7 @@ spmv_rowthread_kernel(const I *__restrict__ pos, const I *__restrict__ crd, cons
   if (FUSE_DOT) {
     const double t = block_sum(dot_local, s_red);
     if (threadIdx.x == 0) blk_partial[blockIdx.x] = t;
+    if (PCG_FUSED && pcg_last_block(pcg_tickets(ex.sc) + 0, gridDim.x, &s_flag)) pcg_tail_pass_a(ex, blk_partial, gridDim.x, s_red);
   }
 }
 
@@ -1202,10 +1209,18 @@ static int launch_pipe(const lapis_b200_csr *h, int ctas_per_sm, const double *x
   return LAPIS_OK;
 }
 
+// Whether spmv_launch will run the one-thread-per-row kernel for this handle (the variant that can carry the
+// head and tail of a PCG iteration's first pass).
+static bool uses_rowthread(const lapis_b200_csr *h) {
+  SpmvVariant v = spmv_override();
+  if (v.threads == 0) v = h->tuned_threads != 0 ? SpmvVariant{h->tuned_threads, h->tuned_minb, h->tuned_hint} : SPMV_DEFAULT;
+  return v.threads == 1 && h->max_row_len >= 0 && h->max_row_len <= SPMV_ROWTHREAD_MAX_LEN;
+}
+
 template <typename I>
 static int launch_spmv(const lapis_b200_csr *h, const double *x, double *y, int accumulate,
                        const double *dotvec, double *blk_partial, const int *skip_flag,
-                       cudaStream_t st) {
+                       cudaStream_t st, const PcgExchange *ex) {
   SpmvVariant v = spmv_override();
   if (v.threads == 0) v = h->tuned_threads != 0 ? SpmvVariant{h->tuned_threads, h->tuned_minb, h->tuned_hint} : SPMV_DEFAULT;
   if (v.threads == 1) {
@@ -1215,17 +1230,22 @@ static int launch_spmv(const lapis_b200_csr *h, const double *x, double *y, int 
       const I *pos = static_cast<const I *>(h->pos);
       const I *crd = static_cast<const I *>(h->crd);
       const int64_t abase = h->base & ~(int64_t)3, ntiles = (h->nrows + 255) / 256;
-      if (dotvec != nullptr)
-        spmv_rowthread_kernel<I, true><<<(unsigned)h->nblk, 256, 0, st>>>(pos, crd, h->val, abase, h->nrows, ntiles, x, y,
-                                                                          accumulate, dotvec, blk_partial, skip_flag);
+      const PcgExchange none = {};
+      if (dotvec != nullptr && ex != nullptr)
+        spmv_rowthread_kernel<I, true, true><<<(unsigned)h->nblk, 256, 0, st>>>(pos, crd, h->val, abase, h->nrows, ntiles, x, y,
+                                                                                accumulate, dotvec, blk_partial, skip_flag, *ex);
+      else if (dotvec != nullptr)
+        spmv_rowthread_kernel<I, true, false><<<(unsigned)h->nblk, 256, 0, st>>>(pos, crd, h->val, abase, h->nrows, ntiles, x, y,
+                                                                                 accumulate, dotvec, blk_partial, skip_flag, none);
       else
-        spmv_rowthread_kernel<I, false><<<(unsigned)h->nblk, 256, 0, st>>>(pos, crd, h->val, abase, h->nrows, ntiles, x, y,
-                                                                           accumulate, nullptr, nullptr, skip_flag);
+        spmv_rowthread_kernel<I, false, false><<<(unsigned)h->nblk, 256, 0, st>>>(pos, crd, h->val, abase, h->nrows, ntiles, x, y,
+                                                                                  accumulate, nullptr, nullptr, skip_flag, none);
       LAPIS_CUDA_TRY(cudaGetLastError());
       return LAPIS_OK;
     }
     v = SPMV_DEFAULT;
   }
+  if (ex != nullptr) return fail(LAPIS_EBADARG, "spmv: the fused PCG pass needs the one-thread-per-row kernel");
   if (v.threads == 4) {
     // one warp per chunk: its 32-byte loads need val and crd 32-byte aligned; otherwise the default kernel runs
     if (((reinterpret_cast<uintptr_t>(h->val) | reinterpret_cast<uintptr_t>(h->crd)) & 31) != 0) v = SPMV_DEFAULT;
@@ -1311,8 +1331,17 @@ int spmv_launch(const lapis_b200_csr *h, const double *x, double *y, int accumul
                 const double *dotvec, double *blk_partial, const int *skip_flag, cudaStream_t st) {
   if (h->nrows == 0) return LAPIS_OK;
   if (h->idx_bytes == 4)
-    return launch_spmv<int32_t>(h, x, y, accumulate, dotvec, blk_partial, skip_flag, st);
-  return launch_spmv<int64_t>(h, x, y, accumulate, dotvec, blk_partial, skip_flag, st);
+    return launch_spmv<int32_t>(h, x, y, accumulate, dotvec, blk_partial, skip_flag, st, nullptr);
+  return launch_spmv<int64_t>(h, x, y, accumulate, dotvec, blk_partial, skip_flag, st, nullptr);
+}
+
+// Pass A of a PCG iteration with its head and tail inside the SpMV kernel; only for handles on which
+// spmv_fuses_pcg_pass() is true.
+bool spmv_fuses_pcg_pass(const lapis_b200_csr *h) { return h->nrows > 0 && uses_rowthread(h); }
+int spmv_launch_pcg_pass(const lapis_b200_csr *h, const double *x, double *y, const double *dotvec, double *blk_partial,
+                         const int *skip_flag, cudaStream_t st, const PcgExchange &ex) {
+  if (h->idx_bytes == 4) return launch_spmv<int32_t>(h, x, y, 0, dotvec, blk_partial, skip_flag, st, &ex);
+  return launch_spmv<int64_t>(h, x, y, 0, dotvec, blk_partial, skip_flag, st, &ex);
 }
 
 template <typename I, int WARPS, int UNROLL>

@@ -134,7 +134,7 @@ class DistPcg:
     row-partitioned matrix.  Construct on every rank with the same host CSR, b and dinv."""
 
     def __init__(self, pos, crd, val, shape, b, dinv, device, group=None, use_graph: bool = True, comm: str = "p2p",
-                 transport_on_one_rank: bool = False, tune: bool = True):
+                 transport_on_one_rank: bool = False, tune: bool = True, fused: bool = True):
         from ._lib import check, load
         from .device import CsrMatrix
         self._check, self._lib = check, load()
@@ -143,6 +143,9 @@ class DistPcg:
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.device = torch.device(device)
         self.use_graph = use_graph
+        # fused: one iteration is three launches (sums and exchanges inside the passes); False keeps the
+        # older form with separate summing / exchange kernels between the passes
+        self.fused = fused
         n_global = int(shape[0])
         if shape[0] != shape[1]:
             raise ValueError("pcg: matrix is not square")
@@ -216,6 +219,12 @@ class DistPcg:
         srcs = sorted({owner for owner, _, _ in self.halo.recv})
         self._nsrc = len(srcs)
         self._srcs = torch.tensor(srcs if srcs else [0], dtype=torch.int32, device=self.device)
+        # the fused passes keep at most 32 halo pieces in shared memory and poll at most 32 sources; the ranks
+        # decide together, so that all of them run the same form of the iteration
+        fits = [self._npieces <= 32 and self._nsrc <= 32] * self.world
+        if self.world > 1:
+            dist.all_gather_object(fits, fits[0], group=self.group)
+        self.fused = self.fused and all(fits)
         if self.world > 1:
             dist.barrier(group=self.group)  # every rank has mapped every buffer before anyone pushes
 
@@ -248,8 +257,30 @@ class DistPcg:
         if self.world > 1:
             dist.all_reduce(t, op=dist.ReduceOp.SUM, group=self.group)
 
+    def _exchange(self):
+        """The exchange description the fused passes take (NULL on one rank without the transport)."""
+        if self.comm != "p2p":
+            return None
+        ex = getattr(self, "_exchange_struct", None)
+        if ex is None:
+            from ._lib import PcgExchange
+            ex = PcgExchange(self.rank, self.world, ctypes.c_void_p(self._mbox_buf.ptr),
+                             ctypes.c_void_p(self._peer_mbox.data_ptr()), ctypes.c_void_p(self._srcs.data_ptr()), self._nsrc,
+                             ctypes.c_void_p(self._pieces.data_ptr()), self._npieces)
+            self._exchange_struct = ex
+        return ctypes.byref(ex)
+
     def _iteration(self, tol: float, maxiter: int):
         lib, check, w = self._lib, self._check, ctypes.c_void_p(self.work.data_ptr())
+        if self.fused and self.comm in ("p2p", "none"):
+            # three launches: the sums are added in the last block of each pass and, with the peer-to-peer
+            # transport, the exchanges happen inside the passes
+            ex = self._exchange()
+            check(lib.lapis_b200_pcg_fused_spmv(w, self.matrix.handle, self.n_p, self.p_off, tol, maxiter, ex, self._stream()))
+            check(lib.lapis_b200_pcg_fused_update(w, self.n, self.n_p, self.p_off, ctypes.c_void_p(self.dinv.data_ptr()),
+                                                  ctypes.c_void_p(self.x.data_ptr()), tol, maxiter, ex, self._stream()))
+            check(lib.lapis_b200_pcg_fused_direction(w, self.n, self.n_p, self.p_off, tol, maxiter, ex, self._stream()))
+            return
         single = 1 if self.comm == "none" else 0
         p2p = self.comm == "p2p"
         if p2p:

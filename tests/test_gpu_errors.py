@@ -101,3 +101,45 @@ def test_results_of_pcg_stay_valid_until_finalize():
     x2, it2, _ = m.pcg(d["pos"], d["crd"], d["val"], spec, d["b"], d["dinv"], 0.0, 9)
     assert it1 == 5 and it2 == 9
     assert np.array_equal(x1, keep) and not np.array_equal(x1, x2)   # the first result was not overwritten
+
+
+@pytest.mark.parametrize("fused", [True, False], ids=["fused", "separate_kernels"])
+def test_a_wait_on_a_peer_that_never_delivers_runs_out(fused):
+    """Failure detection of the row-partitioned solver, made on purpose without faulting anything: one rank
+    with the peer-to-peer transport switched on (it is its own only peer) is told to expect a halo piece from
+    a source that nobody provides.  The wait in front of the SpMV pass is bounded; with the bound lowered to
+    about a thousand polls it runs out at once, the kernel writes its mark into the mailbox, sets the solver's
+    done flag and returns, every later kernel of the iteration returns at its entry, and ``solve`` raises.
+    The CUDA context stays usable.  (The emitted code would abort the process: LAPISSupport.hpp:76-89.)"""
+    assert torch.cuda.is_available(), "needs a CUDA device"
+    from lapis_b200 import workloads as w
+    from lapis_b200._lib import check
+    from lapis_b200.dist import DistPcg
+    dev = torch.device("cuda:0")
+    p = w.pcg_laplacian(48)
+    m = p["shape"][0]
+    lib = load()
+    check(lib.lapis_b200_pcg_p2p_set_wait_limit(1 << 10))
+    try:
+        solver = DistPcg(p["pos"], p["crd"], p["val"], (m, m), p["b"], p["dinv"], dev, use_graph=False, comm="p2p",
+                         transport_on_one_rank=True, fused=fused)
+        assert solver.comm == "p2p" and solver._nsrc == 0
+        # sanity: with nothing to wait for, the same solver runs
+        _, iters, _ = solver.solve(0.0, 5, check_every=5)
+        assert iters == 5 and solver.comm_error() == 0.0
+        # now expect a halo piece from rank 0 (itself) that no pass ever stores
+        solver._srcs = torch.tensor([0], dtype=torch.int32, device=dev)
+        solver._nsrc = 1
+        solver._exchange_struct = None
+        with pytest.raises(RuntimeError, match="did not deliver in time"):
+            solver.solve(0.0, 5, check_every=5)
+        assert solver.comm_error() == 9.0          # the halo wait's mark
+        assert int(solver.flags[0].item()) == 1    # the done flag stopped the iteration
+        assert int(solver.flags[1].item()) == 0    # no iteration completed
+    finally:
+        check(lib.lapis_b200_pcg_p2p_set_wait_limit(0))
+    # the context is intact: an ordinary solve on the same device still works
+    from lapis_b200.device import CsrMatrix
+    A = CsrMatrix.from_host(p["pos"], p["crd"], p["val"], (m, m), dev)
+    x, iters, relres = A.pcg(torch.as_tensor(p["b"]).to(dev), torch.as_tensor(p["dinv"]).to(dev), 0.0, 10)
+    assert iters == 10 and np.isfinite(relres)

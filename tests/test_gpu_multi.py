@@ -53,6 +53,11 @@ def _worker(rank, world, port, out_dir):
             x, iters, relres = solver.solve(0.0, 40, check_every=7)
             np.savez(os.path.join(out_dir, f"pcg{rank}_{comm}_{int(use_graph)}_again.npz"), x=x.cpu().numpy(),
                      r0=solver.halo.r0, r1=solver.halo.r1, iters=iters, relres=relres)
+    # the older form of the iteration (separate summing / exchange kernels between the passes)
+    solver = DistPcg(p["pos"], p["crd"], p["val"], (m, m), p["b"], p["dinv"], dev, use_graph=True, comm="p2p", fused=False)
+    x, iters, relres = solver.solve(0.0, 40, check_every=10)
+    np.savez(os.path.join(out_dir, f"pcg{rank}_unfused.npz"), x=x.cpu().numpy(), r0=solver.halo.r0, r1=solver.halo.r1,
+             iters=iters, relres=relres)
     # a converging solve: every rank must stop in the same iteration
     solver = DistPcg(p["pos"], p["crd"], p["val"], (m, m), p["b"], p["dinv"], dev, use_graph=True, comm="p2p")
     x, iters, relres = solver.solve(1e-8, 2000, check_every=16)
@@ -89,7 +94,7 @@ def test_two_gpu_spmv_and_pcg(tmp_path):
     p = w.pcg_laplacian(96)
     xo, io, ro = oracle.pcg(p["pos"], p["crd"], p["val"], p["b"], p["dinv"], 0.0, 40)
     results = {}
-    for tag in [f"{c}_{g}{a}" for c in ("p2p", "nccl") for g in (0, 1) for a in ("", "_again")]:
+    for tag in [f"{c}_{g}{a}" for c in ("p2p", "nccl") for g in (0, 1) for a in ("", "_again")] + ["unfused"]:
         x = np.zeros(96 * 96)
         for rank in range(world):
             f = np.load(tmp_path / f"pcg{rank}_{tag}.npz")
