@@ -285,16 +285,35 @@ pcg_direction_fused_kernel(int64_t n, int64_t p_off, PcgExchange ex, const doubl
   if (go) {
     for (int q = threadIdx.x; q < ex.npieces; q += VEC_THREADS) s_pieces[q] = ex.pieces[q];
     __syncthreads();
-    for (int64_t i = (int64_t)blockIdx.x * VEC_THREADS + threadIdx.x; i < n; i += (int64_t)gridDim.x * VEC_THREADS) {
-      const double pi = __dadd_rn(__dmul_rn(z[i], 1.0), __dmul_rn(p[i], beta));
-      p[i] = pi;
-      const int64_t wi = p_off + i;  // position in this rank's window
-      for (int q = 0; q < ex.npieces; ++q) {
-        const int64_t d = wi - s_pieces[q].src_off;
-        if (d >= 0 && d < s_pieces[q].len) reinterpret_cast<double *>(s_pieces[q].dst_addr)[d] = pi;
+    bool stored_to_peer = false;
+    // four elements per round, all loads first: the stores into the neighbours' windows may alias anything as
+    // far as the compiler knows, so it would not overlap the loads of successive elements by itself
+    const int64_t stride = (int64_t)gridDim.x * VEC_THREADS;
+    for (int64_t i0 = (int64_t)blockIdx.x * VEC_THREADS + threadIdx.x; i0 < n; i0 += 4 * stride) {
+      double zi[4], po[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int64_t i = i0 + k * stride;
+        zi[k] = i < n ? z[i] : 0.0;
+        po[k] = i < n ? p[i] : 0.0;
+      }
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int64_t i = i0 + k * stride;
+        if (i >= n) break;
+        const double pi = __dadd_rn(__dmul_rn(zi[k], 1.0), __dmul_rn(po[k], beta));
+        p[i] = pi;
+        const int64_t wi = p_off + i;  // position in this rank's window
+        for (int q = 0; q < ex.npieces; ++q) {
+          const int64_t d = wi - s_pieces[q].src_off;
+          if (d >= 0 && d < s_pieces[q].len) {
+            reinterpret_cast<double *>(s_pieces[q].dst_addr)[d] = pi;
+            stored_to_peer = true;
+          }
+        }
       }
     }
-    __threadfence_system();  // this thread's stores into the neighbours' windows, before the block's ticket
+    if (stored_to_peer) __threadfence_system();  // this thread's stores into a neighbour's window, before the block's ticket
   }
   if (!pcg_last_block(pcg_tickets(ex.sc) + 2, gridDim.x, &s_flag)) return;
   (void)s_red;
@@ -533,7 +552,10 @@ extern "C" int lapis_b200_pcg_fused_direction(void *d_work, int64_t n, int64_t n
   LAPIS_TRY(check_exchange(exchange, "pcg_fused_direction"));
   PcgWork w = carve(d_work, n, n_p);
   const PcgExchange ex = make_exchange(w, exchange, tol, maxiter);
-  pcg_direction_fused_kernel<<<w.grid, VEC_THREADS, 0, as_stream(stream)>>>(n, p_offset, ex, w.z, w.p);
+  if (ex.mbox == nullptr)  // the stop test and beta are in the scalar block already: the plain pass
+    pcg_direction_kernel<<<w.grid, VEC_THREADS, 0, as_stream(stream)>>>(n, w.sc, w.fl, w.z, w.p + p_offset);
+  else
+    pcg_direction_fused_kernel<<<w.grid, VEC_THREADS, 0, as_stream(stream)>>>(n, p_offset, ex, w.z, w.p);
   LAPIS_CUDA_TRY(cudaGetLastError());
   return LAPIS_OK;
 }

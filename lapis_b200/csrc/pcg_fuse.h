@@ -87,15 +87,15 @@ __device__ __forceinline__ bool pcg_wait_halo(const PcgExchange &ex, int *s_flag
     bool ok = true;
     if ((int)threadIdx.x < ex.nsrc) ok = p2p_wait_equal(ex.mbox + P2P_HALO + ex.halo_srcs[threadIdx.x], expected, ex.spin_limit);
     const bool all_ok = __all_sync(0xffffffffu, ok);
+    if (all_ok) __threadfence_system();  // the pieces were stored before their flag; the barrier below orders the
+                                         // other warps' reads behind this one
     if (threadIdx.x == 0) {
       if (!all_ok) pcg_give_up(ex, 9.0);
       *s_flag = all_ok ? 1 : 0;
     }
   }
   __syncthreads();
-  const bool go = *s_flag != 0;
-  if (go) __threadfence_system();  // the pieces were stored before their flag
-  return go;
+  return *s_flag != 0;
 }
 
 // Head of passes B and C on several ranks: warp 0 waits for every rank's values of `phase` and adds them in
@@ -103,23 +103,23 @@ __device__ __forceinline__ bool pcg_wait_halo(const PcgExchange &ex, int *s_flag
 // s_vals: three doubles of shared memory.
 __device__ __forceinline__ bool pcg_wait_sums(const PcgExchange &ex, int phase, double *s_vals, double &v0, double &v1) {
   if (threadIdx.x < 32) {
+    const int j = threadIdx.x;
     const double expected = pcg_seq(ex);
+    const volatile double *slot = ex.mbox + (phase * P2P_MAXW + (j < ex.world ? j : 0)) * 4;
     bool ok = true;
-    if ((int)threadIdx.x < ex.world)
-      ok = p2p_wait_equal(ex.mbox + (phase * P2P_MAXW + (int)threadIdx.x) * 4 + 2, expected, ex.spin_limit);
+    if (j < ex.world) ok = p2p_wait_equal(slot + 2, expected, ex.spin_limit);
     const bool all_ok = __all_sync(0xffffffffu, ok);
-    if (threadIdx.x == 0) {
-      double a = 0.0, b = 0.0;
-      if (all_ok) {
-        __threadfence_system();
-        for (int r = 0; r < ex.world; ++r) {  // rank order, on every block of every rank
-          const volatile double *slot = ex.mbox + (phase * P2P_MAXW + r) * 4;
-          a = __dadd_rn(a, slot[0]);
-          b = __dadd_rn(b, slot[1]);
-        }
-      } else {
-        pcg_give_up(ex, 1.0 + phase);
+    double a = 0.0, b = 0.0;
+    if (all_ok) {
+      __threadfence_system();  // the values were stored before their sequence number
+      const double mine0 = j < ex.world ? slot[0] : 0.0, mine1 = j < ex.world ? slot[1] : 0.0;  // one load per lane
+      for (int r = 0; r < ex.world; ++r) {  // added in rank order, on every block of every rank
+        a = __dadd_rn(a, __shfl_sync(0xffffffffu, mine0, r));
+        b = __dadd_rn(b, __shfl_sync(0xffffffffu, mine1, r));
       }
+    }
+    if (j == 0) {
+      if (!all_ok) pcg_give_up(ex, 1.0 + phase);
       s_vals[0] = a;
       s_vals[1] = b;
       s_vals[2] = all_ok ? 1.0 : 0.0;

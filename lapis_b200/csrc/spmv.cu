@@ -1231,9 +1231,24 @@ static int launch_spmv(const lapis_b200_csr *h, const double *x, double *y, int 
       const I *crd = static_cast<const I *>(h->crd);
       const int64_t abase = h->base & ~(int64_t)3, ntiles = (h->nrows + 255) / 256;
       const PcgExchange none = {};
-      if (dotvec != nullptr && ex != nullptr)
-        spmv_rowthread_kernel<I, true, true><<<(unsigned)h->nblk, 256, 0, st>>>(pos, crd, h->val, abase, h->nrows, ntiles, x, y,
-                                                                                accumulate, dotvec, blk_partial, skip_flag, *ex);
+      if (dotvec != nullptr && ex != nullptr) {
+        // as pass A of a PCG iteration: a grid of exactly the blocks that are resident at once, looping over the
+        // row tiles, so that the block that finishes last has about a thousand partial sums to add, not one per
+        // chunk of the plan (a grid larger than what is resident would run its last blocks on a nearly empty GPU)
+        static int per_sm[64] = {0};
+        int dev = 0;
+        LAPIS_CUDA_TRY(cudaGetDevice(&dev));
+        if (dev < 0 || dev >= 64) return fail(LAPIS_EBADARG, "spmv: device index %d not supported", dev);
+        if (per_sm[dev] == 0) {
+          int nb = 0;
+          LAPIS_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, spmv_rowthread_kernel<I, true, true>, 256, 0));
+          per_sm[dev] = nb > 0 ? nb : 1;
+        }
+        const int64_t resident = (int64_t)sm_count() * per_sm[dev];
+        const unsigned grid = (unsigned)std::min<int64_t>(std::min<int64_t>(h->nblk, ntiles), resident);
+        spmv_rowthread_kernel<I, true, true><<<grid < 1 ? 1 : grid, 256, 0, st>>>(pos, crd, h->val, abase, h->nrows, ntiles, x, y,
+                                                                                  accumulate, dotvec, blk_partial, skip_flag, *ex);
+      }
       else if (dotvec != nullptr)
         spmv_rowthread_kernel<I, true, false><<<(unsigned)h->nblk, 256, 0, st>>>(pos, crd, h->val, abase, h->nrows, ntiles, x, y,
                                                                                  accumulate, dotvec, blk_partial, skip_flag, none);
