@@ -93,17 +93,46 @@ def all_windows(pos, crd, bounds):
 class ShardedSpmv:
     """y_local = (y_local) + A[rows of this rank, :] x with x replicated on every rank."""
 
-    def __init__(self, pos, crd, val, shape, rank: int, world: int, device):
+    def __init__(self, pos, crd, val, shape, rank: int, world: int, device, tune="strict"):
         from .device import CsrMatrix
+        self.rank, self.world, self.device = rank, world, torch.device(device)
+        self.ncols = int(shape[1])
         self.bounds, lpos, lcrd, lval = local_block(pos, crd, val, rank, world)
         self.r0, self.r1 = int(self.bounds[rank]), int(self.bounds[rank + 1])
-        self.matrix = CsrMatrix.from_host(lpos, lcrd, lval, (self.r1 - self.r0, shape[1]), device, tune=True)
+        self.matrix = CsrMatrix.from_host(lpos, lcrd, lval, (self.r1 - self.r0, shape[1]), device, tune=tune == "strict")
+        if tune == "relaxed":
+            self.matrix.tune(relaxed=True)
+        self._x = None
+        self._y = None
 
     def spmv(self, x, y_local, accumulate=True):
         return self.matrix.spmv(x, y_local, accumulate)
 
     def spmm(self, B, C_local, accumulate=True):
         return self.matrix.spmm(B, C_local, accumulate)
+
+    def spmv_from_host(self, x_host: torch.Tensor, y_host_local: torch.Tensor, group=None):
+        """y_local = A[rows of this rank, :] x with x and y in (page-locked) host memory: every rank uploads only
+        its 1/world slice of x, the slices are gathered over NVLink into the full x on every GPU (NCCL
+        all-gather; with one rank the whole x is uploaded), the kernel runs, and this rank's block of y is
+        copied back.  Returns when y_host_local is current.  Uploading all of x from the one host on every
+        rank instead costs world times the PCIe traffic for the same result."""
+        n = self.ncols
+        if self._x is None:
+            self._x = torch.empty(n, dtype=torch.float64, device=self.device)
+            self._y = torch.empty(self.r1 - self.r0, dtype=torch.float64, device=self.device)
+        if self.world > 1 and n % self.world == 0:
+            per = n // self.world
+            if getattr(self, "_x_slice", None) is None:
+                self._x_slice = torch.empty(per, dtype=torch.float64, device=self.device)
+            self._x_slice.copy_(x_host[self.rank * per:(self.rank + 1) * per], non_blocking=True)
+            dist.all_gather_into_tensor(self._x, self._x_slice, group=group)
+        else:
+            self._x.copy_(x_host, non_blocking=True)
+        self.matrix.spmv(self._x, self._y, accumulate=False)
+        y_host_local.copy_(self._y, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        return y_host_local
 
 
 class _PeerBuffer:
@@ -343,14 +372,14 @@ class DistPcg:
                     self._iteration(tol, maxiter)
                 self._graph = (g, tol, maxiter)
                 self._init(tol, maxiter)  # capture does not execute; state is still the initial one
-            if self._graph is not None and self._graph[1:] != (tol, maxiter):
-                raise ValueError("a captured solver is bound to its tol/maxiter; build a new DistPcg")
+            # the captured iteration has its tol / maxiter baked in: other values run as plain launches
+            replay = self._graph is not None and self._graph[1:] == (tol, maxiter)
             i = 0
             done = False
             while not done and i < limit:
                 burst = min(check_every, limit - i)
                 for _ in range(burst):
-                    if self._graph is not None:
+                    if replay:
                         self._graph[0].replay()
                     else:
                         self._iteration(tol, maxiter)
