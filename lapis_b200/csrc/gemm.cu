@@ -81,7 +81,10 @@ extern "C" int lapis_b200_bgemm_f32(int64_t batch, int64_t M, int64_t N, int64_t
   if (batch == 0 || M == 0 || N == 0) return LAPIS_OK;
   if (d_C == nullptr || (K > 0 && (d_A == nullptr || d_B == nullptr))) return fail(LAPIS_EBADARG, "bgemm: null operand");
   cudaStream_t st = as_stream(stream);
-  if (bgemm_tcgen05_supported(batch, M, N, K)) return bgemm_tcgen05_launch(batch, M, N, K, d_A, d_B, d_C, st);
+  // the tensor-core kernel moves its operands with TMA, which needs 16-byte aligned bases; other pointers (a
+  // slice of a larger tensor, say) take the general-shape kernel, which has no alignment rule
+  const bool aligned = ((reinterpret_cast<uintptr_t>(d_A) | reinterpret_cast<uintptr_t>(d_B) | reinterpret_cast<uintptr_t>(d_C)) % 16) == 0;
+  if (aligned && bgemm_tcgen05_supported(batch, M, N, K)) return bgemm_tcgen05_launch(batch, M, N, K, d_A, d_B, d_C, st);
   dim3 grid((unsigned)((N + SG_TILE - 1) / SG_TILE), (unsigned)((M + SG_TILE - 1) / SG_TILE),
             (unsigned)(batch < 65535 ? batch : 65535));
   if (grid.y > 65535) return fail(LAPIS_ETOOBIG, "bgemm: M too large for the general-shape kernel");

@@ -131,12 +131,20 @@ __device__ __forceinline__ void mma_tf32(uint32_t tmem_d, uint64_t da, uint64_t 
       : "memory");
 }
 
+// lo = x - hi with hi = the 19 bits the tensor core reads.  An infinity has lo = 0 (inf - inf would turn a whole
+// row or column of C into NaN where the fp32 loop gives an infinity); a NaN stays a NaN in lo, because truncating
+// its payload may leave hi an infinity.
+__device__ __forceinline__ float split_lo(float x) {
+  const uint32_t u = __float_as_uint(x);
+  if ((u & 0x7F800000u) == 0x7F800000u) return (u & 0x007FFFFFu) ? x : 0.0f;
+  return x - __uint_as_float(u & 0xFFFFE000u);
+}
 __device__ __forceinline__ void split_tf32(float4 &hi_lo_in_out, float4 &lo) {
-  float4 x = hi_lo_in_out;
-  lo.x = x.x - __uint_as_float(__float_as_uint(x.x) & 0xFFFFE000u);
-  lo.y = x.y - __uint_as_float(__float_as_uint(x.y) & 0xFFFFE000u);
-  lo.z = x.z - __uint_as_float(__float_as_uint(x.z) & 0xFFFFE000u);
-  lo.w = x.w - __uint_as_float(__float_as_uint(x.w) & 0xFFFFE000u);
+  const float4 x = hi_lo_in_out;
+  lo.x = split_lo(x.x);
+  lo.y = split_lo(x.y);
+  lo.z = split_lo(x.z);
+  lo.w = split_lo(x.w);
 }
 
 // Tile t of the persistent schedule -> (batch, m block, n block).  Within a batch entry the tiles

@@ -468,6 +468,53 @@ def test_bgemm_tensor_core_path(shape):
     assert torch.equal(Cd, Cd2)
 
 
+def test_bgemm_unaligned_operands_take_the_general_kernel():
+    """A tile-aligned shape whose device pointers are not 16-byte aligned (slices of larger tensors) cannot use
+    the tensor-core kernel's TMA loads; it runs on the general-shape kernel instead of being refused, and that
+    kernel is bit-exact against the sequential loop."""
+    from lapis_b200.device import bgemm
+    dev = _dev()
+    rng = np.random.default_rng(9)
+    M = N = 128
+    K = 64
+    A = rng.uniform(-1, 1, (M, K)).astype(np.float32)
+    B = rng.uniform(-1, 1, (K, N)).astype(np.float32)
+    C0 = rng.uniform(-1, 1, (M, N)).astype(np.float32)
+    big = torch.zeros(M * K + 1, dtype=torch.float32, device=dev)
+    Ad = big[1:].view(M, K)                      # 4 bytes past a 16-byte boundary
+    assert Ad.data_ptr() % 16 == 4
+    Ad.copy_(torch.as_tensor(A))
+    Cd = torch.as_tensor(C0).to(dev)
+    bgemm(Ad, torch.as_tensor(B).to(dev), Cd)
+    assert np.array_equal(Cd.cpu().numpy(), oracle.bgemm(A, B, C0))
+
+
+def test_bgemm_tensor_core_path_with_an_infinite_input():
+    """x = hi + lo with lo = x - hi would give lo = NaN for an infinite x and turn a whole row of C into NaN;
+    the split gives lo = 0 there, so the row is infinite with the sign of the other operand, as in the fp32
+    loop (entries whose partner has an exactly zero low part may still be NaN: 0 * inf), and the other rows
+    are untouched."""
+    from lapis_b200.device import bgemm, bgemm_status
+    dev = _dev()
+    rng = np.random.default_rng(10)
+    M, N, K = 128, 256, 64
+    A = rng.uniform(-1, 1, (M, K)).astype(np.float32)
+    B = rng.uniform(0.1, 1, (K, N)).astype(np.float32) * np.where(rng.random((K, N)) < 0.5, -1, 1).astype(np.float32)
+    A[5, 7] = np.inf
+    Cd = torch.zeros((M, N), dtype=torch.float32, device=dev)
+    bgemm(torch.as_tensor(A).to(dev), torch.as_tensor(B).to(dev), Cd)
+    bgemm_status()
+    C = Cd.cpu().numpy()
+    row = C[5]
+    assert np.mean(np.isinf(row)) > 0.98
+    inf_at = np.isinf(row)
+    assert np.array_equal(np.sign(row[inf_at]), np.sign(B[7][inf_at]))
+    others = np.delete(C, 5, axis=0)
+    exact = np.delete(A, 5, axis=0).astype(np.float64) @ B.astype(np.float64)
+    assert np.all(np.isfinite(others)) and np.max(np.abs(others - exact)) <= 1e-5 * np.max(np.abs(exact))
+
+
+
 # ---------------------------------------------------------------------------
 # vector kernels and PCG
 # ---------------------------------------------------------------------------
