@@ -40,12 +40,26 @@ import time
 # CPUs this process may use, read before any OpenMP runtime is loaded: with OMP_PROC_BIND set the runtime pins
 # the initial thread to the first place, after which the process's own affinity mask shows one CPU only
 try:
-    _CPUS_ALLOWED = len(os.sched_getaffinity(0))
+    _CPU_MASK = os.sched_getaffinity(0)
 except Exception:
-    _CPUS_ALLOWED = os.cpu_count() or 1
-# the CPU restatement's OpenMP threads stay on their cores (read by the OpenMP runtime when it is loaded)
-os.environ.setdefault("OMP_PROC_BIND", "close")
-os.environ.setdefault("OMP_PLACES", "cores")
+    _CPU_MASK = None
+_CPUS_ALLOWED = len(_CPU_MASK) if _CPU_MASK else (os.cpu_count() or 1)
+# The CPU restatement's OpenMP threads stay on their cores (read by the OpenMP runtime when it is loaded).  Only in
+# a process that times the CPU restatement (one rank, or the reference arm): in a multi-rank job every rank's main
+# thread would be pinned to the same first core.
+if int(os.environ.get("WORLD_SIZE", "1")) == 1 or "reference" in sys.argv:
+    os.environ.setdefault("OMP_PROC_BIND", "close")
+    os.environ.setdefault("OMP_PLACES", "cores")
+
+
+def release_main_thread():
+    """Gives the main thread its original CPU mask back after the CPU timing (the OpenMP runtime pinned it)."""
+    if _CPU_MASK:
+        try:
+            os.sched_setaffinity(0, _CPU_MASK)
+        except Exception:
+            pass
+
 
 import numpy as np  # noqa: E402
 
@@ -754,6 +768,7 @@ def main():
     d = make_workload(args.workload, args.small, args.shrink)
     # the CPU baseline first, while this process holds no CUDA context, pinned buffers or helper threads
     cpu_base = cpu_baseline(d) if (world == 1 and not args.no_cpu_baseline) else None
+    release_main_thread()
 
     import torch
     import torch.distributed as dist
