@@ -276,7 +276,7 @@ int lapis_b200_normalize_mom2_f64(int64_t n, const double *d_mom1, const double 
  * bytes, 16-byte aligned.  Layout in doubles: [0] p.Ap, [1] r.r, [2] r.z (new),
  * [3] r.z (carried), [4] initial residual norm, [5] relres, [6] alpha, [7] beta,
  * [8] done flag and [9] count of completed iterations as int64, then scratch and the vectors
- * r, z, p, Ap.  n = local rows; n_p >= n = length of the p buffer the matrix's
+ * r, z, p, Ap and a z halo buffer as long as p.  n = local rows; n_p >= n = length of the p buffer the matrix's
  * column indices address; the local part of p starts at p_offset in it.
  * `derive` != 0 lets the pass also run the scalar recurrence that consumes its
  * sums (single-device use); with derive == 0 the caller reduces slots [0] or
@@ -324,24 +324,31 @@ int lapis_b200_pcg_p2p_halo_wait(void *d_work, void *d_mbox, const void *d_srcs,
 /* One iteration in three launches.  The passes above leave the sums to a single-block kernel (or to the
  * caller's collective) between them; these variants add the per-block partial sums inside the pass, in the
  * block that finishes last, and -- with an exchange description -- do the row-partitioned solver's exchanges
- * inside the passes too: pass A waits for the neighbours' halo pieces of p and ends by storing this rank's
- * p.Ap into every rank's mailbox; pass B starts by waiting for every rank's p.Ap (each block adds them in
- * rank order and derives alpha itself) and ends by storing r.r and r.z; pass C starts by waiting for those,
- * repeats the stop test, updates p, stores the rows its neighbours need straight into their windows of p,
- * and its last block raises the halo flags and advances the iteration counter.  Plain peer stores and local
- * polling only; every wait is bounded (lapis_b200_pcg_p2p_set_wait_limit polls, 0 = the default of 2^22,
- * about a second) and a wait that runs out marks the mailbox and sets the done flag instead of hanging.
+ * inside the passes too: pass A ends by storing this rank's p.Ap into every rank's mailbox; pass B starts by
+ * waiting for every rank's p.Ap (each block adds them in rank order and derives alpha itself), also stores the
+ * rows of z behind its neighbours' halo of p into their z halo buffers, and ends by storing r.r and r.z; pass C
+ * starts by waiting for those, repeats the stop test, and updates p on the own rows and on the halo entries of
+ * the window (p_halo = z_halo + beta * p_halo, the owner's operation on the owner's operands), so the halo of p
+ * needs no exchange of its own: two points per iteration at which ranks wait for each other.  Plain peer stores
+ * and local polling only; every wait is bounded (lapis_b200_pcg_p2p_set_wait_limit polls, 0 = the default of
+ * 2^22, about a second) and a wait that runs out marks the mailbox and sets the done flag instead of hanging.
  * exchange == NULL (or d_mbox == NULL): one device, scalars derived locally -- lapis_b200_pcg_f64 is these
- * three calls in a loop.  The initial exchange still uses push_scalars / wait_reduce / halo_push above.
+ * three calls in a loop.  The initial exchange still uses push_scalars / wait_reduce / halo_push / halo_wait
+ * above (the halo of the first p travels as p); nsrc > 0 makes pass A wait for halo flags like halo_wait does.
+ * The z halo buffer of a workspace has n_p doubles and follows Ap: offsets4[3] + n of
+ * lapis_b200_pcg_workspace_layout.
  * Replaces the loop body of examples/pcg_solve.py:74-98 (host loop TranslateToKokkosCpp.cpp:1512-1593). */
 typedef struct {
-  int me, world;            /* this rank and the number of ranks (at most 16) */
-  void *d_mbox;             /* this rank's mailbox (NULL: no exchange) */
-  const void *d_peer_mbox;  /* device array of `world` mailbox addresses, own included */
-  const void *d_halo_srcs;  /* device int array: ranks whose halo pieces pass A waits for */
+  int me, world;             /* this rank and the number of ranks (at most 16) */
+  void *d_mbox;              /* this rank's mailbox (NULL: no exchange) */
+  const void *d_peer_mbox;   /* device array of `world` mailbox addresses, own included */
+  const void *d_halo_srcs;   /* device int array: ranks whose halo flags pass A waits for (normally none) */
   int nsrc;
-  const void *d_pieces;     /* device array of {dst address, source offset, length, flag address} (halo_push) */
-  int npieces;              /* at most 32 */
+  const void *d_z_pieces;    /* device array of {dst address in the peer's z halo buffer, source offset in this
+                                rank's window, length, unused}: the rows of z the neighbours need */
+  int nzpieces;              /* at most 32 */
+  const void *d_halo_ranges; /* device int64 array of {start, length} pairs: halo parts of this rank's window */
+  int nranges;
 } lapis_b200_pcg_exchange;
 int lapis_b200_pcg_fused_spmv(void *d_work, lapis_b200_csr_t h, int64_t n_p, int64_t p_offset, double tol, uint64_t maxiter,
                               const lapis_b200_pcg_exchange *exchange, void *stream);

@@ -91,7 +91,7 @@ _PROTOS = {
 class PcgExchange(ctypes.Structure):
     """``lapis_b200_pcg_exchange`` of include/lapis_b200.h."""
     _fields_ = [("me", c_int), ("world", c_int), ("d_mbox", c_vp), ("d_peer_mbox", c_vp), ("d_halo_srcs", c_vp),
-                ("nsrc", c_int), ("d_pieces", c_vp), ("npieces", c_int)]
+                ("nsrc", c_int), ("d_z_pieces", c_vp), ("nzpieces", c_int), ("d_halo_ranges", c_vp), ("nranges", c_int)]
 
 
 _LIB = None

@@ -175,13 +175,14 @@ static inline unsigned vec_grid(int64_t n) {
   return (unsigned)(g < 1 ? 1 : g);
 }
 
-// Workspace layout (doubles): [scalars 8][flags 2 (as int64)][pad to 16][partials 2*G][r n][z n][p n_p][Ap n]
-// where G = 8 * SM count and n_p >= n is the length of the (halo-extended) p buffer.
+// Workspace layout (doubles): [scalars 8][flags 2 (as int64)][pad to 16][partials 2*G][r n][z n][p n_p][Ap n][zh n_p]
+// where G = 8 * SM count, n_p >= n is the length of the (halo-extended) p buffer and zh is the window-indexed
+// buffer into which neighbours store the rows of z behind this rank's halo of p.
 struct PcgWork {
   double *sc;
   long long *fl;
   double *partials;
-  double *r, *z, *p, *Ap;
+  double *r, *z, *p, *Ap, *zh;
   unsigned grid;
 };
 
@@ -198,6 +199,7 @@ static PcgWork carve(void *d_work, int64_t n, int64_t n_p) {
   w.z = vecs + n;
   w.p = vecs + 2 * n;
   w.Ap = vecs + 2 * n + n_p;
+  w.zh = vecs + 3 * n + n_p;
   w.grid = vec_grid(n);
   return w;
 }
@@ -206,35 +208,70 @@ static PcgWork carve(void *d_work, int64_t n, int64_t n_p) {
 // ---- fused passes: heads that wait for the other ranks' sums, tails in the last block (pcg_fuse.h) --------
 static unsigned g_p2p_spin_limit = P2P_SPIN_LIMIT;  // polls per bounded wait; lapis_b200_pcg_p2p_set_wait_limit
 
-// Pass B.  alpha comes from the scalar block (no exchange) or from every rank's p.Ap (exchange).
+// Pass B.  alpha comes from the scalar block (no exchange) or from every rank's p.Ap (exchange).  With an
+// exchange the rows of z that neighbours need (they stand behind the neighbours' halo of p) are also stored into
+// the neighbours' z halo buffers, and the tail's sequence number covers them.
+constexpr int PCG_MAX_FUSED_PIECES = 32;
 __global__ void __launch_bounds__(VEC_THREADS)
-pcg_update_fused_kernel(int64_t n, PcgExchange ex, const double *__restrict__ p, const double *__restrict__ Ap,
+pcg_update_fused_kernel(int64_t n, int64_t p_off, PcgExchange ex, const double *__restrict__ p, const double *__restrict__ Ap,
                         const double *__restrict__ dinv, double *__restrict__ x, double *__restrict__ r,
                         double *__restrict__ z, double *__restrict__ partials) {
   __shared__ double s_red[VEC_THREADS / 32];
   __shared__ double s_vals[3];
   __shared__ int s_flag;
+  __shared__ HaloPiece s_pieces[PCG_MAX_FUSED_PIECES];
   if (ex.fl[FL_DONE] != 0) return;
   double alpha;
+  const int npieces = ex.mbox != nullptr ? ex.npieces : 0;
   if (ex.mbox != nullptr) {
+    for (int q = threadIdx.x; q < npieces; q += VEC_THREADS) s_pieces[q] = ex.pieces[q];
     double pap, unused;
-    if (!pcg_wait_sums(ex, PH_A, s_vals, pap, unused)) return;
+    if (!pcg_wait_sums(ex, PH_A, s_vals, pap, unused)) return;  // its barrier also publishes s_pieces
     alpha = ex.sc[SC_RZ] / pap;
   } else {
     alpha = ex.sc[SC_ALPHA];
   }
   const double malpha = -alpha;
   double rr = 0.0, rz = 0.0;
-  for (int64_t i = (int64_t)blockIdx.x * VEC_THREADS + threadIdx.x; i < n; i += (int64_t)gridDim.x * VEC_THREADS) {
-    const double xi = __dadd_rn(__dmul_rn(x[i], 1.0), __dmul_rn(p[i], alpha));
-    const double ri = __dadd_rn(__dmul_rn(r[i], 1.0), __dmul_rn(Ap[i], malpha));
-    const double zi = __dmul_rn(ri, dinv[i]);
-    x[i] = xi;
-    r[i] = ri;
-    z[i] = zi;
-    rr = __dadd_rn(rr, __dmul_rn(ri, ri));
-    rz = __dadd_rn(rz, __dmul_rn(ri, zi));
+  bool stored_to_peer = false;
+  // four elements per round, all loads first: the stores into the neighbours' buffers may alias anything as far
+  // as the compiler knows, so it would not overlap the loads of successive elements by itself
+  const int64_t stride = (int64_t)gridDim.x * VEC_THREADS;
+  for (int64_t i0 = (int64_t)blockIdx.x * VEC_THREADS + threadIdx.x; i0 < n; i0 += 4 * stride) {
+    double xv[4], pv[4], rv[4], av[4], dv[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int64_t i = i0 + k * stride;
+      const bool in = i < n;
+      xv[k] = in ? x[i] : 0.0;
+      pv[k] = in ? p[i] : 0.0;
+      rv[k] = in ? r[i] : 0.0;
+      av[k] = in ? Ap[i] : 0.0;
+      dv[k] = in ? dinv[i] : 0.0;
+    }
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int64_t i = i0 + k * stride;
+      if (i >= n) break;
+      const double xi = __dadd_rn(__dmul_rn(xv[k], 1.0), __dmul_rn(pv[k], alpha));
+      const double ri = __dadd_rn(__dmul_rn(rv[k], 1.0), __dmul_rn(av[k], malpha));
+      const double zi = __dmul_rn(ri, dv[k]);
+      x[i] = xi;
+      r[i] = ri;
+      z[i] = zi;
+      rr = __dadd_rn(rr, __dmul_rn(ri, ri));
+      rz = __dadd_rn(rz, __dmul_rn(ri, zi));
+      const int64_t wi = p_off + i;  // position in this rank's window
+      for (int q = 0; q < npieces; ++q) {
+        const int64_t d = wi - s_pieces[q].src_off;
+        if (d >= 0 && d < s_pieces[q].len) {
+          reinterpret_cast<double *>(s_pieces[q].dst_addr)[d] = zi;
+          stored_to_peer = true;
+        }
+      }
+    }
   }
+  if (stored_to_peer) __threadfence_system();  // this thread's stores into a neighbour's buffer, before the block's ticket
   const double t0 = block_sum_vec(rr, s_red);
   const double t1 = block_sum_vec(rz, s_red);
   if (threadIdx.x == 0) {
@@ -253,80 +290,47 @@ pcg_update_fused_kernel(int64_t n, PcgExchange ex, const double *__restrict__ p,
     else ex.sc[SC_ALPHA] = alpha;
   }
   __syncthreads();
+  // every block's stores into the neighbours' buffers were fenced before its ticket; the fence inside the push
+  // orders them before the sequence number that the neighbours wait for
   if (ex.mbox != nullptr) pcg_push_sums(ex, PH_B, s_vals[0], s_vals[1], pcg_seq(ex));
 }
 
-// Pass C.  Without exchange the stop test ran in pass B's tail.  With it every block repeats the test on
-// every rank's r.r and r.z; rows that neighbours need are also stored into their windows of p, and the block
-// that finishes last raises the halo flags and advances the iteration.
-constexpr int PCG_MAX_FUSED_PIECES = 32;
+// Pass C with an exchange (without one the stop test ran in pass B's tail and the plain pass is used): every block
+// repeats the stop test on every rank's r.r and r.z, updates its part of the own rows of p, and the halo entries of
+// the window are updated too -- from the rows of z that the neighbours stored in pass B and the halo's old values
+// of p, the operation the owner performs on the same operands.  The block that finishes last advances the
+// iteration.
 __global__ void __launch_bounds__(VEC_THREADS)
 pcg_direction_fused_kernel(int64_t n, int64_t p_off, PcgExchange ex, const double *__restrict__ z, double *__restrict__ pw) {
-  __shared__ double s_red[VEC_THREADS / 32];
   __shared__ double s_vals[3];
   __shared__ int s_flag;
-  __shared__ HaloPiece s_pieces[PCG_MAX_FUSED_PIECES];
   if (ex.fl[FL_DONE] != 0) return;
-  double *p = pw + p_off;
-  if (ex.mbox == nullptr) {
-    const double beta = ex.sc[SC_BETA];
-    for (int64_t i = (int64_t)blockIdx.x * VEC_THREADS + threadIdx.x; i < n; i += (int64_t)gridDim.x * VEC_THREADS)
-      p[i] = __dadd_rn(__dmul_rn(z[i], 1.0), __dmul_rn(p[i], beta));
-    return;
-  }
+  double *__restrict__ p = pw + p_off;
   double rr, rznew;
   if (!pcg_wait_sums(ex, PH_B, s_vals, rr, rznew)) return;
-  const double seq = pcg_seq(ex);
   const double relres = sqrt(rr) / ex.sc[SC_INITRES];
   const unsigned long long iter = (unsigned long long)ex.fl[FL_ITERS] + 1;  // i starts at 1
   const bool go = (relres > ex.tol) && (iter != ex.maxiter);                // ordered compare: NaN stops the loop
   const double rz_old = ex.sc[SC_RZ];
   const double beta = rznew / rz_old;
   if (go) {
-    for (int q = threadIdx.x; q < ex.npieces; q += VEC_THREADS) s_pieces[q] = ex.pieces[q];
-    __syncthreads();
-    bool stored_to_peer = false;
-    // four elements per round, all loads first: the stores into the neighbours' windows may alias anything as
-    // far as the compiler knows, so it would not overlap the loads of successive elements by itself
-    const int64_t stride = (int64_t)gridDim.x * VEC_THREADS;
-    for (int64_t i0 = (int64_t)blockIdx.x * VEC_THREADS + threadIdx.x; i0 < n; i0 += 4 * stride) {
-      double zi[4], po[4];
-#pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        const int64_t i = i0 + k * stride;
-        zi[k] = i < n ? z[i] : 0.0;
-        po[k] = i < n ? p[i] : 0.0;
-      }
-#pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        const int64_t i = i0 + k * stride;
-        if (i >= n) break;
-        const double pi = __dadd_rn(__dmul_rn(zi[k], 1.0), __dmul_rn(po[k], beta));
-        p[i] = pi;
-        const int64_t wi = p_off + i;  // position in this rank's window
-        for (int q = 0; q < ex.npieces; ++q) {
-          const int64_t d = wi - s_pieces[q].src_off;
-          if (d >= 0 && d < s_pieces[q].len) {
-            reinterpret_cast<double *>(s_pieces[q].dst_addr)[d] = pi;
-            stored_to_peer = true;
-          }
-        }
-      }
+    for (int64_t i = (int64_t)blockIdx.x * VEC_THREADS + threadIdx.x; i < n; i += (int64_t)gridDim.x * VEC_THREADS)
+      p[i] = __dadd_rn(__dmul_rn(z[i], 1.0), __dmul_rn(p[i], beta));
+    // halo entries of the window: the blocks share each range
+    for (int q = 0; q < ex.nranges; ++q) {
+      const long long start = ex.halo_ranges[2 * q], len = ex.halo_ranges[2 * q + 1];
+      for (long long j = (long long)blockIdx.x * VEC_THREADS + threadIdx.x; j < len; j += (long long)gridDim.x * VEC_THREADS)
+        pw[start + j] = __dadd_rn(__dmul_rn(ex.zhalo[start + j], 1.0), __dmul_rn(pw[start + j], beta));
     }
-    if (stored_to_peer) __threadfence_system();  // this thread's stores into a neighbour's window, before the block's ticket
   }
   if (!pcg_last_block(pcg_tickets(ex.sc) + 2, gridDim.x, &s_flag)) return;
-  (void)s_red;
   if (threadIdx.x == 0) {
-    __threadfence_system();
     ex.sc[SC_RR] = rr;
     ex.sc[SC_RZNEW] = rznew;
     ex.sc[SC_RELRES] = relres;
     if (go) {
       ex.sc[SC_BETA] = beta;
       ex.sc[SC_RZ] = rznew;
-      for (int q = 0; q < ex.npieces; ++q)  // the pieces of the next iteration have arrived
-        *reinterpret_cast<volatile double *>(ex.pieces[q].flag_addr) = seq + 1.0;
     } else {
       ex.fl[FL_DONE] = 1;
     }
@@ -360,11 +364,14 @@ static PcgExchange make_exchange(const PcgWork &w, const lapis_b200_pcg_exchange
     ex.mbox = static_cast<double *>(e->d_mbox);
     ex.peer_mbox = static_cast<const unsigned long long *>(e->d_peer_mbox);
     ex.halo_srcs = static_cast<const int *>(e->d_halo_srcs);
-    ex.pieces = static_cast<const HaloPiece *>(e->d_pieces);
+    ex.pieces = static_cast<const HaloPiece *>(e->d_z_pieces);
+    ex.halo_ranges = static_cast<const long long *>(e->d_halo_ranges);
+    ex.zhalo = w.zh;
     ex.me = e->me;
     ex.world = e->world;
     ex.nsrc = e->nsrc;
-    ex.npieces = e->npieces;
+    ex.npieces = e->nzpieces;
+    ex.nranges = e->nranges;
   }
   return ex;
 }
@@ -372,8 +379,9 @@ static PcgExchange make_exchange(const PcgWork &w, const lapis_b200_pcg_exchange
 static int check_exchange(const lapis_b200_pcg_exchange *e, const char *what) {
   if (e == nullptr || e->d_mbox == nullptr) return LAPIS_OK;
   if (e->world < 1 || e->world > P2P_MAXW || e->me < 0 || e->me >= e->world || e->d_peer_mbox == nullptr || e->nsrc < 0 ||
-      e->nsrc > 32 || e->npieces < 0 || e->npieces > PCG_MAX_FUSED_PIECES || (e->nsrc > 0 && e->d_halo_srcs == nullptr) ||
-      (e->npieces > 0 && e->d_pieces == nullptr))
+      e->nsrc > 32 || e->nzpieces < 0 || e->nzpieces > PCG_MAX_FUSED_PIECES || e->nranges < 0 ||
+      (e->nsrc > 0 && e->d_halo_srcs == nullptr) || (e->nzpieces > 0 && e->d_z_pieces == nullptr) ||
+      (e->nranges > 0 && e->d_halo_ranges == nullptr))
     return fail(LAPIS_EBADARG, "%s: bad exchange description (up to %d ranks, 32 halo sources, %d halo pieces)", what,
                 P2P_MAXW, PCG_MAX_FUSED_PIECES);
   return LAPIS_OK;
@@ -424,7 +432,7 @@ extern "C" int lapis_b200_mult_f64(int64_t n, const double *d_x, const double *d
 // ---- multi-device callers that put a halo exchange / allreduce between the steps) ---
 extern "C" int64_t lapis_b200_pcg_workspace_bytes(int64_t n, int64_t n_p) {
   if (n < 0 || n_p < n) return -1;
-  return (int64_t)sizeof(double) * (16 + pcg_partials_len() + 3 * n + n_p);
+  return (int64_t)sizeof(double) * (16 + pcg_partials_len() + 3 * n + 2 * n_p);
 }
 
 extern "C" int lapis_b200_pcg_workspace_layout(int64_t n, int64_t n_p, int64_t *offsets4) {
@@ -539,8 +547,8 @@ extern "C" int lapis_b200_pcg_fused_update(void *d_work, int64_t n, int64_t n_p,
   LAPIS_TRY(check_exchange(exchange, "pcg_fused_update"));
   PcgWork w = carve(d_work, n, n_p);
   const PcgExchange ex = make_exchange(w, exchange, tol, maxiter);
-  pcg_update_fused_kernel<<<w.grid, VEC_THREADS, 0, as_stream(stream)>>>(n, ex, w.p + p_offset, w.Ap, d_dinv, d_x, w.r, w.z,
-                                                                         w.partials);
+  pcg_update_fused_kernel<<<w.grid, VEC_THREADS, 0, as_stream(stream)>>>(n, p_offset, ex, w.p + p_offset, w.Ap, d_dinv, d_x,
+                                                                         w.r, w.z, w.partials);
   LAPIS_CUDA_TRY(cudaGetLastError());
   return LAPIS_OK;
 }

@@ -5,13 +5,18 @@
 //
 // One PCG iteration (examples/pcg_solve.py:74-98 in the LAPIS project) is three launches:
 //
-//   pass A  [wait for the neighbours' halo of p]  Ap = A p, partial sums of p.Ap
+//   pass A  Ap = A p, partial sums of p.Ap
 //           tail: p.Ap summed; one rank: alpha derived; several ranks: {p.Ap, seq} stored into every mailbox
-//   pass B  [wait for every rank's p.Ap; alpha]   x += alpha p, r -= alpha Ap, z = r*dinv, partial r.r and r.z
+//   pass B  [wait for every rank's p.Ap; alpha]   x += alpha p, r -= alpha Ap, z = r*dinv, partial r.r and r.z;
+//           the rows of z that neighbours need are also stored into their halo buffers
 //           tail: sums; one rank: stop test and beta; several ranks: {r.r, r.z, seq} stored into every mailbox
-//   pass C  [wait for every rank's r.r, r.z; stop test; beta]   p = z + beta p, boundary rows also stored into
-//           the neighbours' p windows
-//           tail: several ranks: halo flags raised, iteration counter advanced
+//           (after the z rows: a rank that sees the sequence number also sees the rows)
+//   pass C  [wait for every rank's r.r, r.z; stop test; beta]   p = z + beta p on the own rows AND on the halo
+//           entries of the window, from the neighbours' z rows and the old halo of p (the same operation the
+//           owner performs, so the same bits) -- the halo of p needs no exchange of its own
+//           tail: several ranks: iteration counter advanced
+//
+// Two points per iteration at which a rank waits for the others, not three.
 //
 // A "tail" runs in the block that finishes last (an atomic ticket per pass) and adds the partial sums in a
 // fixed order, so results do not depend on which block that is.  Heads that wait poll this rank's own mailbox
@@ -51,9 +56,11 @@ struct PcgExchange {
   long long *fl;                         // its flags
   double *mbox;                          // this rank's mailbox; null: no exchange, scalars derived locally
   const unsigned long long *peer_mbox;   // addresses of every rank's mailbox, own included
-  const int *halo_srcs;                  // ranks whose halo pieces pass A waits for
-  const HaloPiece *pieces;               // pieces of p that pass C stores into the neighbours' windows
-  int me, world, nsrc, npieces;
+  const int *halo_srcs;                  // ranks whose halo pieces of p a wait in front of pass A covers (first iteration)
+  const HaloPiece *pieces;               // rows of z that pass B stores into the neighbours' z halo buffers
+  const long long *halo_ranges;          // {start, length} pairs: the halo parts of this rank's window
+  const double *zhalo;                   // this rank's z halo buffer (window-indexed)
+  int me, world, nsrc, npieces, nranges;
   unsigned spin_limit;                   // polls per bounded wait
   double tol;
   unsigned long long maxiter;

@@ -205,6 +205,7 @@ class DistPcg:
             offs = (ctypes.c_int64 * 4)()
             check(self._lib.lapis_b200_pcg_workspace_layout(self.n, self.n_p, offs))
             self._p_doubles = int(offs[2])
+            self._zh_doubles = int(offs[3]) + self.n   # the z halo buffer follows Ap
             self.p_ext = self.work[offs[2]:offs[2] + self.n_p]
             self.sc = self.work[0:8]
             self.flags = self.work[8:10].view(torch.int64)
@@ -222,13 +223,13 @@ class DistPcg:
         if self.world > 16:
             raise ValueError("the peer-to-peer transport supports up to 16 ranks")
         self._mbox_buf = _PeerBuffer(lib, check, int(lib.lapis_b200_pcg_p2p_mailbox_bytes()), self.device)
-        mine = (self._work_buf.handle, self._mbox_buf.handle, self.n_p, self._p_doubles)
+        mine = (self._work_buf.handle, self._mbox_buf.handle, self.n_p, self._p_doubles, self._zh_doubles)
         infos = [mine] * self.world
         if self.world > 1:
             dist.all_gather_object(infos, mine, group=self.group)
         self._peer_ptrs = []
         work_addr, mbox_addr = [0] * self.world, [0] * self.world
-        for r, (wh, mh, _, _) in enumerate(infos):
+        for r, (wh, mh, _, _, _) in enumerate(infos):
             if r == self.rank:
                 work_addr[r], mbox_addr[r] = self._work_buf.ptr, self._mbox_buf.ptr
                 continue
@@ -244,13 +245,25 @@ class DistPcg:
         pieces = part.push_pieces(self.halo.send, windows, self.rank, [i[2] for i in infos], [i[3] for i in infos],
                                   work_addr, mbox_addr, HALO)
         self._npieces = len(pieces) // 4
+        # the same pieces aimed at the neighbours' z halo buffers (fused passes), and the halo parts of this
+        # rank's own window, which pass C updates from those buffers
+        zpieces = part.push_pieces(self.halo.send, windows, self.rank, [i[2] for i in infos], [i[4] for i in infos],
+                                   work_addr, mbox_addr, HALO)
+        self._nzpieces = len(zpieces) // 4
+        self._zpieces = torch.tensor(zpieces if zpieces else [0], dtype=torch.int64, device=self.device)
+        ranges = []
+        for (_, s0, e0) in sorted(self.halo.recv, key=lambda t: t[1]):
+            ranges += [s0 - self.halo.c0, e0 - s0]
+        self._nranges = len(ranges) // 2
+        self._halo_ranges = torch.tensor(ranges if ranges else [0], dtype=torch.int64, device=self.device)
+        self._nsrc_fused = 0
         self._pieces = torch.tensor(pieces if pieces else [0], dtype=torch.int64, device=self.device)
         srcs = sorted({owner for owner, _, _ in self.halo.recv})
         self._nsrc = len(srcs)
         self._srcs = torch.tensor(srcs if srcs else [0], dtype=torch.int32, device=self.device)
         # the fused passes keep at most 32 halo pieces in shared memory and poll at most 32 sources; the ranks
         # decide together, so that all of them run the same form of the iteration
-        fits = [self._npieces <= 32 and self._nsrc <= 32] * self.world
+        fits = [self._nzpieces <= 32 and self._nsrc <= 32] * self.world
         if self.world > 1:
             dist.all_gather_object(fits, fits[0], group=self.group)
         self.fused = self.fused and all(fits)
@@ -293,9 +306,12 @@ class DistPcg:
         ex = getattr(self, "_exchange_struct", None)
         if ex is None:
             from ._lib import PcgExchange
+            # no halo flags to wait for in the steady state (_nsrc_fused == 0): the halo of p is recomputed from the
+            # neighbours' rows of z; the halo of the first p is waited for once, after the initialisation
             ex = PcgExchange(self.rank, self.world, ctypes.c_void_p(self._mbox_buf.ptr),
-                             ctypes.c_void_p(self._peer_mbox.data_ptr()), ctypes.c_void_p(self._srcs.data_ptr()), self._nsrc,
-                             ctypes.c_void_p(self._pieces.data_ptr()), self._npieces)
+                             ctypes.c_void_p(self._peer_mbox.data_ptr()), ctypes.c_void_p(self._srcs.data_ptr()),
+                             self._nsrc_fused, ctypes.c_void_p(self._zpieces.data_ptr()), self._nzpieces,
+                             ctypes.c_void_p(self._halo_ranges.data_ptr()), self._nranges)
             self._exchange_struct = ex
         return ctypes.byref(ex)
 
@@ -345,6 +361,8 @@ class DistPcg:
             self.work[10:11].fill_(float(self._epoch) * 4294967296.0)
             self._p2p_scalars(2, 1, tol, maxiter)
             self._p2p_halo_push()
+            if self.fused:
+                self._p2p_halo_wait()  # the halo of the first p; later halos are recomputed inside pass C
         elif not single:
             self._allreduce(self.sc[1:3])
             check(lib.lapis_b200_pcg_derive(w, 1, tol, maxiter, self._stream()))

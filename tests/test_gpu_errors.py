@@ -129,7 +129,10 @@ def test_a_wait_on_a_peer_that_never_delivers_runs_out(fused):
         assert iters == 5 and solver.comm_error() == 0.0
         # now expect a halo piece from rank 0 (itself) that no pass ever stores
         solver._srcs = torch.tensor([0], dtype=torch.int32, device=dev)
-        solver._nsrc = 1
+        if fused:
+            solver._nsrc_fused = 1   # the wait at the head of the fused SpMV pass
+        else:
+            solver._nsrc = 1         # the wait kernel in front of the SpMV pass
         solver._exchange_struct = None
         with pytest.raises(RuntimeError, match="did not deliver in time"):
             solver.solve(0.0, 5, check_every=5)
