@@ -76,6 +76,18 @@ __device__ __forceinline__ bool p2p_wait_equal(const volatile double *flag, doub
   return false;
 }
 
+// The same wait with acquire loads at system scope: what the producer stored before its flag is visible to this
+// thread's later loads without a separate fence.
+__device__ __forceinline__ bool p2p_wait_acquire(const double *flag, double expected, unsigned limit) {
+  for (unsigned i = 0; i < limit; ++i) {
+    double v;
+    asm volatile("ld.acquire.sys.global.f64 %0, [%1];" : "=d"(v) : "l"(flag) : "memory");
+    if (v == expected) return true;
+    __nanosleep(100);
+  }
+  return false;
+}
+
 // Sequence number of the iteration in flight: epoch * 2^32 + completed iterations + 1.
 __device__ __forceinline__ double pcg_seq(const PcgExchange &ex) { return ex.sc[SC_EPOCH] + (double)(ex.fl[FL_ITERS] + 1); }
 
@@ -92,7 +104,7 @@ __device__ __forceinline__ bool pcg_wait_halo(const PcgExchange &ex, int *s_flag
   if (threadIdx.x < 32) {
     const double expected = pcg_seq(ex);
     bool ok = true;
-    if ((int)threadIdx.x < ex.nsrc) ok = p2p_wait_equal(ex.mbox + P2P_HALO + ex.halo_srcs[threadIdx.x], expected, ex.spin_limit);
+    if ((int)threadIdx.x < ex.nsrc) ok = p2p_wait_acquire(ex.mbox + P2P_HALO + ex.halo_srcs[threadIdx.x], expected, ex.spin_limit);
     const bool all_ok = __all_sync(0xffffffffu, ok);
     if (all_ok) __threadfence_system();  // the pieces were stored before their flag; the barrier below orders the
                                          // other warps' reads behind this one
@@ -114,11 +126,11 @@ __device__ __forceinline__ bool pcg_wait_sums(const PcgExchange &ex, int phase, 
     const double expected = pcg_seq(ex);
     const volatile double *slot = ex.mbox + (phase * P2P_MAXW + (j < ex.world ? j : 0)) * 4;
     bool ok = true;
-    if (j < ex.world) ok = p2p_wait_equal(slot + 2, expected, ex.spin_limit);
+    if (j < ex.world) ok = p2p_wait_acquire(const_cast<const double *>(slot) + 2, expected, ex.spin_limit);
     const bool all_ok = __all_sync(0xffffffffu, ok);
     double a = 0.0, b = 0.0;
     if (all_ok) {
-      __threadfence_system();  // the values were stored before their sequence number
+      // the values were stored before their sequence number, which this lane read with an acquire load
       const double mine0 = j < ex.world ? slot[0] : 0.0, mine1 = j < ex.world ? slot[1] : 0.0;  // one load per lane
       for (int r = 0; r < ex.world; ++r) {  // added in rank order, on every block of every rank
         a = __dadd_rn(a, __shfl_sync(0xffffffffu, mine0, r));
