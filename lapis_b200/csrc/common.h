@@ -56,4 +56,9 @@ struct lapis_b200_csr {
   // when no row has more than 32 entries: up to there it returns the same bits as the chunk kernels.
   int64_t max_row_len;
   int device;
+  // Second plan for the warp-walk kernel on small matrices: ranges of walk_tile entries (null: it uses blk_row).
+  int64_t *walk_plan;
+  double *walk_carry;
+  int64_t walk_nblk;
+  int walk_tile;
 };

@@ -53,7 +53,7 @@ constexpr int SPMV_LONG_ROW = 32;     // rows with more in-chunk entries than th
 // ---------------------------------------------------------------------------
 template <typename I>
 __global__ void spmv_plan_kernel(const I *__restrict__ pos, int64_t nrows, int64_t nblk,
-                                 int64_t *__restrict__ plan) {
+                                 int64_t *__restrict__ plan, int tile = SPMV_TILE) {
   int64_t b = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (b > nblk) return;
   if (b == nblk) {
@@ -64,7 +64,7 @@ __global__ void spmv_plan_kernel(const I *__restrict__ pos, int64_t nrows, int64
     plan[0] = 0;
     return;
   }
-  const int64_t c0 = ((int64_t)pos[0] & ~(int64_t)3) + b * (int64_t)SPMV_TILE;
+  const int64_t c0 = ((int64_t)pos[0] & ~(int64_t)3) + b * (int64_t)tile;
   int64_t lo = 0, hi = nrows;
   while (lo < hi) {
     int64_t mid = lo + ((hi - lo) >> 1);
@@ -663,13 +663,14 @@ __device__ __forceinline__ double load_x_ordered(const double *p) {  // volatile
 }
 
 constexpr int SPMV_WALK_THREADS = 128;
+constexpr int SPMV_WALK_FINE_TILE = 512;  // entries per warp on matrices too small to fill the SMs with 2048-entry ranges
 constexpr int SPMV_WALK_STEP = 128;  // entries per step: four per lane
 
 template <typename I, bool FUSE_DOT>
 __global__ void __launch_bounds__(SPMV_WALK_THREADS, FUSE_DOT ? 6 : 8)
 spmv_walk_kernel(const I *__restrict__ pos, const I *__restrict__ crd, const double *__restrict__ val,
                  const int64_t *__restrict__ plan, int64_t abase, int64_t base, int64_t nnz_end, int64_t nrows,
-                 int64_t nblk, const double *__restrict__ x, double *__restrict__ y, int accumulate,
+                 int64_t nblk, int tile, const double *__restrict__ x, double *__restrict__ y, int accumulate,
                  double *__restrict__ carry, const double *__restrict__ dotvec, double *__restrict__ blk_partial,
                  const int *__restrict__ skip_flag) {
   constexpr unsigned FULL = 0xffffffffu;
@@ -679,8 +680,8 @@ spmv_walk_kernel(const I *__restrict__ pos, const I *__restrict__ crd, const dou
   const int lane = threadIdx.x & 31;
   const int64_t w = (int64_t)blockIdx.x * (SPMV_WALK_THREADS / 32) + (threadIdx.x >> 5);
   if (w >= nblk) return;
-  const int64_t c_begin = abase + w * SPMV_TILE;
-  const int64_t c_end = (c_begin + SPMV_TILE < nnz_end) ? c_begin + SPMV_TILE : nnz_end;
+  const int64_t c_begin = abase + w * tile;  // tile: entries per warp, the granularity of the plan this launch uses
+  const int64_t c_end = (c_begin + tile < nnz_end) ? c_begin + tile : nnz_end;
   int64_t r_cur = plan[w];
   double open = 0.0;  // sum so far of the row that is still open; meaningful in lane 0
   double dot_local = 0.0;
@@ -879,7 +880,7 @@ constexpr int spmv_pipe_smem_bytes(int threads) {
 template <typename I>
 __global__ void spmv_fixup_kernel(const I *__restrict__ pos, const int64_t *__restrict__ plan, int64_t abase,
                                   int64_t nblk, int64_t nrows, const double *__restrict__ carry,
-                                  double *__restrict__ y, const int *__restrict__ skip_flag) {
+                                  double *__restrict__ y, const int *__restrict__ skip_flag, int tile) {
   // Launched with programmatic stream serialization: the blocks may already be resident while the SpMV
   // kernel drains; nothing is read before that kernel has completed and its writes are visible.
   asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -889,8 +890,8 @@ __global__ void spmv_fixup_kernel(const I *__restrict__ pos, const int64_t *__re
   const int64_t q = plan[b + 1];
   if (q >= nrows) return;
   const int64_t start = (int64_t)pos[q];
-  const int64_t c0 = abase + b * (int64_t)SPMV_TILE;
-  if (start >= c0 + SPMV_TILE) return;             // row q starts in a later chunk: nothing carried
+  const int64_t c0 = abase + b * (int64_t)tile;
+  if (start >= c0 + tile) return;                   // row q starts in a later chunk: nothing carried
   if (b > 0 && plan[b] == q && start < c0) return;  // chunk b-1 carried into q too: not the head of the run
   double acc = carry[b];
   for (int64_t b2 = b + 1; b2 < nblk - 1 && plan[b2 + 1] == q; ++b2) acc = __dadd_rn(acc, carry[b2]);
@@ -1209,6 +1210,26 @@ static int launch_pipe(const lapis_b200_csr *h, int ctas_per_sm, const double *x
   return LAPIS_OK;
 }
 
+// Adds the carries of a launch over `nblk` chunks of `tile` entries to their rows.
+template <typename I>
+static int launch_fixup(const lapis_b200_csr *h, const int64_t *plan, const double *carry, int64_t nblk, int tile, double *y,
+                        const int *skip_flag, cudaStream_t st) {
+  if (nblk <= 1) return LAPIS_OK;
+  const I *pos = static_cast<const I *>(h->pos);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)((nblk - 1 + 255) / 256));
+  cfg.blockDim = dim3(256);
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;  // lets the fix-up blocks become resident while the SpMV kernel drains
+  LAPIS_CUDA_TRY(cudaLaunchKernelEx(&cfg, spmv_fixup_kernel<I>, pos, plan, (int64_t)(h->base & ~(int64_t)3), nblk,
+                                    (int64_t)h->nrows, carry, y, skip_flag, tile));
+  return LAPIS_OK;
+}
+
 // Whether spmv_launch will run the one-thread-per-row kernel for this handle (the variant that can carry the
 // head and tail of a PCG iteration's first pass).
 static bool uses_rowthread(const lapis_b200_csr *h) {
@@ -1270,15 +1291,26 @@ static int launch_spmv(const lapis_b200_csr *h, const double *x, double *y, int 
     const I *crd = static_cast<const I *>(h->crd);
     const int64_t abase = h->base & ~(int64_t)3, nnz_end = h->base + h->nnz;
     constexpr int WPB = SPMV_WALK_THREADS / 32;
-    const unsigned grid = (unsigned)((h->nblk + WPB - 1) / WPB);
-    if (dotvec != nullptr)
-      spmv_walk_kernel<I, true><<<grid, SPMV_WALK_THREADS, 0, st>>>(pos, crd, h->val, h->blk_row, abase, h->base, nnz_end,
-                                                                    h->nrows, h->nblk, x, y, accumulate, h->carry, dotvec,
-                                                                    blk_partial, skip_flag);
-    else
-      spmv_walk_kernel<I, false><<<grid, SPMV_WALK_THREADS, 0, st>>>(pos, crd, h->val, h->blk_row, abase, h->base, nnz_end,
-                                                                     h->nrows, h->nblk, x, y, accumulate, h->carry, nullptr,
-                                                                     nullptr, skip_flag);
+    if (dotvec != nullptr || h->walk_plan == nullptr) {
+      // chunks of the shared plan (the consumers of the fused dot product expect one partial per chunk)
+      const unsigned grid = (unsigned)((h->nblk + WPB - 1) / WPB);
+      if (dotvec != nullptr)
+        spmv_walk_kernel<I, true><<<grid, SPMV_WALK_THREADS, 0, st>>>(pos, crd, h->val, h->blk_row, abase, h->base, nnz_end,
+                                                                      h->nrows, h->nblk, SPMV_TILE, x, y, accumulate, h->carry,
+                                                                      dotvec, blk_partial, skip_flag);
+      else
+        spmv_walk_kernel<I, false><<<grid, SPMV_WALK_THREADS, 0, st>>>(pos, crd, h->val, h->blk_row, abase, h->base, nnz_end,
+                                                                       h->nrows, h->nblk, SPMV_TILE, x, y, accumulate, h->carry,
+                                                                       nullptr, nullptr, skip_flag);
+    } else {
+      // a small matrix: shorter ranges per warp (the handle's second plan), so that the warps fill the SMs evenly
+      const unsigned grid = (unsigned)((h->walk_nblk + WPB - 1) / WPB);
+      spmv_walk_kernel<I, false><<<grid, SPMV_WALK_THREADS, 0, st>>>(pos, crd, h->val, h->walk_plan, abase, h->base, nnz_end,
+                                                                     h->nrows, h->walk_nblk, h->walk_tile, x, y, accumulate,
+                                                                     h->walk_carry, nullptr, nullptr, skip_flag);
+      LAPIS_CUDA_TRY(cudaGetLastError());
+      return launch_fixup<I>(h, h->walk_plan, h->walk_carry, h->walk_nblk, h->walk_tile, y, skip_flag, st);
+    }
   } else if (v.threads < 0) {  // persistent bulk-copy kernel: threads = -256 or -512, minb = blocks per SM
     int rc;
     if (v.threads == -256)
@@ -1324,22 +1356,7 @@ static int launch_spmv(const lapis_b200_csr *h, const double *x, double *y, int 
   { return fail(LAPIS_EBADARG, "LAPIS_B200_SPMV names an unknown kernel variant"); }
 #undef LAPIS_V
   LAPIS_CUDA_TRY(cudaGetLastError());
-  if (h->nblk > 1) {
-    const I *pos = static_cast<const I *>(h->pos);
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)((h->nblk - 1 + 255) / 256));
-    cfg.blockDim = dim3(256);
-    cfg.stream = st;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;  // lets the fix-up blocks become resident while the SpMV kernel drains
-    LAPIS_CUDA_TRY(cudaLaunchKernelEx(&cfg, spmv_fixup_kernel<I>, pos, (const int64_t *)h->blk_row,
-                                      (int64_t)(h->base & ~(int64_t)3), (int64_t)h->nblk, (int64_t)h->nrows,
-                                      (const double *)h->carry, y, skip_flag));
-  }
-  return LAPIS_OK;
+  return launch_fixup<I>(h, h->blk_row, h->carry, h->nblk, SPMV_TILE, y, skip_flag, st);
 }
 
 int spmv_launch(const lapis_b200_csr *h, const double *x, double *y, int accumulate,
@@ -1451,12 +1468,29 @@ extern "C" int lapis_b200_csr_create(lapis_b200_csr_t *out, int idx_bytes, int64
   h->tuned_threads = h->tuned_minb = h->tuned_hint = 0;
   h->max_row_len = -1;
   h->device = dev;
+  h->walk_plan = nullptr;
+  h->walk_carry = nullptr;
+  h->walk_nblk = 0;
+  h->walk_tile = 0;
+  // The warp-walk kernel gives one warp a range of entries.  With 2048-entry ranges a matrix needs about eight
+  // times as many ranges as the GPU holds warps (32 per SM) before the last, partly filled round of warps stops
+  // mattering; smaller matrices (a row block of a partitioned one) get a second plan of 512-entry ranges.
+  const int64_t resident_warps = (int64_t)sm_count() * 32;
+  if (nblk > 1 && nblk < 8 * resident_warps) {
+    h->walk_tile = SPMV_WALK_FINE_TILE;
+    h->walk_nblk = (ends[1] - (ends[0] & ~(int64_t)3) + h->walk_tile - 1) / h->walk_tile;
+  }
   cudaError_t e = cudaMalloc(&h->blk_row, (size_t)(nblk + 1) * sizeof(int64_t));
   if (e == cudaSuccess) e = cudaMalloc(&h->blk_partial, (size_t)nblk * sizeof(double));
   if (e == cudaSuccess) e = cudaMalloc(&h->carry, (size_t)nblk * sizeof(double));
+  if (e == cudaSuccess && h->walk_nblk > 0) e = cudaMalloc(&h->walk_plan, (size_t)(h->walk_nblk + 1) * sizeof(int64_t));
+  if (e == cudaSuccess && h->walk_nblk > 0) e = cudaMalloc(&h->walk_carry, (size_t)h->walk_nblk * sizeof(double));
   if (e != cudaSuccess) {
     cudaFree(h->blk_row);
     cudaFree(h->blk_partial);
+    cudaFree(h->carry);
+    cudaFree(h->walk_plan);
+    cudaFree(h->walk_carry);
     delete h;
     return fail(LAPIS_ECUDA, "csr_create: cudaMalloc failed: %s", cudaGetErrorString(e));
   }
@@ -1465,11 +1499,22 @@ extern "C" int lapis_b200_csr_create(lapis_b200_csr_t *out, int idx_bytes, int64
     spmv_plan_kernel<int32_t><<<pgrid, 256, 0, st>>>(static_cast<const int32_t *>(d_pos), nrows, nblk, h->blk_row);
   else
     spmv_plan_kernel<int64_t><<<pgrid, 256, 0, st>>>(static_cast<const int64_t *>(d_pos), nrows, nblk, h->blk_row);
+  if (h->walk_nblk > 0) {
+    const unsigned wgrid = (unsigned)((h->walk_nblk + 1 + 255) / 256);
+    if (idx_bytes == 4)
+      spmv_plan_kernel<int32_t><<<wgrid, 256, 0, st>>>(static_cast<const int32_t *>(d_pos), nrows, h->walk_nblk, h->walk_plan,
+                                                       h->walk_tile);
+    else
+      spmv_plan_kernel<int64_t><<<wgrid, 256, 0, st>>>(static_cast<const int64_t *>(d_pos), nrows, h->walk_nblk, h->walk_plan,
+                                                       h->walk_tile);
+  }
   e = cudaGetLastError();
   if (e != cudaSuccess) {
     cudaFree(h->blk_row);
     cudaFree(h->blk_partial);
     cudaFree(h->carry);
+    cudaFree(h->walk_plan);
+    cudaFree(h->walk_carry);
     delete h;
     return fail(LAPIS_ECUDA, "csr_create: plan kernel launch failed: %s", cudaGetErrorString(e));
   }
@@ -1587,6 +1632,8 @@ extern "C" int lapis_b200_csr_destroy(lapis_b200_csr_t h) {
   cudaFree(h->blk_row);
   cudaFree(h->blk_partial);
   cudaFree(h->carry);
+  cudaFree(h->walk_plan);
+  cudaFree(h->walk_carry);
   delete h;
   return LAPIS_OK;
 }
@@ -1711,6 +1758,10 @@ extern "C" int lapis_b200_spmv_f64_noalloc(int idx_bytes, int64_t nrows, int64_t
   h.tuned_threads = h.tuned_minb = h.tuned_hint = 0;
   h.max_row_len = -1;
   h.device = dev;
+  h.walk_plan = nullptr;
+  h.walk_carry = nullptr;
+  h.walk_nblk = 0;
+  h.walk_tile = 0;
   const unsigned pgrid = (unsigned)((nblk + 1 + 255) / 256);
   if (idx_bytes == 4)
     spmv_plan_kernel<int32_t><<<pgrid, 256, 0, st>>>(static_cast<const int32_t *>(d_pos), nrows, nblk, plan);
