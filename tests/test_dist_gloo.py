@@ -21,7 +21,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, grid, iters, out_dir):
+def _worker(rank, world, port, grid, iters, out_dir, zhalo=False):
     sys.path.insert(0, ROOT)
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
@@ -54,8 +54,11 @@ def _worker(rank, world, port, grid, iters, out_dir):
     rr0, rz = allsum(oracle.dot(r, r), oracle.dot(r, z))
     initres = np.sqrt(rr0)
     it = 1
+    z_ext = torch.zeros(halo.window_len, dtype=torch.float64)
+    halo.exchange(p_ext)  # the halo of the first p travels as p
     while True:
-        halo.exchange(p_ext)
+        if not zhalo:
+            halo.exchange(p_ext)
         Ap = oracle.spmv(lpos, lcrd, lval, p_ext.numpy(), np.zeros(n))
         (pAp,) = allsum(oracle.dot(p, Ap))
         alpha = rz / pAp
@@ -68,19 +71,27 @@ def _worker(rank, world, port, grid, iters, out_dir):
             break
         beta = rz_new / rz
         rz = rz_new
-        p[:] = oracle.axpby(1.0, z, beta, p)
+        if zhalo:
+            # the schedule of the fused GPU passes: the neighbours' rows of z arrive with the second pair of sums,
+            # and every rank updates its whole window of p, halo included, itself
+            z_ext.numpy()[off:off + n] = z
+            halo.exchange(z_ext)
+            p_ext.numpy()[:] = oracle.axpby(1.0, z_ext.numpy(), beta, p_ext.numpy())
+        else:
+            p[:] = oracle.axpby(1.0, z, beta, p)
         it += 1
     np.savez(os.path.join(out_dir, f"rank{rank}.npz"), x=x, r0=r0, r1=r1, relres=relres, it=it)
     dist.barrier()
     dist.destroy_process_group()
 
 
+@pytest.mark.parametrize("zhalo", [False, True], ids=["halo_of_p", "halo_from_z"])
 @pytest.mark.parametrize("world", [2, 3])
-def test_row_partitioned_pcg_reproduces_single_rank(tmp_path, world):
+def test_row_partitioned_pcg_reproduces_single_rank(tmp_path, world, zhalo):
     from lapis_b200 import workloads as w
     from oracle import oracle
     grid, iters = 24, 30
-    mp.spawn(_worker, args=(world, _free_port(), grid, iters, str(tmp_path)), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, _free_port(), grid, iters, str(tmp_path), zhalo), nprocs=world, join=True)
     d = w.pcg_laplacian(grid)
     xo, io, ro = oracle.pcg(d["pos"], d["crd"], d["val"], d["b"], d["dinv"], 0.0, iters)
     x = np.zeros(grid * grid)
@@ -123,3 +134,33 @@ def test_row_partitioned_spmv_is_bit_identical(tmp_path):
     d = w.spmv_power_law(1 << 12)
     ref = oracle.spmv(d["pos"], d["crd"], d["val"], d["x"], np.zeros(1 << 12))
     assert np.array_equal(np.load(tmp_path / "y.npy"), ref)   # rows are independent: same bits
+
+
+def _dropout_worker(rank, world, port, out_dir):
+    """Rank 1 leaves between two steps; rank 0 learns of it from the short timeout of its next collective."""
+    import datetime
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=3))
+    t = torch.ones(2, dtype=torch.float64)
+    dist.all_reduce(t)                       # step 1: both ranks take part
+    assert float(t[0]) == world
+    if rank == 1:
+        os._exit(0)                          # leaves between steps, nothing in flight
+    outcome = "completed"
+    try:
+        dist.all_reduce(t)                   # step 2: the peer never joins
+    except Exception as exc:                 # the process-group timeout ends the collective with an error
+        outcome = "peer lost: " + type(exc).__name__
+    with open(os.path.join(out_dir, "rank0.txt"), "w") as f:
+        f.write(outcome)
+    os._exit(0)
+
+
+def test_a_rank_that_leaves_is_noticed_by_the_others(tmp_path):
+    """Failure detection on the host side of the multi-rank solver, without a GPU and without a hang: a rank
+    that exits between two steps makes the next collective of the remaining rank end with an error after the
+    process group's (short) timeout, instead of blocking for ever."""
+    mp.spawn(_dropout_worker, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
+    assert open(tmp_path / "rank0.txt").read().startswith("peer lost")
