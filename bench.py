@@ -85,7 +85,7 @@ def measured_peaks():
 class ClockSampler:
     """Samples SM clocks and throttle reasons of one GPU while the timed region runs (read-only NVML)."""
 
-    def __init__(self, index: int, period_s: float = 0.02):
+    def __init__(self, index: int, period_s: float = 0.005):
         self.index, self.period = index, period_s
         self.samples, self.reasons, self.max_mhz = [], set(), None
         self._stop = threading.Event()
