@@ -83,11 +83,11 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons of one GPU while the timed region runs (read-only NVML)."""
+    """Samples SM clock, power draw and throttle reasons of one GPU while the timed region runs (read-only NVML)."""
 
     def __init__(self, index: int, period_s: float = 0.005):
         self.index, self.period = index, period_s
-        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self.samples, self.watts, self.reasons, self.max_mhz, self.limit_w = [], [], set(), None, None
         self._stop = threading.Event()
         self._thread = None
         try:
@@ -98,6 +98,11 @@ class ClockSampler:
             self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM)
         except Exception:
             self._nvml = None
+            return
+        try:
+            self.limit_w = pynvml.nvmlDeviceGetEnforcedPowerLimit(self._h) / 1000.0
+        except Exception:
+            pass
 
     def _loop(self):
         nv = self._nvml
@@ -111,6 +116,7 @@ class ClockSampler:
         while not self._stop.is_set():
             try:
                 self.samples.append(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM))
+                self.watts.append(nv.nvmlDeviceGetPowerUsage(self._h) / 1000.0)
                 mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self._h)
                 for k, bit in names.items():
                     if mask & bit:
@@ -129,7 +135,8 @@ class ClockSampler:
         if self._thread is not None:
             self._thread.join()
         return {"sm_mhz": statistics.median(self.samples) if self.samples else None,
-                "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(self.samples)}
+                "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(self.samples),
+                "power_w": statistics.median(self.watts) if self.watts else None, "power_limit_w": self.limit_w}
 
 
 def physical_cores() -> int:
@@ -340,8 +347,8 @@ NCU_TRAFFIC = {
     "spmv_pipe_kernel": 3.160e9,    # same list
     "spmm": 3.387e10,               # profiles/spmm_row_kernel_config3.md
     "bgemm": 1.036e9,               # profiles/bgemm_tcgen05_kernel.md (4096 x 128^3)
-    "gemm": 3.455e9,                # profiles/bgemm_tcgen05_kernel.md (8192^3)
-    "pcg": 2.69e9,                  # profiles/pcg_iteration_config5.md (all kernels of one iteration)
+    "gemm": 8.15e9,                 # profiles/bgemm_tcgen05_kernel.md (8192^3, K in segments of 1024)
+    "pcg": 2.715e9,                 # profiles/pcg_iteration_config5.md (the three kernels of one iteration)
 }
 
 
@@ -734,12 +741,116 @@ def run_ours(args, d, hx: Harness, cpu_base):
     print(json.dumps(line), flush=True)
 
 
+def run_formats(args):
+    """The neighbouring kernels of the path (CSRV batched SpMM, DCSR SpMM, hitting-time moments) on one GPU: device
+    time with operands resident, algorithmic GB/s against the measured copy bandwidth, and the CPU restatement on
+    a sample of the same inputs.  One JSON line per kernel; these are not the headline metric."""
+    import torch
+    from lapis_b200 import device as D
+    from lapis_b200 import workloads as w
+    from oracle import oracle
+    dev = torch.device("cuda:0")
+    peaks, peak_kind = measured_peaks()
+    t = lambda a: torch.as_tensor(np.ascontiguousarray(a)).to(dev)
+    steps = max(3, min(args.steps, 20))
+
+    def gpu_ms(fn):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / steps
+
+    def line(kernel, workload, ms, nbytes, cpu_ms, extra):
+        gbs = nbytes / (ms * 1e-3) * 1e-9
+        out = {"workload": "formats", "kernel": kernel, "case": workload, "ms": ms, "algorithmic_bytes": int(nbytes),
+               "gbs": gbs, "frac_of_copy_peak": gbs / peaks["hbm_gbs"], "peak_source": peak_kind,
+               "cpu_ms_1_thread": cpu_ms, "steps": steps}
+        out.update(extra)
+        print(json.dumps(out), flush=True)
+
+    # CSRV batched SpMM: 32 stored fibers per row, fibers of 8, dh = 64 (2 KiB rows of B and C)
+    n = 1 << (14 if args.small else 17)
+    sp = w.spmm_uniform(n, per_row=32, k=1, idx_dtype=np.int32)
+    nh, dh = 8, 64
+    rng = np.random.default_rng(12)
+    nnz = len(sp["crd"])
+    val = rng.standard_normal(nnz * nh).astype(np.float32)
+    B = rng.standard_normal((n, dh, nh)).astype(np.float32)
+    dpos, dcrd, dval, dB = t(sp["pos"]), t(sp["crd"]), t(val), t(B)
+    C = torch.zeros((n, dh, nh), dtype=torch.float32, device=dev)
+    ms = gpu_ms(lambda: D.bspmm_csrv(dpos, dcrd, dval, dB, n, C))
+    rows_cpu = min(n, 1 << 12)
+    end = int(sp["pos"][rows_cpu])
+    t0 = time.perf_counter()
+    oracle.bspmm(sp["pos"][:rows_cpu + 1], sp["crd"][:end], val[:end * nh], B)
+    cpu_ms = (time.perf_counter() - t0) * 1e3 * n / rows_cpu
+    line("bspmm_csrv_kernel", f"CSRV {n} x {n}, 32 per row, nh 8, dh 64, fp32, int32 indices", ms,
+         nnz * (4 + 4 * nh) + 4 * (n + 1) + 3 * 4 * n * dh * nh, cpu_ms,
+         {"gathered_B_bytes": nnz * dh * nh * 4, "cpu_sample": f"first {rows_cpu} rows, scaled by rows"})
+    del dB, C, dval
+
+    # DCSR SpMM: every other row stored, 32 per stored row, k = 64
+    n = 1 << (15 if args.small else 19)
+    sp = w.spmm_uniform(n, per_row=32, k=64, idx_dtype=np.int64)
+    nnz = len(sp["crd"])
+    i1 = np.arange(0, 2 * n, 2, dtype=np.int64)
+    dB = t(sp["B"])
+    Cd = torch.zeros((2 * n, 64), dtype=torch.float64, device=dev)
+    di1, dp2, di2, dv = t(i1), t(sp["pos"]), t(sp["crd"]), t(sp["val"])
+    ms = gpu_ms(lambda: D.spmm_dcsr(di1, dp2, di2, dv, dB, Cd, n))
+    rows_cpu = min(n, 1 << 13)
+    t0 = time.perf_counter()
+    oracle.spmm_dcsr(i1[:rows_cpu], sp["pos"][:rows_cpu + 1], sp["crd"], sp["val"], sp["B"], np.zeros((2 * rows_cpu, 64)))
+    cpu_ms = (time.perf_counter() - t0) * 1e3 * n / rows_cpu
+    line("spmm_dcsr_kernel", f"DCSR {2 * n} x {n}, {n} stored rows, 32 per row, k 64, fp64, int64 indices", ms,
+         nnz * 16 + 8 * (2 * n + 1) + 3 * 8 * n * 64, cpu_ms,
+         {"gathered_B_bytes": nnz * 64 * 8, "cpu_sample": f"first {rows_cpu} stored rows, scaled by rows"})
+    del dB, Cd
+
+    # hitting-time moments on a grid graph: adjacency of the 5-point stencil (unit weights), d = degree
+    def grid_graph(gg):
+        pos, crd, _ = w.laplacian_2d(gg, idx_dtype=np.int32)
+        rows = np.repeat(np.arange(gg * gg), np.diff(pos))
+        off = crd != rows
+        apos_ = np.concatenate([[0], np.cumsum(np.bincount(rows[off], minlength=gg * gg))]).astype(np.int32)
+        mask_ = np.ones(gg * gg)
+        mask_[:: gg * 7 + 3] = 0.0
+        return apos_, crd[off].astype(np.int32), np.diff(apos_).astype(np.float64), mask_
+
+    g = 512 if args.small else 2048
+    apos, acrd, dvec, mask = grid_graph(g)
+    A = D.CsrMatrix.from_host(apos, acrd, np.ones(len(acrd)), (g * g, g * g), dev, tune=True)
+    dm, dd = t(mask), t(dvec)
+    A.mht(dm, dd, 0.95, 0.0, 100)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    _, _, iters, _ = A.mht(dm, dd, 0.95, 0.0, 100, info=True)
+    torch.cuda.synchronize()
+    ms = (time.perf_counter() - t0) * 1e3 / sum(iters)
+    gc = min(g, 512)
+    cpos, ccrd, cd, cmask = (apos, acrd, dvec, mask) if gc == g else grid_graph(gc)
+    t0 = time.perf_counter()
+    oracle.mht(cpos, ccrd, np.ones(len(ccrd)), cmask, cd, 0.95, 0.0, 8)
+    cpu_ms = (time.perf_counter() - t0) * 1e3 / 16 * (g * g) / (gc * gc)
+    nn, nnz = g * g, len(acrd)
+    line("mht passes (spmv + mht_update + mht_direction)", f"hitting-time moments, {g} x {g} grid graph, int32 indices, "
+         f"{sum(iters)} iterations over the two solves (host-timed, whole solve)", ms,
+         nnz * 12 + 4 * (nn + 1) + 19 * 8 * nn, cpu_ms, {"cpu_sample": f"{gc} x {gc} grid, 16 iterations, scaled by rows"})
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=None)
     ap.add_argument("--warmup", type=int, default=None)
-    ap.add_argument("--workload", default="spmv", choices=["spmv", "spmv1", "spmm", "pcg", "bgemm", "gemm"])
+    ap.add_argument("--workload", default="spmv", choices=["spmv", "spmv1", "spmm", "pcg", "bgemm", "gemm", "formats"],
+                    help="'formats' times the CSRV, DCSR and hitting-time kernels on one GPU (one line per kernel)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--comm", default="p2p", choices=["p2p", "nccl"],
                     help="exchange of the row-partitioned PCG on several GPUs: own peer-memory kernels or NCCL")
@@ -749,7 +860,8 @@ def main():
     ap.add_argument("--no-secondary", action="store_true", help="skip the PCG / GEMM figures of the default run")
     ap.add_argument("--shrink", type=int, default=0, help="divide the SpMV/SpMM row count by 2^SHRINK (profiler captures)")
     args = ap.parse_args()
-    defaults = {"spmv": (500, 10), "spmv1": (1000, 10), "spmm": (50, 5), "pcg": (200, 5), "bgemm": (200, 10), "gemm": (20, 3)}
+    defaults = {"spmv": (500, 10), "spmv1": (1000, 10), "spmm": (50, 5), "pcg": (200, 5), "bgemm": (200, 10), "gemm": (20, 3),
+                "formats": (20, 3)}
     if args.steps is None:
         args.steps = defaults[args.workload][0] if args.impl == "ours" else 10
     if args.warmup is None:
@@ -759,6 +871,13 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
 
+    if args.workload == "formats":
+        if rank == 0 and args.impl == "ours":
+            release_main_thread()
+            run_formats(args)
+        elif rank == 0:
+            print(json.dumps({"impl": "reference", "unavailable": "the formats lines time the CPU restatement beside each kernel"}))
+        return 0
     if args.impl == "reference":
         if rank != 0:
             return 0
