@@ -409,4 +409,6 @@ class DistPcg:
             err = self.comm_error()
             if err != 0.0:
                 raise RuntimeError(f"pcg: a peer did not deliver in time (exchange {int(err)}: 1-3 scalar sums, 9 halo)")
+            # a persistent SpMV block whose bounded wait gave up leaves Ap incomplete: the solve is not valid then
+            self._check(self._lib.lapis_b200_spmv_status(self._stream()))
         return self.x, iters, relres
