@@ -178,14 +178,19 @@ def test_backend_refuses_functions_that_only_resemble_a_known_one():
     assert _classify_text(padded) == [("spmv", "i32")]
 
 
-@pytest.mark.skipif(not os.path.isdir("/root/reference/examples"), reason="needs a checkout of the LAPIS project")
+# a checkout of the LAPIS project: LAPIS_SOURCE_DIR, else a directory `reference` beside this repository
+_LAPIS_SRC = os.environ.get("LAPIS_SOURCE_DIR") or os.path.join(
+    os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "reference")
+
+
+@pytest.mark.skipif(not os.path.isdir(os.path.join(_LAPIS_SRC, "examples")), reason="needs a checkout of the LAPIS project")
 def test_backend_accepts_the_reference_examples_as_written():
     """The module texts of the LAPIS examples, read from the checkout, bind without an edit."""
     want = {"pcg_solve.py": [("pcg", "i32")], "hitting_times.py": [("mht", "i32"), ("normalize_mom2", "")],
             "spmv_noalloc.py": [("spmv", "i32")], "gemm_no_alloc.py": [("matmul", "")],
             "batched_gemm_no_alloc.py": [("batch_matmul", "")]}
     for fname, kinds in want.items():
-        text = open(os.path.join("/root/reference/examples", fname)).read()
+        text = open(os.path.join(_LAPIS_SRC, "examples", fname)).read()
         module = re.search(r'=\s*"""(.*?)"""', text, re.S).group(1)
         assert _classify_text(module) == kinds, fname
 
