@@ -324,61 +324,85 @@ bgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
     // accumulator row = TMEM lane; a warp may touch lanes 32*(warp%4)..+31
     const int q = warp & 3;
     float *stile = reinterpret_cast<float *>(smem + STAGES * STAGE_BYTES + 256) + (warp - 6) * 32 * EPI_PITCH;
+    constexpr int NC = BN / 32;  // 32-column chunks of a tile
+    static_assert(NC % 2 == 0 && NC >= 2, "the epilogue walks the chunks in pairs");
+    auto warp_rows = [&](int t) {  // this warp's 32 rows of tile t in C
+      const TileCoord tc = tile_coord(t, tm, tn, BN);
+      return C + ((size_t)tc.batch * M + tc.m0 + 32 * q) * (size_t)N + tc.n0;
+    };
+    // C_in chunk (32 rows x 32 columns), coalesced: 8 lanes cover the 128 bytes of one row.  Two chunks are
+    // requested together, so that the latency of these loads is paid once per pair.
+    auto load_cin = [&](float4(&cin)[8], const float *cwarp, int c) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        cin[i] = *reinterpret_cast<const float4 *>(cwarp + (size_t)(4 * i + (lane >> 3)) * N + 32 * c + 4 * (lane & 7));
+    };
+    auto drain = [&](const float4(&cin)[8], float *cwarp, int c, uint32_t buf, bool last) {
+      // thread = row in tensor memory; transpose through shared memory so that stores are coalesced.  The 32
+      // columns come in two halves of 16 (the registers of a half are free before the next is read).
+      const uint32_t taddr = tmem_base + buf * BN + ((uint32_t)(32 * q) << 16) + (uint32_t)(32 * c);
+      __syncwarp();
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint32_t r[16];
+        asm volatile(
+            "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+            "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+            : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+              "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+            : "r"(taddr + 16u * half));
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (last && half == 1) {  // the accumulator is in registers: hand it back to the MMA warp
+          asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+          mbar_arrive(&acc_empty[buf]);
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          *reinterpret_cast<float4 *>(stile + lane * EPI_PITCH + 16 * half + 4 * i) =
+              make_float4(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]), __uint_as_float(r[4 * i + 2]),
+                          __uint_as_float(r[4 * i + 3]));
+      }
+      __syncwarp();
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int row = 4 * i + (lane >> 3);
+        const float4 a = *reinterpret_cast<const float4 *>(stile + row * EPI_PITCH + 4 * (lane & 7));
+        float4 o = cin[i];
+        o.x = __fadd_rn(a.x, o.x);
+        o.y = __fadd_rn(a.y, o.y);
+        o.z = __fadd_rn(a.z, o.z);
+        o.w = __fadd_rn(a.w, o.w);
+        *reinterpret_cast<float4 *>(cwarp + (size_t)row * N + 32 * c + 4 * (lane & 7)) = o;
+      }
+    };
     uint32_t it = 0;
     bool ok = true;
     for (int u = 0, t = blockIdx.x; t < total_tiles && ok; ++it) {
       // unit of work: one K segment of one tile; u counts the segments of tile t
-      const TileCoord tc = tile_coord(t, tm, tn, BN);
+      float *cwarp = warp_rows(t);
       if (++u == nseg) {
         u = 0;
         t += gridDim.x;
       }
       const uint32_t buf = it & 1;
-      float *cwarp = C + ((size_t)tc.batch * M + tc.m0 + 32 * q) * (size_t)N + tc.n0;  // this warp's 32 rows
       ok = mbar_wait(&acc_full[buf], (it >> 1) & 1);
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      if (BN == 128) {
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        // C_in chunk (32 rows x 32 columns), coalesced: 8 lanes cover the 128 bytes of one row
-        float4 cin[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i)
-          cin[i] = *reinterpret_cast<const float4 *>(cwarp + (size_t)(4 * i + (lane >> 3)) * N + 32 * c + 4 * (lane & 7));
-        uint32_t r[32];
-        const uint32_t taddr = tmem_base + buf * BN + ((uint32_t)(32 * q) << 16) + (uint32_t)(32 * c);
-        asm volatile(
-            "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-            "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-            "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-            : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-              "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-              "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-              "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-            : "r"(taddr));
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        if (c == BN / 32 - 1) {  // the accumulator is in registers: hand it back to the MMA warp
-          asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-          mbar_arrive(&acc_empty[buf]);
+        for (int c = 0; c < NC; c += 2) {
+          float4 cin_a[8], cin_b[8];
+          load_cin(cin_a, cwarp, c);
+          load_cin(cin_b, cwarp, c + 1);
+          drain(cin_a, cwarp, c, buf, false);
+          drain(cin_b, cwarp, c + 1, buf, c + 2 == NC);
         }
-        // thread = row in tensor memory; transpose through shared memory so that stores are coalesced
-        __syncwarp();
-#pragma unroll
-        for (int i = 0; i < 8; ++i)
-          *reinterpret_cast<float4 *>(stile + lane * EPI_PITCH + 4 * i) =
-              make_float4(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]), __uint_as_float(r[4 * i + 2]),
-                          __uint_as_float(r[4 * i + 3]));
-        __syncwarp();
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const int row = 4 * i + (lane >> 3);
-          const float4 a = *reinterpret_cast<const float4 *>(stile + row * EPI_PITCH + 4 * (lane & 7));
-          float4 o = cin[i];
-          o.x = __fadd_rn(a.x, o.x);
-          o.y = __fadd_rn(a.y, o.y);
-          o.z = __fadd_rn(a.z, o.z);
-          o.w = __fadd_rn(a.w, o.w);
-          *reinterpret_cast<float4 *>(cwarp + (size_t)row * N + 32 * c + 4 * (lane & 7)) = o;
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < NC; ++c) {
+          float4 cin_a[8];
+          load_cin(cin_a, cwarp, c);
+          drain(cin_a, cwarp, c, buf, c + 1 == NC);
         }
       }
     }
