@@ -162,6 +162,8 @@ class DistPcg:
     """Jacobi-preconditioned CG (examples/pcg_solve.py:52-101 in the LAPIS project) on a
     row-partitioned matrix.  Construct on every rank with the same host CSR, b and dinv."""
 
+    GRAPH_UNROLL = 5  # iterations per launch of the larger of the two captured graphs
+
     def __init__(self, pos, crd, val, shape, b, dinv, device, group=None, use_graph: bool = True, comm: str = "p2p",
                  transport_on_one_rank: bool = False, tune: bool = True, fused: bool = True):
         from ._lib import check, load
@@ -388,18 +390,27 @@ class DistPcg:
                 g = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(g):
                     self._iteration(tol, maxiter)
-                self._graph = (g, tol, maxiter)
+                # the same iteration GRAPH_UNROLL times in one graph: a graph launch costs more on the device than the
+                # step from one kernel to the next inside a graph, which shows once a rank's share is small
+                gk = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(gk):
+                    for _ in range(self.GRAPH_UNROLL):
+                        self._iteration(tol, maxiter)
+                self._graph = (g, tol, maxiter, gk)
                 self._init(tol, maxiter)  # capture does not execute; state is still the initial one
             # the captured iteration has its tol / maxiter baked in: other values run as plain launches
-            replay = self._graph is not None and self._graph[1:] == (tol, maxiter)
+            replay = self._graph is not None and self._graph[1:3] == (tol, maxiter)
             i = 0
             done = False
             while not done and i < limit:
                 burst = min(check_every, limit - i)
-                for _ in range(burst):
-                    if replay:
+                if replay:
+                    for _ in range(burst // self.GRAPH_UNROLL):
+                        self._graph[3].replay()
+                    for _ in range(burst % self.GRAPH_UNROLL):
                         self._graph[0].replay()
-                    else:
+                else:
+                    for _ in range(burst):
                         self._iteration(tol, maxiter)
                 i += burst
                 fl = self.flags.cpu()
