@@ -314,13 +314,14 @@ class LAPISModule:
         self._plans[key] = (tuple(weakref.ref(o) for o in (pos, crd, val)), versions, shape, A)
         return A
 
-    def _row_blocks(self, A, pos_dv, nblocks: int = 4):
+    def _row_blocks(self, A, pos_dv, nblocks: int = 0):
         """Handles over nnz-balanced row blocks of a planned matrix (they share its device arrays; a handle
         may start at any row because the plan is built from pos[r0:r1+1]), kept with the plan."""
         from . import partition as part
         from .device import CsrMatrix
         blocks = getattr(A, "_row_blocks", None)
         if blocks is None:
+            nblocks = nblocks or self.PIPELINE_ROW_BLOCKS
             bounds = part.partition_rows(pos_dv.host_view(), nblocks)
             blocks = []
             for g in range(nblocks):
@@ -356,14 +357,16 @@ class LAPISModule:
     # matrix is also kept as two column halves: the half that only reads x[:mid] runs while x[mid:] is still
     # on its way.  Used by spmv(..., sync_host=True) for large x whose host side was modified.
     PIPELINE_MIN_X_BYTES = 8 << 20
+    PIPELINE_ROW_BLOCKS = 4  # row blocks whose results go back to the host one behind the other
 
-    def _column_halves(self, A, pos_dv, crd_dv, val_dv, nblocks: int = 4):
+    def _column_halves(self, A, pos_dv, crd_dv, val_dv, nblocks: int = 0):
         """(mid, handle over columns [0, mid), row-block handles over columns [mid, ncols)), kept with the plan."""
         import torch
         from . import partition as part
         from .device import CsrMatrix
         halves = getattr(A, "_col_halves", None)
         if halves is None:
+            nblocks = nblocks or self.PIPELINE_ROW_BLOCKS
             pos, crd, val = pos_dv.host_view(), crd_dv.host_view(), val_dv.host_view()
             mid = A.ncols // 2
             left = crd < mid
