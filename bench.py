@@ -586,12 +586,15 @@ def run_pcg(args, d, hx: Harness, iterations: int, with_e2e: bool):
     tuned = solver.matrix.tuned_kernel()
     if solver.comm == "nccl":
         launches_per_it = 8 - (1 if tuned[0] == 1 else 0)
+    elif solver.fused and solver._two_pass():
+        launches_per_it = 2
     elif solver.fused:
         launches_per_it = 3 if tuned[0] == 1 else (5 if tuned[0] in (-256, -512) else 6)
     else:
         launches_per_it = (6 if world == 1 and solver.comm == "none" else 12) - (1 if tuned[0] == 1 else 0)
     ms_it = ms / max(1, it)
     roof = hx.hbm_roofline(d["bytes_per_step"] / world, ms_it,
+                           "pcg_spmv_direction_kernel + pcg_update_fused_kernel" if solver.fused and solver._two_pass() else
                            "spmv_rowthread_kernel (pass A) + pcg_update_fused_kernel + pcg_direction(_fused)_kernel",
                            NCU_TRAFFIC["pcg"] / world)
     # check: the relative residual after three iterations against the CPU oracle's (same recurrences, full grid)
@@ -614,7 +617,7 @@ def run_pcg(args, d, hx: Harness, iterations: int, with_e2e: bool):
                "d2h_bytes_per_step": 8 * n / it2, "steps": it2,
                "api": "KokkosBackend.compile(...).pcg -> py_pcg, pinned host buffers, copies amortised over the solve"}
     detail = {"spmv_kernel_tuned": list(tuned), "iterations": int(it), "launches_per_iteration": launches_per_it,
-              "exchange": {"p2p": "stores into peer memory + flags inside the three passes (own kernels)"
+              "exchange": {"p2p": "stores into peer memory + flags inside the passes (own kernels)"
                                   if solver.fused else "stores into peer memory + flags (own kernels between the passes)",
                            "nccl": "NCCL send/recv + allreduce", "none": "none (one rank)"}[solver.comm]}
     return {"value": it / (ms * 1e-3), "ms_per_step": ms_it, "clocks": clocks, "e2e": e2e,

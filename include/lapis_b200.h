@@ -356,6 +356,16 @@ int lapis_b200_pcg_fused_update(void *d_work, int64_t n, int64_t n_p, int64_t p_
                                 double tol, uint64_t maxiter, const lapis_b200_pcg_exchange *exchange, void *stream);
 int lapis_b200_pcg_fused_direction(void *d_work, int64_t n, int64_t n_p, int64_t p_offset, double tol, uint64_t maxiter,
                                    const lapis_b200_pcg_exchange *exchange, void *stream);
+/* Two launches per iteration where the matrix allows it (lapis_b200_pcg_folds_direction(h) != 0: rows short enough
+ * for the one-thread-per-row SpMV kernel): lapis_b200_pcg_fused_spmv_direction is pass A with the direction update
+ * of the iteration before folded in (its SpMV reads z + beta * p_old wherever it gathers and stores the new p into
+ * the second p buffer of the workspace), followed by lapis_b200_pcg_fused_update; lapis_b200_pcg_fused_direction
+ * is not called.  Same bits as the three-launch form.  With an exchange, the stop test of an iteration runs at
+ * the head of the next lapis_b200_pcg_fused_spmv_direction: call it once more after the last update before
+ * reading lapis_b200_pcg_status.  One solve uses one form throughout. */
+int lapis_b200_pcg_folds_direction(lapis_b200_csr_t h);
+int lapis_b200_pcg_fused_spmv_direction(void *d_work, lapis_b200_csr_t h, int64_t n_p, int64_t p_offset, double tol,
+                                        uint64_t maxiter, const lapis_b200_pcg_exchange *exchange, void *stream);
 int lapis_b200_pcg_p2p_set_wait_limit(uint32_t polls);
 /* Copies {done, iters, relres} to the host; synchronises `stream`. */
 int lapis_b200_pcg_status(void *d_work, int *done, uint64_t *iters, double *relres, void *stream);

@@ -76,6 +76,8 @@ _PROTOS = {
     "lapis_b200_pcg_fused_spmv": (c_int, [c_vp, c_vp, c_i64, c_i64, c_dbl, c_u64, c_vp, c_vp]),
     "lapis_b200_pcg_fused_update": (c_int, [c_vp, c_i64, c_i64, c_i64, c_vp, c_vp, c_dbl, c_u64, c_vp, c_vp]),
     "lapis_b200_pcg_fused_direction": (c_int, [c_vp, c_i64, c_i64, c_i64, c_dbl, c_u64, c_vp, c_vp]),
+    "lapis_b200_pcg_folds_direction": (c_int, [c_vp]),
+    "lapis_b200_pcg_fused_spmv_direction": (c_int, [c_vp, c_vp, c_i64, c_i64, c_dbl, c_u64, c_vp, c_vp]),
     "lapis_b200_pcg_p2p_set_wait_limit": (c_int, [ctypes.c_uint32]),
     "lapis_b200_pcg_status": (c_int, [c_vp, ctypes.POINTER(c_int), ctypes.POINTER(c_u64), ctypes.POINTER(c_dbl), c_vp]),
     "lapis_b200_read_matrix_market": (c_int, [ctypes.c_char_p, c_int, ctypes.POINTER(c_i64), ctypes.POINTER(c_i64),

@@ -34,6 +34,8 @@ int spmv_launch(const lapis_b200_csr *h, const double *x, double *y, int accumul
 bool spmv_fuses_pcg_pass(const lapis_b200_csr *h);
 int spmv_launch_pcg_pass(const lapis_b200_csr *h, const double *x, double *y, const double *dotvec, double *blk_partial,
                          const int *skip_flag, cudaStream_t st, const PcgExchange &ex);
+int spmv_launch_pcg_direction_pass(const lapis_b200_csr *h, int64_t p_off, double *pw0, double *pw1, double *Ap,
+                                   double *blk_partial, cudaStream_t st, const PcgExchange &ex);
 
 constexpr int VEC_THREADS = 256;
 constexpr int SUM_THREADS = 1024;
@@ -175,14 +177,15 @@ static inline unsigned vec_grid(int64_t n) {
   return (unsigned)(g < 1 ? 1 : g);
 }
 
-// Workspace layout (doubles): [scalars 8][flags 2 (as int64)][pad to 16][partials 2*G][r n][z n][p n_p][Ap n][zh n_p]
-// where G = 8 * SM count, n_p >= n is the length of the (halo-extended) p buffer and zh is the window-indexed
-// buffer into which neighbours store the rows of z behind this rank's halo of p.
+// Workspace layout (doubles): [scalars 8][flags 2 (as int64)][pad to 16][partials 2*G][r n][z n][p n_p][Ap n][zh n_p][p1 n_p]
+// where G = 8 * SM count, n_p >= n is the length of the (halo-extended) p buffer, zh is the window-indexed
+// buffer of z (the fused passes keep the own rows of z there too; neighbours store the rows behind this rank's
+// halo of p into it) and p1 is the second p buffer of the two-pass form.
 struct PcgWork {
   double *sc;
   long long *fl;
   double *partials;
-  double *r, *z, *p, *Ap, *zh;
+  double *r, *z, *p, *Ap, *zh, *p1;
   unsigned grid;
 };
 
@@ -200,6 +203,7 @@ static PcgWork carve(void *d_work, int64_t n, int64_t n_p) {
   w.p = vecs + 2 * n;
   w.Ap = vecs + 2 * n + n_p;
   w.zh = vecs + 3 * n + n_p;
+  w.p1 = vecs + 3 * n + 2 * n_p;
   w.grid = vec_grid(n);
   return w;
 }
@@ -213,14 +217,16 @@ static unsigned g_p2p_spin_limit = P2P_SPIN_LIMIT;  // polls per bounded wait; l
 // the neighbours' z halo buffers, and the tail's sequence number covers them.
 constexpr int PCG_MAX_FUSED_PIECES = 32;
 __global__ void __launch_bounds__(VEC_THREADS)
-pcg_update_fused_kernel(int64_t n, int64_t p_off, PcgExchange ex, const double *__restrict__ p, const double *__restrict__ Ap,
-                        const double *__restrict__ dinv, double *__restrict__ x, double *__restrict__ r,
-                        double *__restrict__ z, double *__restrict__ partials) {
+pcg_update_fused_kernel(int64_t n, int64_t p_off, PcgExchange ex, const double *p_first, const double *p_second,
+                        const double *__restrict__ Ap, const double *__restrict__ dinv, double *__restrict__ x,
+                        double *__restrict__ r, double *__restrict__ z, double *__restrict__ partials) {
   __shared__ double s_red[VEC_THREADS / 32];
   __shared__ double s_vals[3];
   __shared__ int s_flag;
   __shared__ HaloPiece s_pieces[PCG_MAX_FUSED_PIECES];
   if (ex.fl[FL_DONE] != 0) return;
+  // the own rows of the current p: the two-pass form alternates between two buffers
+  const double *__restrict__ p = reinterpret_cast<const long long *>(ex.sc)[SC_PCUR] != 0 ? p_second : p_first;
   double alpha;
   const int npieces = ex.mbox != nullptr ? ex.npieces : 0;
   if (ex.mbox != nullptr) {
@@ -360,13 +366,13 @@ static PcgExchange make_exchange(const PcgWork &w, const lapis_b200_pcg_exchange
   ex.spin_limit = g_p2p_spin_limit;
   ex.tol = tol;
   ex.maxiter = maxiter;
+  ex.zhalo = w.zh;  // the window-indexed z buffer (own rows and halo)
   if (e != nullptr && e->d_mbox != nullptr) {
     ex.mbox = static_cast<double *>(e->d_mbox);
     ex.peer_mbox = static_cast<const unsigned long long *>(e->d_peer_mbox);
     ex.halo_srcs = static_cast<const int *>(e->d_halo_srcs);
     ex.pieces = static_cast<const HaloPiece *>(e->d_z_pieces);
     ex.halo_ranges = static_cast<const long long *>(e->d_halo_ranges);
-    ex.zhalo = w.zh;
     ex.me = e->me;
     ex.world = e->world;
     ex.nsrc = e->nsrc;
@@ -432,7 +438,7 @@ extern "C" int lapis_b200_mult_f64(int64_t n, const double *d_x, const double *d
 // ---- multi-device callers that put a halo exchange / allreduce between the steps) ---
 extern "C" int64_t lapis_b200_pcg_workspace_bytes(int64_t n, int64_t n_p) {
   if (n < 0 || n_p < n) return -1;
-  return (int64_t)sizeof(double) * (16 + pcg_partials_len() + 3 * n + 2 * n_p);
+  return (int64_t)sizeof(double) * (16 + pcg_partials_len() + 3 * n + 3 * n_p);
 }
 
 extern "C" int lapis_b200_pcg_workspace_layout(int64_t n, int64_t n_p, int64_t *offsets4) {
@@ -455,6 +461,7 @@ extern "C" int lapis_b200_pcg_init(void *d_work, int64_t n, int64_t n_p, int64_t
   cudaStream_t st = as_stream(stream);
   LAPIS_CUDA_TRY(cudaMemsetAsync(w.sc, 0, 16 * sizeof(double), st));
   if (n_p > n) LAPIS_CUDA_TRY(cudaMemsetAsync(w.p, 0, (size_t)n_p * sizeof(double), st));
+  LAPIS_CUDA_TRY(cudaMemsetAsync(w.p1, 0, (size_t)n_p * sizeof(double), st));
   LAPIS_CUDA_TRY(cudaMemsetAsync(w.partials, 0, (size_t)pcg_partials_len() * sizeof(double), st));
   pcg_init_kernel<<<w.grid, VEC_THREADS, 0, st>>>(n, d_b, d_dinv, w.r, w.z, w.p + p_offset, d_x, w.partials);
   sum_partials_kernel<<<1, SUM_THREADS, 0, st>>>(w.partials, w.grid, 2, w.sc + SC_RR, w.sc + SC_RZNEW,
@@ -547,8 +554,9 @@ extern "C" int lapis_b200_pcg_fused_update(void *d_work, int64_t n, int64_t n_p,
   LAPIS_TRY(check_exchange(exchange, "pcg_fused_update"));
   PcgWork w = carve(d_work, n, n_p);
   const PcgExchange ex = make_exchange(w, exchange, tol, maxiter);
-  pcg_update_fused_kernel<<<w.grid, VEC_THREADS, 0, as_stream(stream)>>>(n, p_offset, ex, w.p + p_offset, w.Ap, d_dinv, d_x,
-                                                                         w.r, w.z, w.partials);
+  // z goes into the window-indexed buffer (own rows at the window's own offset)
+  pcg_update_fused_kernel<<<w.grid, VEC_THREADS, 0, as_stream(stream)>>>(n, p_offset, ex, w.p + p_offset, w.p1 + p_offset, w.Ap,
+                                                                         d_dinv, d_x, w.r, w.zh + p_offset, w.partials);
   LAPIS_CUDA_TRY(cudaGetLastError());
   return LAPIS_OK;
 }
@@ -561,11 +569,27 @@ extern "C" int lapis_b200_pcg_fused_direction(void *d_work, int64_t n, int64_t n
   PcgWork w = carve(d_work, n, n_p);
   const PcgExchange ex = make_exchange(w, exchange, tol, maxiter);
   if (ex.mbox == nullptr)  // the stop test and beta are in the scalar block already: the plain pass
-    pcg_direction_kernel<<<w.grid, VEC_THREADS, 0, as_stream(stream)>>>(n, w.sc, w.fl, w.z, w.p + p_offset);
+    pcg_direction_kernel<<<w.grid, VEC_THREADS, 0, as_stream(stream)>>>(n, w.sc, w.fl, w.zh + p_offset, w.p + p_offset);
   else
-    pcg_direction_fused_kernel<<<w.grid, VEC_THREADS, 0, as_stream(stream)>>>(n, p_offset, ex, w.z, w.p);
+    pcg_direction_fused_kernel<<<w.grid, VEC_THREADS, 0, as_stream(stream)>>>(n, p_offset, ex, w.zh + p_offset, w.p);
   LAPIS_CUDA_TRY(cudaGetLastError());
   return LAPIS_OK;
+}
+
+// Whether the matrix is served by the kernel that folds the direction update into the SpMV pass (two launches
+// per iteration: lapis_b200_pcg_fused_spmv_direction, lapis_b200_pcg_fused_update).
+extern "C" int lapis_b200_pcg_folds_direction(lapis_b200_csr_t h) { return h != nullptr && spmv_fuses_pcg_pass(h) ? 1 : 0; }
+
+extern "C" int lapis_b200_pcg_fused_spmv_direction(void *d_work, lapis_b200_csr_t h, int64_t n_p, int64_t p_offset, double tol,
+                                                   uint64_t maxiter, const lapis_b200_pcg_exchange *exchange, void *stream) {
+  clear_error();
+  if (d_work == nullptr || h == nullptr) return fail(LAPIS_EBADARG, "pcg_fused_spmv_direction: null argument");
+  if (h->ncols != n_p || p_offset < 0 || p_offset + h->nrows > n_p)
+    return fail(LAPIS_EBADSHAPE, "pcg_fused_spmv_direction: matrix columns must index the p window");
+  LAPIS_TRY(check_exchange(exchange, "pcg_fused_spmv_direction"));
+  PcgWork w = carve(d_work, h->nrows, n_p);
+  const PcgExchange ex = make_exchange(w, exchange, tol, maxiter);
+  return spmv_launch_pcg_direction_pass(h, p_offset, w.p, w.p1, w.Ap, h->blk_partial, as_stream(stream), ex);
 }
 
 // Reads {done, iters} and relres back (synchronises the stream).
@@ -609,10 +633,16 @@ extern "C" int lapis_b200_pcg_f64(lapis_b200_csr_t h, const double *d_b, const d
   // The same holds here, up to a bound of 2^31 iterations.
   const uint64_t limit = maxiter == 0 ? (1ull << 31) : maxiter;
   const uint64_t check_every = 16;
+  const bool two_pass = lapis_b200_pcg_folds_direction(h) != 0;  // the direction update inside the next SpMV pass
   for (uint64_t i = 1; status == LAPIS_OK && !done && i <= limit; ++i) {
-    status = lapis_b200_pcg_fused_spmv(work, h, n, 0, tol, maxiter, nullptr, st);
-    if (status == LAPIS_OK) status = lapis_b200_pcg_fused_update(work, n, n, 0, d_dinv, d_x, tol, maxiter, nullptr, st);
-    if (status == LAPIS_OK) status = lapis_b200_pcg_fused_direction(work, n, n, 0, tol, maxiter, nullptr, st);
+    if (two_pass) {
+      status = lapis_b200_pcg_fused_spmv_direction(work, h, n, 0, tol, maxiter, nullptr, st);
+      if (status == LAPIS_OK) status = lapis_b200_pcg_fused_update(work, n, n, 0, d_dinv, d_x, tol, maxiter, nullptr, st);
+    } else {
+      status = lapis_b200_pcg_fused_spmv(work, h, n, 0, tol, maxiter, nullptr, st);
+      if (status == LAPIS_OK) status = lapis_b200_pcg_fused_update(work, n, n, 0, d_dinv, d_x, tol, maxiter, nullptr, st);
+      if (status == LAPIS_OK) status = lapis_b200_pcg_fused_direction(work, n, n, 0, tol, maxiter, nullptr, st);
+    }
     if (status == LAPIS_OK && (i % check_every == 0 || i == limit))
       status = lapis_b200_pcg_status(work, &done, &it, &rel, st);
   }

@@ -18,6 +18,15 @@
 //
 // Two points per iteration at which a rank waits for the others, not three.
 //
+// Two-pass form (matrices served by the one-thread-per-row SpMV kernel): pass C is folded into the next
+// iteration's pass A.  That kernel's head is pass C's head (wait for r.r / r.z, stop test, beta); its SpMV reads
+// z + beta * p_old at every column it gathers (the values pass C would have stored, the same bits), stores the
+// own rows and the halo entries of the new p into the second p buffer (the buffers alternate; SC_PCUR names the
+// current one), and its tail is pass C's bookkeeping followed by pass A's tail.  Before the first SpMV of a solve
+// (SC_STAGE == 0) p is read as initialised.  Pass B keeps z in the window-indexed z buffer, own rows included,
+// so that the SpMV can gather from it.  Two launches per iteration; with several ranks the stop test of an
+// iteration runs at the head of the launch after it.
+//
 // A "tail" runs in the block that finishes last (an atomic ticket per pass) and adds the partial sums in a
 // fixed order, so results do not depend on which block that is.  Heads that wait poll this rank's own mailbox
 // (local memory) with a bound; every block of a pass does its own wait and adds the ranks' values in rank
@@ -35,6 +44,8 @@ enum { DERIVE_NONE = 0, DERIVE_INIT = 1, DERIVE_ALPHA = 2, DERIVE_DECIDE = 3, DE
 constexpr int SC_EPOCH = 10;   // header slot holding epoch * 2^32 (row-partitioned solver)
 constexpr int SC_DMP2 = 11;    // header slot: sum of d * (mask*p)^2 of the masked-Laplacian operator
 constexpr int SC_TICKET = 12;  // header slots 12..13 reinterpreted as four unsigned tickets (one per pass)
+constexpr int SC_STAGE = 14;   // header slot (int64): 0 until the first SpMV pass of a solve has run (two-pass form)
+constexpr int SC_PCUR = 15;    // header slot (int64): which of the two p buffers holds the current p (two-pass form)
 
 constexpr int P2P_MAXW = 16;
 constexpr int P2P_HALO = 4 * P2P_MAXW * 4;

@@ -972,6 +972,141 @@ spmv_rowthread_kernel(const I *__restrict__ pos, const I *__restrict__ crd, cons
   }
 }
 
+// ---------------------------------------------------------------------------
+// Pass A of a PCG iteration with the direction update of the iteration before folded in (pcg_fuse.h, two-pass
+// form): the operand of the SpMV at column c is z[c] + beta * p_old[c], which the kernel also stores for its own
+// rows (and the halo entries of its window) as the new p.  Row sums are formed exactly as in
+// spmv_rowthread_kernel, on operand values that have the bits pass C would have stored, so Ap, p and p.Ap are
+// those of the three-pass form.
+// ---------------------------------------------------------------------------
+template <typename I, bool DIR>
+__device__ __forceinline__ double row_piece_sum_pcg(const I *__restrict__ crd, const double *__restrict__ val,
+                                                    const double *__restrict__ zw, const double *__restrict__ pw,
+                                                    double beta, int64_t lo, int64_t hi) {
+  auto operand = [&](int64_t c) {
+    const double pv = __ldg(pw + c);
+    if (!DIR) return pv;
+    return __dadd_rn(__dmul_rn(__ldg(zw + c), 1.0), __dmul_rn(pv, beta));
+  };
+  double acc = 0.0;
+  int64_t j = lo;
+  for (; j + 3 < hi; j += 4) {
+    double a[4], xv[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      a[u] = __ldg(val + j + u);
+      xv[u] = operand((int64_t)__ldg(crd + j + u));
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) acc = __dadd_rn(acc, __dmul_rn(a[u], xv[u]));
+  }
+  for (; j < hi; ++j) acc = __dadd_rn(acc, __dmul_rn(__ldg(val + j), operand((int64_t)__ldg(crd + j))));
+  return acc;
+}
+
+template <typename I, bool DIR>
+__device__ __forceinline__ double pcg_spmv_rows(const I *__restrict__ pos, const I *__restrict__ crd,
+                                                const double *__restrict__ val, int64_t abase, int64_t nrows,
+                                                int64_t ntiles, int64_t p_off, const double *__restrict__ zw,
+                                                const double *__restrict__ pold, double *__restrict__ pnew,
+                                                double beta, double *__restrict__ Ap) {
+  double dot_local = 0.0;
+  for (int64_t tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+    const int64_t row = tile * 256 + threadIdx.x;
+    if (row >= nrows) continue;
+    const int64_t lo = (int64_t)pos[row], hi = (int64_t)pos[row + 1];
+    double dv = pold[p_off + row];
+    if (DIR) {
+      dv = __dadd_rn(__dmul_rn(zw[p_off + row], 1.0), __dmul_rn(dv, beta));
+      pnew[p_off + row] = dv;
+    }
+    const int64_t bnd = abase + ((lo - abase) / SPMV_TILE + 1) * (int64_t)SPMV_TILE;  // first chunk boundary after lo
+    if (bnd >= hi) {
+      const double s = row_piece_sum_pcg<I, DIR>(crd, val, zw, pold, beta, lo, hi);
+      Ap[row] = __dadd_rn(s, 0.0);
+      dot_local = __dadd_rn(dot_local, __dmul_rn(s, dv));
+    } else {  // the pieces and their order of spmv_rowthread_kernel
+      double carried = row_piece_sum_pcg<I, DIR>(crd, val, zw, pold, beta, lo, bnd);
+      int64_t b0 = bnd;
+      while (b0 + SPMV_TILE < hi) {
+        carried = __dadd_rn(carried, row_piece_sum_pcg<I, DIR>(crd, val, zw, pold, beta, b0, b0 + SPMV_TILE));
+        b0 += SPMV_TILE;
+      }
+      const double s_last = row_piece_sum_pcg<I, DIR>(crd, val, zw, pold, beta, b0, hi);
+      Ap[row] = __dadd_rn(__dadd_rn(s_last, 0.0), carried);
+      dot_local = __dadd_rn(dot_local, __dmul_rn(__dadd_rn(carried, s_last), dv));
+    }
+  }
+  return dot_local;
+}
+
+template <typename I>
+__global__ void __launch_bounds__(256, 5)
+pcg_spmv_direction_kernel(const I *__restrict__ pos, const I *__restrict__ crd, const double *__restrict__ val,
+                          int64_t abase, int64_t nrows, int64_t ntiles, int64_t p_off, double *pw0, double *pw1,
+                          double *__restrict__ Ap, double *__restrict__ blk_partial, PcgExchange ex) {
+  __shared__ double s_red[8];
+  __shared__ double s_vals[3];
+  __shared__ int s_flag;
+  if (ex.fl[FL_DONE] != 0) return;
+  long long *hdr = reinterpret_cast<long long *>(ex.sc);
+  const long long stage = hdr[SC_STAGE], cur = hdr[SC_PCUR];
+  double beta = 0.0, rr = 0.0, rznew = 0.0, relres = 0.0;
+  unsigned long long iter = 0;
+  bool go = true;
+  if (stage == 0) {  // the first pass of a solve: p as initialised (its halo travelled as p)
+    if (ex.mbox != nullptr && !pcg_wait_halo(ex, &s_flag)) return;
+  } else if (ex.mbox != nullptr) {  // the head of pass C: every rank's r.r and r.z, stop test, beta
+    if (!pcg_wait_sums(ex, PH_B, s_vals, rr, rznew)) return;
+    relres = sqrt(rr) / ex.sc[SC_INITRES];
+    iter = (unsigned long long)ex.fl[FL_ITERS] + 1;    // i starts at 1
+    go = (relres > ex.tol) && (iter != ex.maxiter);    // ordered compare: NaN stops the loop
+    beta = rznew / ex.sc[SC_RZ];
+  } else {
+    beta = ex.sc[SC_BETA];  // derived by pass B's tail, which also ran the stop test
+  }
+  const double *pold = cur != 0 ? pw1 : pw0;
+  double *pnew = cur != 0 ? pw0 : pw1;
+  const double *zw = ex.zhalo;
+  double dot_local = 0.0;
+  if (go) {
+    if (stage == 0) {
+      dot_local = pcg_spmv_rows<I, false>(pos, crd, val, abase, nrows, ntiles, p_off, zw, pold, pnew, 0.0, Ap);
+    } else {
+      // halo entries of the new p's window, from the neighbours' rows of z and the old halo: the blocks share each range
+      for (int q = 0; q < ex.nranges; ++q) {
+        const long long start = ex.halo_ranges[2 * q], len = ex.halo_ranges[2 * q + 1];
+        for (long long j = (long long)blockIdx.x * 256 + threadIdx.x; j < len; j += (long long)gridDim.x * 256)
+          pnew[start + j] = __dadd_rn(__dmul_rn(zw[start + j], 1.0), __dmul_rn(pold[start + j], beta));
+      }
+      dot_local = pcg_spmv_rows<I, true>(pos, crd, val, abase, nrows, ntiles, p_off, zw, pold, pnew, beta, Ap);
+    }
+  }
+  const double t = block_sum(dot_local, s_red);
+  if (threadIdx.x == 0) blk_partial[blockIdx.x] = t;
+  if (!pcg_last_block(pcg_tickets(ex.sc) + 0, gridDim.x, &s_flag)) return;
+  if (threadIdx.x == 0) {
+    if (stage != 0 && ex.mbox != nullptr) {  // pass C's bookkeeping
+      ex.sc[SC_RR] = rr;
+      ex.sc[SC_RZNEW] = rznew;
+      ex.sc[SC_RELRES] = relres;
+      if (go) {
+        ex.sc[SC_BETA] = beta;
+        ex.sc[SC_RZ] = rznew;
+      } else {
+        ex.fl[FL_DONE] = 1;
+      }
+      __threadfence();
+      ex.fl[FL_ITERS] = (long long)iter;
+    }
+    if (stage == 0) hdr[SC_STAGE] = 1;
+    else if (go) hdr[SC_PCUR] = cur ^ 1;
+    __threadfence();
+  }
+  __syncthreads();
+  if (go) pcg_tail_pass_a(ex, blk_partial, gridDim.x, s_red);  // reads the iteration counter advanced above
+}
+
 template <typename I>
 __global__ void max_row_len_kernel(const I *__restrict__ pos, int64_t nrows, unsigned long long *out) {
   unsigned long long m = 0;
@@ -1238,6 +1373,29 @@ static bool uses_rowthread(const lapis_b200_csr *h) {
   return v.threads == 1 && h->max_row_len >= 0 && h->max_row_len <= SPMV_ROWTHREAD_MAX_LEN;
 }
 
+// Grid of the SpMV pass of a PCG iteration in both of its forms (spmv_rowthread_kernel with head and tail,
+// pcg_spmv_direction_kernel): the blocks that are resident at once for either kernel, looping over the row
+// tiles.  One size for both, so that the per-block partial sums of p.Ap group the same way and the two forms
+// return the same bits.
+template <typename I>
+static int pcg_pass_grid(const lapis_b200_csr *h, unsigned *grid) {
+  static int per_sm[64] = {0};
+  int dev = 0;
+  LAPIS_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return fail(LAPIS_EBADARG, "spmv: device index %d not supported", dev);
+  if (per_sm[dev] == 0) {
+    int na = 0, nb = 0;
+    LAPIS_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&na, spmv_rowthread_kernel<I, true, true>, 256, 0));
+    LAPIS_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, pcg_spmv_direction_kernel<I>, 256, 0));
+    const int m = na < nb ? na : nb;
+    per_sm[dev] = m > 0 ? m : 1;
+  }
+  const int64_t ntiles = (h->nrows + 255) / 256, resident = (int64_t)sm_count() * per_sm[dev];
+  const int64_t g = std::min<int64_t>(std::min<int64_t>(h->nblk, ntiles), resident);
+  *grid = (unsigned)(g < 1 ? 1 : g);
+  return LAPIS_OK;
+}
+
 template <typename I>
 static int launch_spmv(const lapis_b200_csr *h, const double *x, double *y, int accumulate,
                        const double *dotvec, double *blk_partial, const int *skip_flag,
@@ -1256,18 +1414,9 @@ static int launch_spmv(const lapis_b200_csr *h, const double *x, double *y, int 
         // as pass A of a PCG iteration: a grid of exactly the blocks that are resident at once, looping over the
         // row tiles, so that the block that finishes last has about a thousand partial sums to add, not one per
         // chunk of the plan (a grid larger than what is resident would run its last blocks on a nearly empty GPU)
-        static int per_sm[64] = {0};
-        int dev = 0;
-        LAPIS_CUDA_TRY(cudaGetDevice(&dev));
-        if (dev < 0 || dev >= 64) return fail(LAPIS_EBADARG, "spmv: device index %d not supported", dev);
-        if (per_sm[dev] == 0) {
-          int nb = 0;
-          LAPIS_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, spmv_rowthread_kernel<I, true, true>, 256, 0));
-          per_sm[dev] = nb > 0 ? nb : 1;
-        }
-        const int64_t resident = (int64_t)sm_count() * per_sm[dev];
-        const unsigned grid = (unsigned)std::min<int64_t>(std::min<int64_t>(h->nblk, ntiles), resident);
-        spmv_rowthread_kernel<I, true, true><<<grid < 1 ? 1 : grid, 256, 0, st>>>(pos, crd, h->val, abase, h->nrows, ntiles, x, y,
+        unsigned grid = 1;
+        LAPIS_TRY(pcg_pass_grid<I>(h, &grid));
+        spmv_rowthread_kernel<I, true, true><<<grid, 256, 0, st>>>(pos, crd, h->val, abase, h->nrows, ntiles, x, y,
                                                                                   accumulate, dotvec, blk_partial, skip_flag, *ex);
       }
       else if (dotvec != nullptr)
@@ -1374,6 +1523,26 @@ int spmv_launch_pcg_pass(const lapis_b200_csr *h, const double *x, double *y, co
                          const int *skip_flag, cudaStream_t st, const PcgExchange &ex) {
   if (h->idx_bytes == 4) return launch_spmv<int32_t>(h, x, y, 0, dotvec, blk_partial, skip_flag, st, &ex);
   return launch_spmv<int64_t>(h, x, y, 0, dotvec, blk_partial, skip_flag, st, &ex);
+}
+
+// Pass A with the direction update folded in (two-pass PCG); only where spmv_fuses_pcg_pass() is true.
+template <typename I>
+static int launch_pcg_direction_pass(const lapis_b200_csr *h, int64_t p_off, double *pw0, double *pw1, double *Ap,
+                                     double *blk_partial, cudaStream_t st, const PcgExchange &ex) {
+  const int64_t ntiles = (h->nrows + 255) / 256;
+  unsigned grid = 1;
+  LAPIS_TRY(pcg_pass_grid<I>(h, &grid));
+  pcg_spmv_direction_kernel<I><<<grid, 256, 0, st>>>(static_cast<const I *>(h->pos), static_cast<const I *>(h->crd),
+                                                                    h->val, h->base & ~(int64_t)3, h->nrows, ntiles, p_off, pw0,
+                                                                    pw1, Ap, blk_partial, ex);
+  LAPIS_CUDA_TRY(cudaGetLastError());
+  return LAPIS_OK;
+}
+int spmv_launch_pcg_direction_pass(const lapis_b200_csr *h, int64_t p_off, double *pw0, double *pw1, double *Ap,
+                                   double *blk_partial, cudaStream_t st, const PcgExchange &ex) {
+  if (!spmv_fuses_pcg_pass(h)) return fail(LAPIS_EBADARG, "pcg: the two-pass form needs the one-thread-per-row SpMV kernel");
+  if (h->idx_bytes == 4) return launch_pcg_direction_pass<int32_t>(h, p_off, pw0, pw1, Ap, blk_partial, st, ex);
+  return launch_pcg_direction_pass<int64_t>(h, p_off, pw0, pw1, Ap, blk_partial, st, ex);
 }
 
 template <typename I, int WARPS, int UNROLL>

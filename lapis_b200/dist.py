@@ -165,7 +165,7 @@ class DistPcg:
     GRAPH_UNROLL = 5  # iterations per launch of the larger of the two captured graphs
 
     def __init__(self, pos, crd, val, shape, b, dinv, device, group=None, use_graph: bool = True, comm: str = "p2p",
-                 transport_on_one_rank: bool = False, tune: bool = True, fused: bool = True):
+                 transport_on_one_rank: bool = False, tune: bool = True, fused: bool = True, two_pass: bool = True):
         from ._lib import check, load
         from .device import CsrMatrix
         self._check, self._lib = check, load()
@@ -177,6 +177,8 @@ class DistPcg:
         # fused: one iteration is three launches (sums and exchanges inside the passes); False keeps the
         # older form with separate summing / exchange kernels between the passes
         self.fused = fused
+        # two_pass: fold the direction update into the next SpMV pass where the matrix allows it (two launches)
+        self.two_pass = two_pass
         n_global = int(shape[0])
         if shape[0] != shape[1]:
             raise ValueError("pcg: matrix is not square")
@@ -317,16 +319,31 @@ class DistPcg:
             self._exchange_struct = ex
         return ctypes.byref(ex)
 
+    def _two_pass(self) -> bool:
+        """Whether an iteration is two launches (matrices served by the one-thread-per-row SpMV kernel)."""
+        tp = getattr(self, "_two_pass_cached", None)
+        if tp is None:
+            tp = bool(self.two_pass and self.fused and self.comm in ("p2p", "none")
+                      and self._lib.lapis_b200_pcg_folds_direction(self.matrix.handle))
+            self._two_pass_cached = tp
+        return tp
+
     def _iteration(self, tol: float, maxiter: int):
         lib, check, w = self._lib, self._check, ctypes.c_void_p(self.work.data_ptr())
         if self.fused and self.comm in ("p2p", "none"):
             # three launches: the sums are added in the last block of each pass and, with the peer-to-peer
             # transport, the exchanges happen inside the passes
             ex = self._exchange()
-            check(lib.lapis_b200_pcg_fused_spmv(w, self.matrix.handle, self.n_p, self.p_off, tol, maxiter, ex, self._stream()))
+            if self._two_pass():
+                # two launches: the direction update of the iteration before is folded into the SpMV pass
+                check(lib.lapis_b200_pcg_fused_spmv_direction(w, self.matrix.handle, self.n_p, self.p_off, tol, maxiter, ex,
+                                                              self._stream()))
+            else:
+                check(lib.lapis_b200_pcg_fused_spmv(w, self.matrix.handle, self.n_p, self.p_off, tol, maxiter, ex, self._stream()))
             check(lib.lapis_b200_pcg_fused_update(w, self.n, self.n_p, self.p_off, ctypes.c_void_p(self.dinv.data_ptr()),
                                                   ctypes.c_void_p(self.x.data_ptr()), tol, maxiter, ex, self._stream()))
-            check(lib.lapis_b200_pcg_fused_direction(w, self.n, self.n_p, self.p_off, tol, maxiter, ex, self._stream()))
+            if not self._two_pass():
+                check(lib.lapis_b200_pcg_fused_direction(w, self.n, self.n_p, self.p_off, tol, maxiter, ex, self._stream()))
             return
         single = 1 if self.comm == "none" else 0
         p2p = self.comm == "p2p"
@@ -415,6 +432,12 @@ class DistPcg:
                 i += burst
                 fl = self.flags.cpu()
                 done = bool(fl[0].item())
+            if not done and self.comm == "p2p" and self._two_pass():
+                # with an exchange the stop test of an iteration runs at the head of the next SpMV pass: one more
+                # (it stops there: the iteration count has reached maxiter)
+                self._check(self._lib.lapis_b200_pcg_fused_spmv_direction(
+                    ctypes.c_void_p(self.work.data_ptr()), self.matrix.handle, self.n_p, self.p_off, tol, maxiter,
+                    self._exchange(), self._stream()))
             iters = int(self.flags[1].item())
             relres = float(self.sc[5].item())
             err = self.comm_error()

@@ -604,6 +604,56 @@ def test_pcg_laplacian_converges_and_graph_matches_eager():
     assert np.linalg.norm(res) <= 2e-8 * np.linalg.norm(d["b"])
 
 
+def test_pcg_two_launches_per_iteration_repeat_the_three_launch_form():
+    """On matrices served by the one-thread-per-row SpMV kernel the direction update is folded into the next
+    SpMV pass (two launches per iteration): x, the iteration count and the residual are those of the
+    three-launch form bit for bit -- without and with the exchange kernels in the loop (the rank as its own
+    peer), eager and from captured graphs, for a solve that converges and for one that stops at maxiter."""
+    from lapis_b200._lib import check, load
+    from lapis_b200.dist import DistPcg
+    dev = _dev()
+    lib = load()
+    for grid, idx in ((64, np.int32), (96, np.int64)):
+        d = w.pcg_laplacian(grid, idx_dtype=idx)
+        n = d["shape"][0]
+        args = (d["pos"], d["crd"], d["val"], (n, n), d["b"], d["dinv"], dev)
+        check(lib.lapis_b200_spmv_select_kernel(1, 0, 1))   # the one-thread-per-row kernel, whatever the tuner timed
+        try:
+            for transport in (False, True):
+                kw = dict(comm="p2p", transport_on_one_rank=transport)
+                three = DistPcg(*args, use_graph=False, two_pass=False, **kw)
+                assert not three._two_pass()
+                for tol, maxiter in ((1e-9, 500), (0.0, 37)):
+                    xr, ir, rr = three.solve(tol, maxiter, check_every=8)
+                    xr = xr.clone()
+                    for use_graph in (False, True):
+                        two = DistPcg(*args, use_graph=use_graph, **kw)
+                        assert two._two_pass()
+                        for _ in range(2):   # the second solve starts from the state the first one left
+                            x, it, rel = two.solve(tol, maxiter, check_every=8)
+                            assert it == ir and rel == rr and torch.equal(x, xr), (grid, transport, tol, use_graph)
+                            assert two.comm_error() == 0.0
+        finally:
+            check(lib.lapis_b200_spmv_select_kernel(0, 0, 0))
+    # the C-level solver takes the same form by itself
+    from lapis_b200.device import CsrMatrix
+    d = w.pcg_laplacian(64)
+    n = d["shape"][0]
+    A = CsrMatrix.from_host(d["pos"], d["crd"], d["val"], (n, n), dev)
+    A.tune()
+    bd, dd = torch.as_tensor(d["b"]).to(dev), torch.as_tensor(d["dinv"]).to(dev)
+    x0, i0, r0 = A.pcg(bd, dd, 1e-9, 500)
+    check(lib.lapis_b200_spmv_select_kernel(1, 0, 1))
+    try:
+        assert lib.lapis_b200_pcg_folds_direction(A._h) == 1
+        x1, i1, r1 = A.pcg(bd, dd, 1e-9, 500)
+    finally:
+        check(lib.lapis_b200_spmv_select_kernel(0, 0, 0))
+    xo, io, ro = oracle.pcg(d["pos"], d["crd"], d["val"], d["b"], d["dinv"], 1e-9, 500)
+    assert abs(i1 - io) <= 2 and r1 <= 1e-9
+    assert np.max(np.abs(x1.cpu().numpy() - xo)) <= 1e-6 * np.max(np.abs(xo))
+
+
 def test_pcg_peer_transport_on_one_rank():
     """The peer-to-peer exchange kernels with the rank as its own only peer (push, then wait, in stream
     order: nothing waits on another launch): same bits as the fused single-rank scalar steps, over
