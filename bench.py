@@ -349,6 +349,7 @@ NCU_TRAFFIC = {
     "bgemm": 1.036e9,               # profiles/bgemm_tcgen05_kernel.md (4096 x 128^3)
     "gemm": 8.15e9,                 # profiles/bgemm_tcgen05_kernel.md (8192^3, K in segments of 1024)
     "pcg": 2.715e9,                 # profiles/pcg_iteration_config5.md (the three kernels of one iteration)
+    "pcg_two_pass": 2.565e9,        # same file (the two kernels of one iteration)
 }
 
 
@@ -596,7 +597,7 @@ def run_pcg(args, d, hx: Harness, iterations: int, with_e2e: bool):
     roof = hx.hbm_roofline(d["bytes_per_step"] / world, ms_it,
                            "pcg_spmv_direction_kernel + pcg_update_fused_kernel" if solver.fused and solver._two_pass() else
                            "spmv_rowthread_kernel (pass A) + pcg_update_fused_kernel + pcg_direction(_fused)_kernel",
-                           NCU_TRAFFIC["pcg"] / world)
+                           NCU_TRAFFIC["pcg_two_pass" if solver.fused and solver._two_pass() else "pcg"] / world)
     # check: the relative residual after three iterations against the CPU oracle's (same recurrences, full grid)
     _, it3, rel3 = solver.solve(0.0, 3, check_every=3)
     ok = True
